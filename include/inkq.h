@@ -1,0 +1,150 @@
+/*
+ * inkq.h - C ABI of the B200 (sm_100a) A8W4 quantized-matmul path.
+ *
+ * This is the one boundary between host code (the C++ linear layer that mirrors
+ * Qwen3.Ink.Cpp's Qwen_Linear_with_bias_Int4, a test driver, a model runtime) and
+ * the CUDA kernels.  Plain pointers and sizes only.  Every entry point returns an
+ * inkq_status (0 = ok), never throws and never aborts; inkq_last_error() gives
+ * the message of the last failure.  There is no CPU fallback: without a CUDA
+ * device inkq_ctx_create() fails.
+ *
+ * Each declaration cites the reference interface it stands in for, as
+ * file:line inside the reference project.
+ *
+ * Logical ("on-disk") weight format accepted by inkq_weight_create, exactly what
+ * the reference linear layer loads (qwen3/include/qwen/QwenOperator.h:128-140):
+ *   nib  u8  [N][K/2]  byte[32g+e] = q[64g+e] | q[64g+32+e] << 4   (AWQ interleave)
+ *   d    f32 [N][K/32] block scales
+ *   m    f32 [N][K/32] block mins        (A81W41 / W41; NULL otherwise)
+ *   zp   u8  [N][K/32] block zero points (A80W4Z; NULL otherwise)
+ * N % 8 == 0 and K % 64 == 0, as the reference requires
+ * (qwen3/src/qwen/quantized_gemx_kernels.cc:359-361).
+ */
+#ifndef INKQ_H
+#define INKQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    INKQ_OK = 0,
+    INKQ_ERR_INVALID = 1,     /* bad argument (shape, null pointer, handle) */
+    INKQ_ERR_CUDA = 2,        /* a CUDA runtime/driver call failed */
+    INKQ_ERR_ALLOC = 3,       /* device or host allocation failed */
+    INKQ_ERR_UNSUPPORTED = 4, /* valid request this build cannot serve */
+    INKQ_ERR_TIMEOUT = 5      /* a bounded device-side wait ran out; the context stays usable */
+} inkq_status;
+
+/* Quantization schemes (reference: enum LinearKernelType, qwen3/include/qwen/QwenConfig.h:13). */
+typedef enum {
+    INKQ_A81W41 = 0, /* Q8_1 activations x Q4_1 weights: sum_b d_a*d_w*I + m_w*s_a */
+    INKQ_A80W40 = 1, /* Q8_0 activations x Q4_0 weights (q-8) */
+    INKQ_A80W4Z = 2, /* Q8_0 activations x zero-point int4 weights (q-zp) */
+    INKQ_W41 = 3     /* weight-only Q4_1, fp16 activations, fp32 accumulate */
+} inkq_scheme;
+
+/* Activation quantizer variants. */
+typedef enum {
+    INKQ_Q8_0_F16 = 0, /* quantize_row_q8_0_repack        quantized_gemx_kernels.cc:584-691 */
+    INKQ_Q8_1_F16 = 1, /* quantize_row_q8_1_repack_fp16   quantized_gemx_kernels.cc:693-801 */
+    INKQ_Q8_1_F32 = 2  /* quantize_row_q8_1_repack_fp32   quantized_gemx_kernels.cc:803-911 */
+} inkq_qmode;
+
+/* How a weight's block scales are held on the device. */
+typedef enum {
+    INKQ_SCALES_F32 = 0, /* as given (what gemm_repack_A81W41_fp32 sees; repack_w81_weight_fp32, QwenOperator.cc:852-892) */
+    INKQ_SCALES_F16 = 1  /* rounded to fp16 (what the three fp16 kernels see; repack_w81_weight_fp16 / repack_w80_weight, QwenOperator.cc:757-850) */
+} inkq_scale_mode;
+
+typedef struct inkq_ctx inkq_ctx;       /* device, stream, scratch; stands in for ModelContext, QwenOperator.h:34-43 */
+typedef struct inkq_weight inkq_weight; /* one linear layer's re-tiled weights; stands in for weight_repack_fp16/_fp32, QwenOperator.h:102-103 */
+typedef struct inkq_act inkq_act;       /* quantized activations; stands in for ModelContext::activation_buffer */
+typedef struct inkq_f16w inkq_f16w;     /* fp16 weight matrix (lm_head) */
+
+/* ---- context ------------------------------------------------------------ */
+/* stream: a cudaStream_t cast to void*, or NULL for the default stream. */
+int inkq_ctx_create(int device, void *stream, inkq_ctx **out);
+int inkq_ctx_destroy(inkq_ctx *ctx);
+int inkq_ctx_set_stream(inkq_ctx *ctx, void *stream);
+int inkq_ctx_synchronize(inkq_ctx *ctx);
+/* Message of the last error on this context (or of the last context-less error when ctx is NULL). */
+const char *inkq_last_error(const inkq_ctx *ctx);
+/* Number of kernels this library has launched on the context since creation. */
+uint64_t inkq_launch_count(const inkq_ctx *ctx);
+
+/* ---- load-time weight re-tiling ------------------------------------------
+ * Replaces repack_w80_weight / repack_w81_weight_fp16 / repack_w81_weight_fp32
+ * (qwen3/include/qwen/QwenOperator.h:82-84; QwenOperator.cc:757-892) and the
+ * constructor's load (QwenOperator.h:112-157).  Host pointers in the logical
+ * format; rows [n_begin, n_end) are uploaded and re-tiled on the device into the
+ * 128-row, chunk-swizzled sm_100a layout (n_begin = 0, n_end = N for the whole
+ * matrix; a sub-range is one tensor-parallel column shard).  *_dev takes device
+ * pointers instead. */
+int inkq_weight_create(inkq_ctx *ctx, int scheme, int scale_mode, int N, int K,
+                       const uint8_t *nib, const float *d, const float *m, const uint8_t *zp,
+                       int n_begin, int n_end, inkq_weight **out);
+int inkq_weight_create_dev(inkq_ctx *ctx, int scheme, int scale_mode, int N, int K,
+                           const uint8_t *nib_dev, const float *d_dev, const float *m_dev, const uint8_t *zp_dev,
+                           int n_begin, int n_end, inkq_weight **out);
+int inkq_weight_destroy(inkq_weight *w);
+/* rows = n_end - n_begin, device bytes held. */
+int inkq_weight_info(const inkq_weight *w, int *rows, int *K, int *scheme, size_t *device_bytes);
+/* Inverse of the re-tiling, for round-trip checks: writes the logical format of
+ * the held rows to host buffers (any of the outputs may be NULL). d/m come back as
+ * the values the kernels see (fp16-rounded when scale_mode is F16). */
+int inkq_weight_export(inkq_ctx *ctx, const inkq_weight *w, uint8_t *nib, float *d, float *m, uint8_t *zp);
+
+/* ---- activation quantizer -------------------------------------------------
+ * Replaces quantize_row_q8_0_repack / quantize_row_q8_1_repack_fp16 / _fp32
+ * (QwenOperator.h:276-278).  x_dev: fp32 [M][K] on the device. */
+int inkq_act_create(inkq_ctx *ctx, int max_rows, int K, inkq_act **out);
+int inkq_act_destroy(inkq_act *a);
+int inkq_quantize(inkq_ctx *ctx, int qmode, const float *x_dev, int M, int K, inkq_act *act);
+/* Copies the quantized form to host: q s8 [M][K], d f32 [M][K/32], s f32 [M][K/32]
+ * (s = 0 for Q8_0), isum s32 [M][K/32] (block sums of q).  Any output may be NULL. */
+int inkq_act_export(inkq_ctx *ctx, const inkq_act *act, int8_t *q, float *d, float *s, int32_t *isum);
+
+/* ---- matmuls ---------------------------------------------------------------
+ * inkq_gemm  : tcgen05 int8 tensor-core path, any M >= 1. Replaces
+ *              gemm_repack_A81W41_fp32 / gemm_repack_A80W40 (QwenOperator.h:280-298).
+ * inkq_gemv  : bandwidth path, M == 1. Replaces gemv_repack_A81W41_fp16 /
+ *              gemv_repack_A80W40 (QwenOperator.h:286-304).
+ * inkq_gemm_simt : plain CUDA-core path kept as an on-device cross-check of the
+ *              tensor-core kernel (same layouts, same per-output operation order).
+ * C_dev: fp32 [M][ldc] on the device; columns [0, rows) of each row are written. */
+int inkq_gemm(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, float *C_dev, int ldc);
+int inkq_gemv(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, float *C_dev);
+int inkq_gemm_simt(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, float *C_dev, int ldc);
+/* Every int32 block dot, dots_dev s32 [M][rows][K/32]; for bit-exactness checks. */
+int inkq_debug_block_dots(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, int32_t *dots_dev);
+/* As inkq_debug_block_dots but produced by the tensor-core kernel's own MMA path. */
+int inkq_debug_block_dots_tc(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, int32_t *dots_dev);
+
+/* ---- the linear layer's forward ---------------------------------------------
+ * Replaces Qwen_Linear_with_bias_Int4::forward (QwenOperator.h:224,
+ * QwenOperator.cc:80-124): quantize, then M > 1 -> QGEMM, M == 1 -> QGEMV.  As
+ * in the reference, an A81W41 layer quantizes with Q8_1/fp32 scales for M > 1
+ * and Q8_1/fp16 scales for M == 1; A80 schemes use Q8_0/fp16.
+ * inkq_linear       : x and C on the device (uses the context's activation scratch).
+ * inkq_linear_host  : x and C in host memory; the copies are part of the call. */
+int inkq_linear(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, int M, float *C_dev, int ldc);
+int inkq_linear_host(inkq_ctx *ctx, const inkq_weight *w, const float *x_host, int M, float *C_host, int ldc);
+
+/* ---- weight-only W41 (fp16 activations) and fp16 lm_head ---------------------
+ * No C++ kernel exists in the reference for these two; they follow
+ * notebooks/evaluate-qwen3_8b_W4.ipynb cell 13 and, for lm_head, the fp32 GEMV
+ * gemv_fp32_rcr_mt_impl_1 (qwen3/src/qwen/fp32_gemx_kernels_rcr.cc:494-507). */
+int inkq_gemm_w41_f16act(inkq_ctx *ctx, const uint16_t *a16_dev, int M, const inkq_weight *w, float *C_dev, int ldc);
+int inkq_f16w_create(inkq_ctx *ctx, int N, int K, const uint16_t *w16_host, int n_begin, int n_end, inkq_f16w **out);
+int inkq_f16w_create_dev(inkq_ctx *ctx, int N, int K, const uint16_t *w16_dev, int n_begin, int n_end, inkq_f16w **out);
+int inkq_f16w_destroy(inkq_f16w *w);
+int inkq_f16w_matmul(inkq_ctx *ctx, const inkq_f16w *w, const float *x_dev, int M, float *C_dev, int ldc);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INKQ_H */

@@ -1,0 +1,1 @@
+/* empty: the reference only uses cblas under #ifdef OPENBLAS */

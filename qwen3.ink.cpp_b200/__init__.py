@@ -1,0 +1,264 @@
+"""B200-native A8W4 quantized-matmul path of Qwen3.Ink.Cpp: Python driver side.
+
+The product is the CUDA library (csrc/ -> libinkq.so) behind the C ABI declared in
+include/inkq.h, plus the C++ host mirror of the reference's linear layer in host/.
+This package is the thin ctypes binding tests and benchmarks drive it with.  It
+never computes anything itself: if libinkq.so is missing or no B200 is present the
+calls raise, there is no CPU fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import build as _build
+from . import synth  # noqa: F401  (re-exported)
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libinkq.so")
+
+# enums of include/inkq.h
+A81W41, A80W40, A80W4Z, W41 = 0, 1, 2, 3
+Q8_0_F16, Q8_1_F16, Q8_1_F32 = 0, 1, 2
+SCALES_F32, SCALES_F16 = 0, 1
+OK, ERR_INVALID, ERR_CUDA, ERR_ALLOC, ERR_UNSUPPORTED, ERR_TIMEOUT = range(6)
+
+# every symbol include/inkq.h declares
+SYMBOLS = [
+    "inkq_ctx_create", "inkq_ctx_destroy", "inkq_ctx_set_stream", "inkq_ctx_synchronize", "inkq_last_error",
+    "inkq_launch_count", "inkq_weight_create", "inkq_weight_create_dev", "inkq_weight_destroy", "inkq_weight_info",
+    "inkq_weight_export", "inkq_act_create", "inkq_act_destroy", "inkq_quantize", "inkq_act_export", "inkq_gemm",
+    "inkq_gemv", "inkq_gemm_simt", "inkq_debug_block_dots", "inkq_debug_block_dots_tc", "inkq_linear",
+    "inkq_linear_host", "inkq_gemm_w41_f16act", "inkq_f16w_create", "inkq_f16w_create_dev", "inkq_f16w_destroy",
+    "inkq_f16w_matmul",
+]
+
+
+class InkqError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"inkq status {code}: {msg}")
+        self.code = code
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads libinkq.so (must have been built: `__graft_entry__.build()`)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise FileNotFoundError(f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'`")
+        L = C.CDLL(LIB_PATH)
+        L.inkq_last_error.restype = C.c_char_p
+        L.inkq_last_error.argtypes = [C.c_void_p]
+        L.inkq_launch_count.restype = C.c_uint64
+        L.inkq_launch_count.argtypes = [C.c_void_p]
+        for name in SYMBOLS:
+            fn = getattr(L, name)
+            if name not in ("inkq_last_error", "inkq_launch_count"):
+                fn.restype = C.c_int
+        _lib = L
+    return _lib
+
+
+def _dp(t):
+    """Device pointer of a torch tensor (or an int address, or None)."""
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return C.c_void_p(t)
+    return C.c_void_p(t.data_ptr())
+
+
+def _hp(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+class Context:
+    """One device + stream.  Mirrors the role of the reference's ModelContext
+    (qwen3/include/qwen/QwenOperator.h:34-43): it owns the activation scratch."""
+
+    def __init__(self, device: int = 0, stream: int | None = None):
+        self.L = lib()
+        h = C.c_void_p()
+        rc = self.L.inkq_ctx_create(int(device), C.c_void_p(stream or 0), C.byref(h))
+        if rc != OK:
+            raise InkqError(rc, self.L.inkq_last_error(None).decode())
+        self.h = h
+        self.device = device
+
+    def check(self, rc: int):
+        if rc != OK:
+            raise InkqError(rc, self.L.inkq_last_error(self.h).decode())
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.inkq_ctx_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_stream(self, stream: int):
+        self.check(self.L.inkq_ctx_set_stream(self.h, C.c_void_p(stream)))
+
+    def synchronize(self):
+        self.check(self.L.inkq_ctx_synchronize(self.h))
+
+    @property
+    def launches(self) -> int:
+        return int(self.L.inkq_launch_count(self.h))
+
+    # ---- weights ----------------------------------------------------------------
+    def weight(self, scheme: int, scale_mode: int, nib, d, m=None, zp=None, n_begin: int = 0, n_end: int | None = None):
+        """Host NumPy arrays in the logical disk format -> device-resident re-tiled weight."""
+        nib = np.ascontiguousarray(nib, np.uint8)
+        d = np.ascontiguousarray(d, np.float32)
+        m = None if m is None else np.ascontiguousarray(m, np.float32)
+        zp = None if zp is None else np.ascontiguousarray(zp, np.uint8)
+        N, K = nib.shape[0], nib.shape[1] * 2
+        h = C.c_void_p()
+        self.check(self.L.inkq_weight_create(self.h, scheme, scale_mode, N, K, _hp(nib), _hp(d), _hp(m), _hp(zp),
+                                             n_begin, N if n_end is None else n_end, C.byref(h)))
+        return Weight(self, h, scheme)
+
+    def weight_dev(self, scheme: int, scale_mode: int, N: int, K: int, nib, d, m=None, zp=None, n_begin: int = 0,
+                   n_end: int | None = None):
+        """Same from device tensors (torch) holding the logical format."""
+        h = C.c_void_p()
+        self.check(self.L.inkq_weight_create_dev(self.h, scheme, scale_mode, N, K, _dp(nib), _dp(d), _dp(m), _dp(zp),
+                                                 n_begin, N if n_end is None else n_end, C.byref(h)))
+        return Weight(self, h, scheme)
+
+    def act(self, max_rows: int, K: int):
+        h = C.c_void_p()
+        self.check(self.L.inkq_act_create(self.h, max_rows, K, C.byref(h)))
+        return Act(self, h, K)
+
+    def f16w(self, w16: np.ndarray, n_begin: int = 0, n_end: int | None = None):
+        w16 = np.ascontiguousarray(w16, np.float16)
+        N, K = w16.shape
+        h = C.c_void_p()
+        self.check(self.L.inkq_f16w_create(self.h, N, K, _hp(w16), n_begin, N if n_end is None else n_end, C.byref(h)))
+        return F16W(self, h, (N if n_end is None else n_end) - n_begin, K)
+
+    def f16w_dev(self, w16, N: int, K: int, n_begin: int = 0, n_end: int | None = None):
+        h = C.c_void_p()
+        self.check(self.L.inkq_f16w_create_dev(self.h, N, K, _dp(w16), n_begin, N if n_end is None else n_end, C.byref(h)))
+        return F16W(self, h, (N if n_end is None else n_end) - n_begin, K)
+
+    # ---- kernels ------------------------------------------------------------------
+    def quantize(self, act: "Act", x, M: int, qmode: int):
+        self.check(self.L.inkq_quantize(self.h, qmode, _dp(x), M, act.K, act.h))
+
+    def gemm(self, act, w, Cdev, ldc: int):
+        self.check(self.L.inkq_gemm(self.h, act.h, w.h, _dp(Cdev), ldc))
+
+    def gemm_simt(self, act, w, Cdev, ldc: int):
+        self.check(self.L.inkq_gemm_simt(self.h, act.h, w.h, _dp(Cdev), ldc))
+
+    def gemv(self, act, w, Cdev):
+        self.check(self.L.inkq_gemv(self.h, act.h, w.h, _dp(Cdev)))
+
+    def block_dots(self, act, w, dots_dev, tensor_core: bool = False):
+        fn = self.L.inkq_debug_block_dots_tc if tensor_core else self.L.inkq_debug_block_dots
+        self.check(fn(self.h, act.h, w.h, _dp(dots_dev)))
+
+    def linear(self, w, x, M: int, Cdev, ldc: int):
+        """Qwen_Linear_with_bias_Int4::forward on device buffers."""
+        self.check(self.L.inkq_linear(self.h, w.h, _dp(x), M, _dp(Cdev), ldc))
+
+    def linear_host(self, w, x_host, M: int, C_host, ldc: int):
+        """Same with host buffers (NumPy arrays, or torch CPU tensors, ideally pinned)."""
+        xp = x_host.ctypes.data_as(C.c_void_p) if isinstance(x_host, np.ndarray) else C.c_void_p(x_host.data_ptr())
+        cp = C_host.ctypes.data_as(C.c_void_p) if isinstance(C_host, np.ndarray) else C.c_void_p(C_host.data_ptr())
+        self.check(self.L.inkq_linear_host(self.h, w.h, xp, M, cp, ldc))
+
+    def gemm_w41_f16act(self, a16, M: int, w, Cdev, ldc: int):
+        self.check(self.L.inkq_gemm_w41_f16act(self.h, _dp(a16), M, w.h, _dp(Cdev), ldc))
+
+    def f16w_matmul(self, w, x, M: int, Cdev, ldc: int):
+        self.check(self.L.inkq_f16w_matmul(self.h, w.h, _dp(x), M, _dp(Cdev), ldc))
+
+
+class Weight:
+    def __init__(self, ctx: Context, h, scheme: int):
+        self.ctx, self.h, self.scheme = ctx, h, scheme
+        rows, K, sch, nbytes = C.c_int(), C.c_int(), C.c_int(), C.c_size_t()
+        ctx.check(ctx.L.inkq_weight_info(h, C.byref(rows), C.byref(K), C.byref(sch), C.byref(nbytes)))
+        self.rows, self.K, self.device_bytes = rows.value, K.value, nbytes.value
+
+    def export(self):
+        """Inverse re-tiling -> (nib, d, m, zp) host arrays of the held rows."""
+        nb = self.K // 32
+        nib = np.empty((self.rows, self.K // 2), np.uint8)
+        d = np.empty((self.rows, nb), np.float32)
+        m = np.empty((self.rows, nb), np.float32)
+        zp = np.empty((self.rows, nb), np.uint8)
+        self.ctx.check(self.ctx.L.inkq_weight_export(self.ctx.h, self.h, _hp(nib), _hp(d), _hp(m), _hp(zp)))
+        return nib, d, m, zp
+
+    def close(self):
+        if self.h:
+            self.ctx.L.inkq_weight_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            if self.ctx.h:
+                self.close()
+        except Exception:
+            pass
+
+
+class Act:
+    def __init__(self, ctx: Context, h, K: int):
+        self.ctx, self.h, self.K = ctx, h, K
+
+    def export(self, M: int):
+        nb = self.K // 32
+        q = np.empty((M, self.K), np.int8)
+        d = np.empty((M, nb), np.float32)
+        s = np.empty((M, nb), np.float32)
+        isum = np.empty((M, nb), np.int32)
+        self.ctx.check(self.ctx.L.inkq_act_export(self.ctx.h, self.h, _hp(q), _hp(d), _hp(s), _hp(isum)))
+        return q, d, s, isum
+
+    def close(self):
+        if self.h:
+            self.ctx.L.inkq_act_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            if self.ctx.h:
+                self.close()
+        except Exception:
+            pass
+
+
+class F16W:
+    def __init__(self, ctx: Context, h, rows: int, K: int):
+        self.ctx, self.h, self.rows, self.K = ctx, h, rows, K
+
+    def close(self):
+        if self.h:
+            self.ctx.L.inkq_f16w_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            if self.ctx.h:
+                self.close()
+        except Exception:
+            pass
+
+
+def build(force: bool = False) -> None:
+    _build.build_all(force)

@@ -1,0 +1,122 @@
+// Internal definitions shared by the .cu files: handle structs, device layouts,
+// error plumbing.  Nothing here is part of the public ABI (see include/inkq.h).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <string>
+
+#include "inkq.h"
+
+namespace inkq {
+
+constexpr int QK = 32;       // quantization block (reference: QK, qwen3/include/qwen/QwenConfig.h:8)
+constexpr int TILE_N = 128;  // weight rows per device tile (one UMMA M=128 operand)
+
+// ---------------------------------------------------------------------------
+// Device layouts
+//
+// Weights of one layer (rows R = n_end - n_begin, T = ceil(R/128) tiles, P = K/64 pairs):
+//   nibT  u8     [T][P][128][32]   row r of a tile holds the layer's 32 disk bytes of pair p
+//                                  (low nibble = element e of block 2p, high nibble = element e
+//                                  of block 2p+1); its two 16-byte chunks are stored at chunk
+//                                  position c ^ ((r >> 2) & 1) so that 8 consecutive rows read
+//                                  the same logical chunk from 8 distinct bank groups.
+//   sc32  float4 [T][P][128]       {d_lo, d_hi, m_lo, m_hi}, only when scales are kept in fp32
+//   sc16  half x4[T][P][128]       the same rounded to fp16 (always present)
+//   zpT   u8 x2  [T][P][128]       {z_lo, z_hi}: 0 (Q4_1), 8 (Q4_0) or the block zero point
+// Rows beyond R inside the last tile hold zero nibbles, zero scales, zero z.
+// One (tile, pair) is 4096 contiguous bytes of nibbles: a pipeline stage is one
+// untiled bulk copy.
+//
+// Quantized activations (M rows, NB = K/32 blocks, M_ld = round_up(M, 4)):
+//   q     s8  [M][K]      row-major (K-major operand for the MMA, TMA-tiled with 128B swizzle)
+//   d, s  f32 [NB][M_ld]  block scale and scaled block sum, block-major so that one
+//                         tile's columns of one block are contiguous
+//   isum  s32 [NB][M_ld]  integer block sums of q
+// ---------------------------------------------------------------------------
+__host__ __device__ inline size_t nib_offset(int P, int t, int p, int r, int chunk)
+{
+    return ((static_cast<size_t>(t) * P + p) * TILE_N + r) * 32 + static_cast<size_t>((chunk ^ ((r >> 2) & 1)) * 16);
+}
+
+struct Weight {
+    inkq_ctx *ctx;
+    int scheme, scale_mode;
+    int rows, K, tiles, pairs;
+    uint8_t *nibT;
+    float4 *sc32;   // may be null
+    uint2 *sc16;    // 4 x fp16
+    uchar2 *zpT;
+    size_t bytes;
+};
+
+struct Act {
+    inkq_ctx *ctx;
+    int max_rows, K;
+    int M, M_ld, qmode;  // of the last quantize call
+    int8_t *q;
+    float *d, *s;
+    int32_t *isum;
+};
+
+struct F16W {
+    inkq_ctx *ctx;
+    int rows, K;
+    uint16_t *w;
+    size_t bytes;
+};
+
+}  // namespace inkq
+
+struct inkq_ctx {
+    int device;
+    cudaStream_t stream;
+    std::string err;
+    uint64_t launches;
+    int num_sms;
+    int *dev_flag;        // device word set by a kernel whose bounded wait ran out
+    inkq::Act *scratch_act;  // activation scratch of inkq_linear (grown on demand)
+    float *lin_x, *lin_c;    // device staging of inkq_linear_host
+    size_t lin_x_cap, lin_c_cap;
+    float *pin_x, *pin_c;    // pinned host staging of inkq_linear_host
+    size_t pin_x_cap, pin_c_cap;
+    void *encode_tiled;      // cuTensorMapEncodeTiled entry point
+};
+struct inkq_weight : inkq::Weight {};
+struct inkq_act : inkq::Act {};
+struct inkq_f16w : inkq::F16W {};
+
+namespace inkq {
+
+void set_global_error(const std::string &msg);
+int fail(inkq_ctx *ctx, int code, const std::string &msg);
+
+#define INKQ_CUDA(ctx, call)                                                                         \
+    do {                                                                                             \
+        cudaError_t e__ = (call);                                                                    \
+        if (e__ != cudaSuccess)                                                                      \
+            return ::inkq::fail((ctx), INKQ_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e__)); \
+    } while (0)
+
+#define INKQ_REQUIRE(ctx, cond, msg)                                            \
+    do {                                                                        \
+        if (!(cond)) return ::inkq::fail((ctx), INKQ_ERR_INVALID, (msg));       \
+    } while (0)
+
+// Checks the launch, counts it.
+int after_launch(inkq_ctx *ctx, const char *what);
+
+// kernels' host launchers (defined in the respective .cu files)
+int launch_quantize(inkq_ctx *ctx, int qmode, const float *x, int M, int K, Act *a);
+int launch_retile(inkq_ctx *ctx, Weight *w, const uint8_t *nib, const float *d, const float *m, const uint8_t *zp, int n_begin);
+int launch_export(inkq_ctx *ctx, const Weight *w, uint8_t *nib, float *d, float *m, uint8_t *zp);
+int launch_gemv(inkq_ctx *ctx, const Act *a, const Weight *w, float *C);
+int launch_gemm_simt(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc);
+int launch_block_dots(inkq_ctx *ctx, const Act *a, const Weight *w, int32_t *dots);
+int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc, int32_t *dots);
+int launch_gemm_w41_f16(inkq_ctx *ctx, const uint16_t *a16, int M, const Weight *w, float *C, int ldc);
+int launch_f16w_matmul(inkq_ctx *ctx, const F16W *w, const float *x, int M, float *C, int ldc);
+
+}  // namespace inkq
