@@ -1,0 +1,379 @@
+#!/usr/bin/env python
+"""Benchmark of the A8W4 quantized-matmul path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One JSON line on stdout (rank 0).  A "step" is one forward of the quantized linear
+layer (activation quantizer + QGEMM) on synthetic inputs of the prefill gate_proj
+shape: M=322 activations x K=4096, N=12288 A81W41 weights (fp32 block scales).
+  value   whole-job int8 TOPS (2*M*N*K per step) with inputs resident in HBM
+  e2e     the same metric through the host-buffer entry point (inkq_linear_host):
+          pinned host activations in, host result out, copies inside the timed region
+  N > 1   the weight rows (output columns) are sharded across the ranks, every rank
+          quantizes the full activations, runs its shard and an NCCL all-gather
+          assembles the fp32 output on every rank (strong scaling)
+  --impl reference   the reference project's own AVX kernels (oracle/_ref, compiled
+          unmodified) on this box's host cores, same shape, all host threads
+Other workloads (--workload): qgemv_sweep, qgemm_m2048, qgemm_m8192.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+from __graft_entry__ import load_package  # noqa: E402
+
+M_PP, K_PP, N_PP = 322, 4096, 12288
+GEMV_SHAPES = [("q_proj/o_proj", 4096, 4096), ("k_proj/v_proj", 1024, 4096), ("gate/up_proj", 12288, 4096),
+               ("down_proj", 4096, 12288), ("qkv_fused", 6144, 4096)]
+L2_BYTES = 126e6
+
+
+def peaks():
+    p = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        p = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+             "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    except Exception:
+        pass
+    return p
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows = []
+        self.proc = None
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=3)
+        except Exception:
+            pass
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+                for nme, v in zip(names, r[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(nme)
+            except Exception:
+                continue
+        busy = [v for v in sm if mx and v > 0.5 * mx] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cuda_time_ms(torch, fn, iters):
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(iters):
+        fn(i)
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b)
+
+
+# --------------------------------------------------------------------------- reference arm
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    from oracle.inkq_oracle import Oracle, Reference
+    pkg = load_package()
+    M, K, N = M_PP, K_PP, N_PP
+    x = pkg.synth.activations(M, K)
+    w = pkg.synth.weights(N, K)
+    cores = os.cpu_count() or 1
+    kind = "reference" if Reference.available_path()[0] else "port"
+    isa = "scalar"
+    if kind == "reference":
+        ref = Reference()
+        isa = ref.isa
+        B = ref.repack(w["nib"], w["d"], w["m"], 2)
+
+        def step():
+            A = ref.quantize_struct(x, 2, pad_rows=6 * K // 64, prefill=0)     # quantize_row_q8_1_repack_fp32
+            return ref.matmul("gemm_repack_A81W41_fp32", A, B, M, N, K)       # gemm_repack_A81W41_fp32
+        sample = f"full workload: quantize_row_q8_1_repack_fp32 + gemm_repack_A81W41_fp32 at {M}x{N}x{K}, all {cores} host threads"
+        ops = 2.0 * M * N * K
+    else:
+        orc = Oracle()
+        ncols = 1536
+
+        def step():
+            q, d, s = orc.quantize(x, 2)
+            return orc.gemm(0, q, d, s, w["nib"][:ncols], w["d"][:ncols], w["m"][:ncols])
+        sample = f"first {ncols} of {N} output columns (oracle port, OpenMP over columns)"
+        ops = 2.0 * M * ncols * K
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    tops = ops / dt / 1e12
+    line = {"impl": "reference", "metric": "qgemm_int8_tops_pp322", "value": tops, "unit": "TOPS", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 * (2.0 * M * N * K / ops), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "s8 x u4 -> s32, fp32 scale/accumulate", "data": "synthetic",
+            "config": {"workload": "qgemm_pp322", "M": M, "N": N, "K": K, "scheme": "A81W41", "isa": isa},
+            "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cores, "kind": kind, "sample": sample},
+            "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- CPU baseline leg of our arm
+def cpu_baseline_pp322(pkg, x, w):
+    from oracle.inkq_oracle import Oracle, Reference
+    M, K, N = M_PP, K_PP, N_PP
+    cores = os.cpu_count() or 1
+    if Reference.available_path()[0]:
+        ref = Reference()
+        B = ref.repack(w["nib"], w["d"], w["m"], 2)
+        iters, t_q, t_g = 0, 0.0, 0.0
+        t_end = time.perf_counter() + 12.0
+        ref.matmul("gemm_repack_A81W41_fp32", ref.quantize_struct(x, 2, pad_rows=6 * K // 64, prefill=0), B, M, N, K)
+        while time.perf_counter() < t_end and iters < 200:
+            t0 = time.perf_counter()
+            A = ref.quantize_struct(x, 2, pad_rows=6 * K // 64, prefill=0)
+            t1 = time.perf_counter()
+            ref.matmul("gemm_repack_A81W41_fp32", A, B, M, N, K)
+            t2 = time.perf_counter()
+            t_q, t_g, iters = t_q + (t1 - t0), t_g + (t2 - t1), iters + 1
+        per = (t_q + t_g) / iters
+        return {"value": 2.0 * M * N * K / per / 1e12, "unit": "TOPS", "cores": cores, "kind": "reference",
+                "sample": f"{iters} iterations of the full workload in ~12 s; quantizer {t_q / iters * 1e3:.2f} ms (1 thread, as the reference), "
+                          f"GEMM {t_g / iters * 1e3:.2f} ms ({cores} threads), isa {ref.isa}"}
+    orc = Oracle()
+    ncols = 768
+    t0 = time.perf_counter()
+    q, d, s = orc.quantize(x, 2)
+    orc.gemm(0, q, d, s, w["nib"][:ncols], w["d"][:ncols], w["m"][:ncols])
+    dt = time.perf_counter() - t0
+    return {"value": 2.0 * M * ncols * K / dt / 1e12, "unit": "TOPS", "cores": cores, "kind": "port",
+            "sample": f"one pass over the first {ncols} of {N} columns with the scalar oracle"}
+
+
+# --------------------------------------------------------------------------- GEMV sweep (extra figures)
+def gemv_sweep(pkg, torch, ctx, peak_gbs, iters=200):
+    out = []
+    for name, n, k in GEMV_SHAPES:
+        wt = pkg.synth.weights(n, k)
+        per = n * k * 0.625
+        copies = int(min(48, max(3, 2.2 * L2_BYTES // per + 1)))     # distinct weight sets: > L2 in total
+        ws = [ctx.weight(pkg.A81W41, pkg.SCALES_F16, wt["nib"], wt["d"], wt["m"]) for _ in range(copies)]
+        x = torch.randn((1, k), device="cuda")
+        C = torch.empty((copies, n), device="cuda")
+        act = ctx.act(1, k)
+        ctx.quantize(act, x, 1, pkg.Q8_1_F16)
+        torch.cuda.synchronize()
+        # one CUDA graph that walks every copy once: launch gaps do not enter the figure
+        g = torch.cuda.CUDAGraph()
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            ctx.set_stream(s.cuda_stream)
+            for i in range(copies):
+                ctx.gemv(act, ws[i], C[i])
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g, stream=s):
+                for i in range(copies):
+                    ctx.gemv(act, ws[i], C[i])
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        reps = max(3, iters // copies)
+        for _ in range(2):
+            g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / (reps * copies)
+        nbytes = per + k + (k // 32) * 8 + n * 4
+        gbs = nbytes / us / 1e3
+        out.append({"shape": name, "N": n, "K": k, "us": round(us, 3), "GBs": round(gbs, 1), "frac_of_hbm": round(gbs / peak_gbs, 4),
+                    "weight_sets": copies})
+        for h in ws:
+            h.close()
+        act.close()
+    return out
+
+
+# --------------------------------------------------------------------------- our arm
+def run_ours(args, rank, world, local_rank):
+    import torch
+    pkg = load_package()
+    pk = peaks()
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = pkg.Context(local_rank, torch.cuda.current_stream().cuda_stream)
+
+    wl = args.workload
+    M = {"qgemm_pp322": M_PP, "qgemm_m2048": 2048, "qgemm_m8192": 8192, "qgemv_sweep": M_PP}[wl]
+    K, N = K_PP, N_PP
+    assert N % (world * 8) == 0
+    n_loc = N // world
+    n0, n1 = rank * n_loc, (rank + 1) * n_loc
+    x_host = pkg.synth.activations(M, K)
+    wt = pkg.synth.weights(N, K)
+
+    # distinct weight sets so that consecutive steps never find their weights in L2
+    w_bytes_one = n_loc * K * (0.5 + 0.125 * 3) + n_loc * (K // 64) * 2
+    sets = int(max(3, min(16, 1.5 * L2_BYTES // w_bytes_one + 2)))
+    ws = [ctx.weight(pkg.A81W41, pkg.SCALES_F32, wt["nib"], wt["d"], wt["m"], None, n0, n1) for _ in range(sets)]
+    xs = [torch.from_numpy(x_host).cuda() for _ in range(sets)]
+    if world > 1:
+        gathered = torch.empty((world, M, n_loc), device="cuda")        # all-gather target, rank-major
+        Cfull = torch.empty((M, N), device="cuda")
+        Cs = [gathered[rank]]
+    else:
+        Cs = [torch.empty((M, n_loc), device="cuda") for _ in range(2)]
+
+    def step(i):
+        w = ws[i % sets]
+        C = Cs[i % len(Cs)]
+        ctx.linear(w, xs[i % sets], M, C, n_loc)                        # quantizer + QGEMM (Qwen_Linear_with_bias_Int4::forward)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered.view(-1), gathered[rank].reshape(-1))
+            Cfull.view(M, world, n_loc).copy_(gathered.permute(1, 0, 2))  # [P][M][N/P] -> [M][N]
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    l0 = ctx.launches
+    torch.cuda.synchronize()
+    ms = cuda_time_ms(torch, step, args.steps)
+    launches = ctx.launches - l0
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    ctx.synchronize()
+    clocks = sampler.stop()
+    ops = 2.0 * M * N * K
+    tops = ops * args.steps / (ms * 1e-3) / 1e12
+
+    line = {"metric": "qgemm_int8_tops_pp322" if wl in ("qgemm_pp322", "qgemv_sweep") else f"qgemm_int8_tops_{wl.split('_')[1]}",
+            "value": tops, "unit": "TOPS", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "s8 x u4 -> s32 block dots (tcgen05 kind::i8), fp32 scale/accumulate", "data": "synthetic",
+            "config": {"workload": wl if wl != "qgemv_sweep" else "qgemm_pp322", "M": M, "N": N, "K": K, "scheme": "A81W41",
+                       "weight_scales": "fp32", "parallelism": f"tp{world} (N-sharded, NCCL all-gather)" if world > 1 else "single GPU",
+                       "l2": f"{sets} distinct weight sets ({sets * w_bytes_one / 1e6:.0f} MB per rank) rotated between steps, > 126 MB L2"},
+            "clocks": clocks, "gpu_launches": int(launches)}
+
+    if rank == 0:
+        # ---- kernel-only figures for the roofline (dominant kernel: the tensor-core QGEMM) ----
+        act = ctx.act(M, K)
+        ctx.quantize(act, xs[0], M, pkg.Q8_1_F32)
+        Ck = Cs[0]
+        for i in range(3):
+            ctx.gemm(act, ws[i % sets], Ck, n_loc)
+        torch.cuda.synchronize()
+        it = max(10, args.steps)
+        ms_g = cuda_time_ms(torch, lambda i: ctx.gemm(act, ws[i % sets], Ck, n_loc), it) / it
+        ms_q = cuda_time_ms(torch, lambda i: ctx.quantize(act, xs[i % sets], M, pkg.Q8_1_F32), it) / it
+        ach = 2.0 * M * n_loc * K / (ms_g * 1e-3) / 1e12
+        int8_peak = 2.0 * pk["bf16_tflops"]
+        line["roofline"] = {"bound": "tensor", "achieved": ach, "peak": int8_peak, "unit": "TOP/s", "frac": ach / int8_peak,
+                            "traffic": None, "kernel": "k_qgemm_tc", "us_per_launch": ms_g * 1e3,
+                            "peak_note": f"2 x the {pk['source']} dense bf16 figure ({pk['bf16_tflops']} TFLOP/s); int8 itself is not in MEASURED_PEAKS.json",
+                            "cuda_core_note": "every K=32 MMA is followed by an fp32 scale+accumulate of its whole tile on the CUDA cores "
+                                              "(M*N*K/32 block dots per launch); that, not the tensor pipe, bounds this kernel"}
+        line["quantizer"] = {"us_per_launch": ms_q * 1e3, "GBs": M * K * 5.375 / (ms_q * 1e-3) / 1e9, "frac_of_hbm": M * K * 5.375 / (ms_q * 1e-3) / 1e9 / pk["hbm_gbs"]}
+        act.close()
+
+        # ---- end to end through the host-buffer entry point ----
+        if world == 1:
+            xh = torch.from_numpy(x_host).pin_memory()
+            ch = torch.empty((M, N), dtype=torch.float32).pin_memory()
+            for i in range(3):
+                ctx.linear_host(ws[i % sets], xh, M, ch, N)
+            it = max(10, args.steps)
+            t0 = time.perf_counter()
+            for i in range(it):
+                ctx.linear_host(ws[i % sets], xh, M, ch, N)
+            dt = (time.perf_counter() - t0) / it
+            line["e2e"] = {"value": ops / dt / 1e12, "unit": "TOPS", "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * 4,
+                           "ms_per_step": dt * 1e3}
+        else:
+            line["e2e"] = {"value": None, "unit": "TOPS", "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * 4,
+                           "note": "measured at N=1 only"}
+        if world == 1 and wl in ("qgemm_pp322", "qgemv_sweep"):
+            line["cpu_baseline"] = cpu_baseline_pp322(pkg, x_host, wt)
+        if world == 1 and (wl == "qgemv_sweep" or args.gemv):
+            for h in ws:
+                h.close()
+            ws = []
+            line["gemv"] = gemv_sweep(pkg, torch, ctx, pk["hbm_gbs"])
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="qgemm_pp322", choices=["qgemm_pp322", "qgemv_sweep", "qgemm_m2048", "qgemm_m8192"])
+    ap.add_argument("--no-gemv", dest="gemv", action="store_false", help="skip the decode QGEMV sweep figures")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

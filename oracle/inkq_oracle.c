@@ -388,10 +388,12 @@ void ink_gemm_w41_f16act(int M, int N, int K, const uint16_t *a16,
 }
 
 /*
- * lm_head with fp16 weights and fp32 activations: logits[n] = sum_k x[k]*w[n][k],
- * fp32 accumulate, k ascending.  Nearest reference arithmetic:
- * gemv_fp32_rcr_mt_impl_1, qwen3/src/qwen/fp32_gemx_kernels_rcr.cc:494-507
- * (the reference's own lm_head is an int4 A81W41 linear, QwenForCausalLM.cc:121).
+ * lm_head with fp16 weights and fp32 activations: logits[n] = sum_k x[k]*w[n][k].
+ * Nearest reference arithmetic: gemv_fp32_rcr_mt_impl_1,
+ * qwen3/src/qwen/fp32_gemx_kernels_rcr.cc:494-507 (the reference's own lm_head is
+ * an int4 A81W41 linear, QwenForCausalLM.cc:121).  There is no reference kernel
+ * to be bit-compatible with, so the oracle accumulates in double and rounds once:
+ * it is the exact value any fp32 summation order is compared against.
  */
 void ink_lmhead_f16w(int M, int N, int K, const float *x, const uint16_t *w16, float *C, int ldc,
                      int n0, int n1)
@@ -399,10 +401,10 @@ void ink_lmhead_f16w(int M, int N, int K, const float *x, const uint16_t *w16, f
 #pragma omp parallel for schedule(static)
     for (int n = n0; n < n1; n++)
         for (int i = 0; i < M; i++) {
-            float acc = 0.0f;
+            double acc = 0.0;
             for (int k = 0; k < K; k++)
-                acc = fmaf(x[(size_t)i * K + k], ink_f16_to_f32(w16[(size_t)n * K + k]), acc);
-            C[(size_t)i * ldc + n] = acc;
+                acc += (double)x[(size_t)i * K + k] * (double)ink_f16_to_f32(w16[(size_t)n * K + k]);
+            C[(size_t)i * ldc + n] = (float)acc;
         }
 }
 

@@ -36,6 +36,7 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t by
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
 }
+// One probe of the barrier (returns at once when the phase is incomplete).
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 {
     uint32_t ok;
@@ -48,29 +49,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
-// Bounded wait.  Returns false when the limit ran out (the caller records it).
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
+// Bounded wait.  Returns false when the limit ran out, or as soon as *abort (a
+// shared-memory word another role sets when its own wait ran out) is non-zero.
+// After `eager` failed probes the thread sleeps `sleep_ns` between probes, so a
+// role that is far ahead of its consumer does not take issue slots from the warps
+// doing the arithmetic; the clock is read only every 64 probes.
+__device__ __forceinline__ bool mbar_wait_abortable(volatile int *abort, uint64_t *bar, uint32_t parity, uint32_t sleep_ns = 256u,
+                                                    uint32_t eager = 2u)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > INKQ_SPIN_LIMIT_CYCLES) return false;
+#pragma unroll 1
+    for (uint32_t spin = 1;; spin++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (spin > eager) __nanosleep(sleep_ns);
+        if ((spin & 63u) == 0u && (*abort != 0 || clock64() - t0 > INKQ_SPIN_LIMIT_CYCLES)) return false;
     }
-    return true;
 }
-
-// As mbar_wait, and also gives up as soon as *abort (a shared-memory word another
-// role sets when its own wait ran out) becomes non-zero.
-__device__ __forceinline__ bool mbar_wait_abortable(volatile int *abort, uint64_t *bar, uint32_t parity)
-{
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (*abort != 0 || clock64() - t0 > INKQ_SPIN_LIMIT_CYCLES) return false;
-    }
-    return true;
-}
-
 // ---- fences -------------------------------------------------------------------
 // Make generic-proxy shared-memory writes visible to the async proxy (UMMA / TMA reads).
 __device__ __forceinline__ void fence_proxy_async_smem()
@@ -169,6 +164,13 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar)
 }
 
 // ---- TMEM -> registers (whole warp; lane i reads TMEM lane base+i, N consecutive columns) ----
+__device__ __forceinline__ void tmem_ld_x4(uint32_t taddr, uint32_t *r)
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr)
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t *r)
 {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"

@@ -15,19 +15,24 @@
 // the UMMA N side (TMEM columns, BLOCK_M = 16..128 in steps of 16), which keeps
 // the padding of a ragged M small and makes the store of C[m][n0..n0+127] coalesced.
 //
-// Persistent, warp-specialised, one CTA per SM, 512 threads:
-//   warp 0      TMA producer: per stage (4 blocks = 128 K-bytes) one tiled 2-D copy of the
-//               int8 activations [BLOCK_M rows][128 B] (128-byte swizzle, rows beyond M are
-//               zero-filled by TMA) and two untiled bulk copies of the packed weights
+// Persistent, warp-specialised, one CTA per SM, 768 threads:
+//   warp 0      operand TMA producer: per stage (4 blocks = 128 K-bytes) one tiled 2-D copy of
+//               the int8 activations [BLOCK_M rows][128 B] (128-byte swizzle, rows beyond M
+//               are zero-filled by TMA) and two untiled bulk copies of the packed weights
 //               (2 pairs x 4096 B) and their zero points
 //   warp 1      MMA issuer: one elected thread issues the K=32 MMAs and commits
 //   warp 2      tensor-memory allocation / release
+//   warp 3      scale TMA producer: per stage the activation block scales d_a and sums s_a of
+//               the tile's rows, [4 blocks][BLOCK_M] fp32 each (tiled 2-D copies, zero-filled
+//               past the end), into their own ring because the epilogue consumes them later
+//               than the MMA consumes the operands
 //   warps 4-7   unpack: packed nibbles (smem) -> signed int8 (q - z) in the canonical
 //               no-swizzle K-major core-matrix layout the MMA reads
-//   warps 8-15  epilogue: tcgen05.ld of a block's int32 tile, s32->f32, scale, accumulate
-//               in registers in exactly the reference's order; at the end of a tile the
-//               fp32 accumulators are stored to C
-// Rings: 4 raw stages, 2 unpacked stages, 4 TMEM accumulators of 128 columns.
+//   warps 8-23  epilogue (the binding resource: it owns all four schedulers): tcgen05.ld of a
+//               block's int32 tile, s32->f32, scale, accumulate in registers in exactly the
+//               reference's order; at the end of a tile the fp32 accumulators are stored to C.
+//               Warp w reads TMEM lanes 32*(w%4).. and a quarter of the columns.
+// Rings: 4 raw stages, 2 unpacked stages, 4 scale stages, 4 TMEM accumulators of 128 columns.
 // Every mbarrier wait is bounded; on expiry the kernel sets a device flag and all
 // roles drain and leave (the context stays usable, the host reports INKQ_ERR_TIMEOUT).
 //
@@ -43,12 +48,16 @@
 
 namespace inkq {
 
-constexpr int TC_THREADS = 512;
+constexpr int TC_THREADS = 768;
+constexpr int EPI_WARPS = 16;
 constexpr int STAGE_PAIRS = 2;                         // pairs per stage
 constexpr int STAGE_BLOCKS = 2 * STAGE_PAIRS;          // 4 MMAs per stage
 constexpr int RAW_STAGES = 4;
 constexpr int U8_STAGES = 2;
 constexpr int ACC_STAGES = 4;
+constexpr int SC_STAGES = 4;
+constexpr int SC_PLANE_BYTES = STAGE_BLOCKS * 128 * 4;    // one plane of a scale stage: [4 blocks][128 rows] fp32
+constexpr int SC_STAGE_BYTES = 2 * SC_PLANE_BYTES;       // d_a and s_a
 constexpr int ACC_COLS = 128;                          // TMEM columns per accumulator
 constexpr int RAW_A_BYTES = 128 * 128;                 // activations: up to 128 rows x 128 B
 constexpr int RAW_W_BYTES = STAGE_PAIRS * TILE_N * 32; // packed weights: 8192
@@ -56,19 +65,18 @@ constexpr int RAW_Z_BYTES = STAGE_PAIRS * TILE_N * 2;  // zero points: 512
 constexpr int RAW_STAGE_BYTES = 25600;                 // 16384 + 8192 + 512, rounded to 1024
 constexpr int U8_BLOCK_BYTES = TILE_N * 32;            // one unpacked block: 4096
 constexpr int U8_STAGE_BYTES = STAGE_BLOCKS * U8_BLOCK_BYTES;
-constexpr int TC_SMEM_BYTES = 1024 /*align slack*/ + RAW_STAGES * RAW_STAGE_BYTES + U8_STAGES * U8_STAGE_BYTES + 256 /*barriers*/;
+constexpr int TC_SMEM_BYTES =
+    1024 /*align slack*/ + RAW_STAGES * RAW_STAGE_BYTES + U8_STAGES * U8_STAGE_BYTES + SC_STAGES * SC_STAGE_BYTES + 512 /*barriers*/;
 
 struct TcParams {
     const uint8_t *nibT;
     const float4 *sc32;
     const uint2 *sc16;
     const uchar2 *zpT;
-    const float *d_a, *s_a;
     float *C;
     int32_t *dots;   // non-null: dump raw int32 block dots [M][rows][K/32] instead of computing C
     int *flag;
     int M, M_ld, rows, K, pairs, tiles_n, tiles_m, block_m, ldc;
-    int desc_swap;   // debug: exchange the two offsets of the no-swizzle descriptor
 };
 
 struct Ring {
@@ -84,20 +92,82 @@ struct Ring {
     }
 };
 
-// CW = columns of the accumulator handled by one epilogue warpgroup (BLOCK_M / 2).
-template <int CW, bool HAS_MIN>
-__global__ void __launch_bounds__(TC_THREADS, 1) k_qgemm_tc(const __grid_constant__ CUtensorMap map_a, const TcParams prm)
+// Exact s32 -> f32 (a block dot is at most 32 * 128 * 15 = 61440 in magnitude).  The
+// alternative under INKQ_CVT_MAGIC avoids the conversion instruction: adding 0x4B400000 as
+// an integer yields the bit pattern of the float 12582912 + v (ulp = 1 in [2^23, 2^24)), and
+// the float subtraction of 12582912 is exact for |v| < 2^22.
+__device__ __forceinline__ float s32_to_f32_exact(uint32_t v)
 {
-    constexpr int BLOCK_M = 2 * CW;
-    extern __shared__ unsigned char smem_dyn[];
-    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
+#ifdef INKQ_CVT_MAGIC
+    return __int_as_float(static_cast<int>(v + 0x4B400000u)) - 12582912.0f;
+#else
+    return static_cast<float>(static_cast<int32_t>(v));
+#endif
+}
+
+// Two fp32 values in one 64-bit register and the IEEE (round-to-nearest) packed
+// multiply / fused multiply-add of sm_100: each half rounds exactly like the scalar
+// instruction, so results stay bit-identical while the issue slots are halved.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi)
+{
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float &lo, float &hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b)
+{
+    unsigned long long r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c)
+{
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+// Loads N consecutive TMEM columns of this thread's lane; N a multiple of 4 up to 16.
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t *r)
+{
+    if constexpr (N == 16) {
+        tmem_ld_x16(taddr, r);
+    } else if constexpr (N == 12) {
+        tmem_ld_x8(taddr, r);
+        tmem_ld_x4(taddr + 8, r + 8);
+    } else if constexpr (N == 8) {
+        tmem_ld_x8(taddr, r);
+    } else {
+        static_assert(N == 4, "column chunk must be 4, 8, 12 or 16");
+        tmem_ld_x4(taddr, r);
+    }
+}
+
+// CW = columns of the accumulator handled by one epilogue warp (BLOCK_M / 4).
+template <int CW, bool HAS_MIN>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+    k_qgemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_s,
+               const TcParams prm)
+{
+    constexpr int BLOCK_M = 4 * CW;
+    // 1024-byte alignment (128-byte swizzle atoms) by an offset from the shared array itself, so
+    // that every access below stays a shared-space (not generic) load or store
+    extern __shared__ __align__(1024) unsigned char smem_dyn[];
+    unsigned char *smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
     unsigned char *raw_base = smem;
-    unsigned char *u8_base = smem + RAW_STAGES * RAW_STAGE_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(u8_base + U8_STAGES * U8_STAGE_BYTES);
-    uint64_t *raw_full = bars, *raw_empty = bars + RAW_STAGES;
-    uint64_t *u8_full = bars + 2 * RAW_STAGES, *u8_empty = u8_full + U8_STAGES;
+    unsigned char *u8_base = raw_base + RAW_STAGES * RAW_STAGE_BYTES;
+    unsigned char *sc_base = u8_base + U8_STAGES * U8_STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sc_base + SC_STAGES * SC_STAGE_BYTES);
+    uint64_t *raw_full = bars, *raw_empty = raw_full + RAW_STAGES;
+    uint64_t *u8_full = raw_empty + RAW_STAGES, *u8_empty = u8_full + U8_STAGES;
     uint64_t *acc_full = u8_empty + U8_STAGES, *acc_empty = acc_full + ACC_STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + ACC_STAGES);
+    uint64_t *sc_full = acc_empty + ACC_STAGES, *sc_empty = sc_full + SC_STAGES;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sc_empty + SC_STAGES);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -115,7 +185,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_qgemm_tc(const __grid_constan
         }
         for (int i = 0; i < ACC_STAGES; i++) {
             mbar_init(&acc_full[i], 1);
-            mbar_init(&acc_empty[i], 8);  // one arrive per epilogue warp
+            mbar_init(&acc_empty[i], EPI_WARPS);
+        }
+        for (int i = 0; i < SC_STAGES; i++) {
+            mbar_init(&sc_full[i], 1);
+            mbar_init(&sc_empty[i], EPI_WARPS);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -129,8 +203,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_qgemm_tc(const __grid_constan
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
+    // A failed (timed-out or aborted) wait: record it for the host and for the other roles.
+#define INKQ_GIVE_UP()            \
+    {                             \
+        *abort_flag = 1;          \
+        atomicExch(prm.flag, 1);  \
+        dead = true;              \
+        break;                    \
+    }
+
     if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
+        // ------------------------------ operand TMA producer ------------------------------
         if (lane == 0) {
             tma_prefetch_desc(&map_a);
             Ring raw(RAW_STAGES);
@@ -138,13 +221,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_qgemm_tc(const __grid_constan
             for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
                 const int tn = tile / prm.tiles_m, tm = tile % prm.tiles_m;
                 for (int ks = 0; ks < k_stages; ks++) {
-                    if (*abort_flag) { dead = true; break; }
-                    if (!mbar_wait_abortable(abort_flag, &raw_empty[raw.idx], raw.phase ^ 1)) {
-                        *abort_flag = 1;
-                        atomicExch(prm.flag, 1);
-                        dead = true;
-                        break;
-                    }
+                    if (!mbar_wait_abortable(abort_flag, &raw_empty[raw.idx], raw.phase ^ 1, 1000u)) INKQ_GIVE_UP();
                     const int np = min(STAGE_PAIRS, prm.pairs - ks * STAGE_PAIRS);
                     unsigned char *st = raw_base + raw.idx * RAW_STAGE_BYTES;
                     const uint32_t tx = BLOCK_M * 128 + np * (TILE_N * 32) + np * (TILE_N * 2);
@@ -159,6 +236,27 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_qgemm_tc(const __grid_constan
             }
         }
         __syncwarp();
+    } else if (warp == 3) {
+        // ------------------------------ scale TMA producer ------------------------------
+        if (lane == 0 && prm.dots == nullptr) {  // the block-dot dump applies no scales
+            tma_prefetch_desc(&map_d);
+            if (HAS_MIN) tma_prefetch_desc(&map_s);
+            Ring sc(SC_STAGES);
+            bool dead = false;
+            for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
+                const int tm = tile % prm.tiles_m;
+                for (int ks = 0; ks < k_stages; ks++) {
+                    if (!mbar_wait_abortable(abort_flag, &sc_empty[sc.idx], sc.phase ^ 1, 1000u)) INKQ_GIVE_UP();
+                    unsigned char *st = sc_base + sc.idx * SC_STAGE_BYTES;
+                    const uint32_t plane = STAGE_BLOCKS * BLOCK_M * 4;  // the box is always full size; out-of-range parts arrive as zeros
+                    mbar_arrive_expect_tx(&sc_full[sc.idx], HAS_MIN ? 2 * plane : plane);
+                    tma_tensor2d_g2s(st, &map_d, tm * BLOCK_M, ks * STAGE_BLOCKS, &sc_full[sc.idx]);
+                    if (HAS_MIN) tma_tensor2d_g2s(st + SC_PLANE_BYTES, &map_s, tm * BLOCK_M, ks * STAGE_BLOCKS, &sc_full[sc.idx]);
+                    sc.advance();
+                }
+            }
+        }
+        __syncwarp();
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
@@ -167,30 +265,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_qgemm_tc(const __grid_constan
             bool dead = false;
             for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
                 for (int ks = 0; ks < k_stages && !dead; ks++) {
-                    if (*abort_flag) { dead = true; break; }
-                    if (!mbar_wait_abortable(abort_flag, &raw_full[raw.idx], raw.phase) || !mbar_wait_abortable(abort_flag, &u8_full[u8.idx], u8.phase)) {
-                        *abort_flag = 1;
-                        atomicExch(prm.flag, 1);
-                        dead = true;
-                        break;
-                    }
+                    if (!mbar_wait_abortable(abort_flag, &raw_full[raw.idx], raw.phase) ||
+                        !mbar_wait_abortable(abort_flag, &u8_full[u8.idx], u8.phase))
+                        INKQ_GIVE_UP();
                     tc_fence_after_sync();
                     const int nblk = 2 * min(STAGE_PAIRS, prm.pairs - ks * STAGE_PAIRS);
                     const uint32_t a_smem = smem_u32(u8_base + u8.idx * U8_STAGE_BYTES);
                     const uint32_t b_smem = smem_u32(raw_base + raw.idx * RAW_STAGE_BYTES);
                     for (int j = 0; j < nblk; j++) {
-                        if (!mbar_wait_abortable(abort_flag, &acc_empty[acc.idx], acc.phase ^ 1)) {
-                            *abort_flag = 1;
-                            atomicExch(prm.flag, 1);
-                            dead = true;
-                            break;
-                        }
+                        if (!mbar_wait_abortable(abort_flag, &acc_empty[acc.idx], acc.phase ^ 1)) INKQ_GIVE_UP();
                         tc_fence_after_sync();
                         // A: unpacked weights of block j, no swizzle: element (row r, k) at
-                        //    (k / 16) * 2048 + r * 16 + (k % 16): 8-row core matrices 128 B apart
-                        //    along rows, the two K halves 2048 B apart.
-                        const uint64_t a_desc = prm.desc_swap ? umma_smem_desc(a_smem + j * U8_BLOCK_BYTES, 128, 2048, 0)
-                                                              : umma_smem_desc(a_smem + j * U8_BLOCK_BYTES, 2048, 128, 0);
+                        //    (k / 16) * 2048 + r * 16 + (k % 16): the two K halves 2048 B apart
+                        //    (leading offset), 8-row core matrices 128 B apart (stride offset).
+                        const uint64_t a_desc = umma_smem_desc(a_smem + j * U8_BLOCK_BYTES, 2048, 128, 0);
                         // B: activations, 128-byte swizzled rows of 128 B; block j is the j-th
                         //    32-byte slice of the row; 8-row groups are 1024 B apart.
                         const uint64_t b_desc = umma_smem_desc(b_smem + j * 32, 16, 1024, 2);
@@ -198,6 +286,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_qgemm_tc(const __grid_constan
                         umma_commit(&acc_full[acc.idx]);
                         acc.advance();
                     }
+                    if (dead) break;
                     umma_commit(&raw_empty[raw.idx]);
                     umma_commit(&u8_empty[u8.idx]);
                     raw.advance();
@@ -218,13 +307,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_qgemm_tc(const __grid_constan
         bool dead = false;
         for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
             for (int ks = 0; ks < k_stages; ks++) {
-                if (*abort_flag) { dead = true; break; }
-                if (!mbar_wait_abortable(abort_flag, &raw_full[raw.idx], raw.phase) || !mbar_wait_abortable(abort_flag, &u8_empty[u8.idx], u8.phase ^ 1)) {
-                    *abort_flag = 1;
-                    atomicExch(prm.flag, 1);
-                    dead = true;
-                    break;
-                }
+                if (!mbar_wait_abortable(abort_flag, &raw_full[raw.idx], raw.phase) ||
+                    !mbar_wait_abortable(abort_flag, &u8_empty[u8.idx], u8.phase ^ 1))
+                    INKQ_GIVE_UP();
                 const int np = min(STAGE_PAIRS, prm.pairs - ks * STAGE_PAIRS);
                 const unsigned char *wsrc = raw_base + raw.idx * RAW_STAGE_BYTES + RAW_A_BYTES;
                 const unsigned char *zsrc = wsrc + RAW_W_BYTES;
@@ -259,98 +344,141 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_qgemm_tc(const __grid_constan
         }
     } else if (warp >= 8) {
         // ------------------------------ epilogue ------------------------------
-        const int quad = warp & 3;            // TMEM lane quadrant this warp may read
-        const int half = (warp - 8) >> 2;     // which half of the accumulator columns
-        const int row = quad * 32 + lane;     // weight row inside the tile = TMEM lane
+        constexpr int CH = (CW >= 16) ? 16 : CW;   // columns per TMEM load step
+        constexpr int NCH = (CW + CH - 1) / CH;    // 1 or 2 steps (CW <= 32); the last one may be shorter
+        constexpr int CH_LAST = CW - (NCH - 1) * CH;
+        const int quad = warp & 3;             // TMEM lane quadrant this warp may read
+        const int cq = (warp - 8) >> 2;        // which quarter of the accumulator columns
+        const int row = quad * 32 + lane;      // weight row inside the tile = TMEM lane
         const int nbk = 2 * prm.pairs;
-        Ring acc(ACC_STAGES);
+        Ring acc(ACC_STAGES), sc(SC_STAGES);
         bool dead = false;
         for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
             const int tn = tile / prm.tiles_m, tm = tile % prm.tiles_m;
             const int n = tn * TILE_N + row;
-            const int m_base = tm * BLOCK_M + half * CW;
+            const int col0 = cq * CW;            // first column of this warp inside the tile
+#ifndef INKQ_SCALAR_EPILOGUE
+            unsigned long long accp[CW / 2];
+#pragma unroll
+            for (int j = 0; j < CW / 2; j++) accp[j] = 0ull;
+#else
             float accf[CW];
 #pragma unroll
             for (int j = 0; j < CW; j++) accf[j] = 0.0f;
-            float4 sc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int b = 0; b < nbk; b++) {
-                if ((b & 1) == 0) {
-                    const size_t rec = (static_cast<size_t>(tn) * prm.pairs + (b >> 1)) * TILE_N + row;
-                    if (prm.sc32 != nullptr) {
-                        sc = prm.sc32[rec];
-                    } else {
-                        const uint2 pk = prm.sc16[rec];
-                        const float2 x0 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.x));
-                        const float2 x1 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.y));
-                        sc = make_float4(x0.x, x0.y, x1.x, x1.y);
-                    }
+#endif
+            // this row's weight scales {d_lo, d_hi, m_lo, m_hi} of a pair, fetched one pair ahead
+            auto load_wsc = [&](int pair) -> float4 {
+                const size_t rec = (static_cast<size_t>(tn) * prm.pairs + min(pair, prm.pairs - 1)) * TILE_N + row;
+                if (prm.sc32 != nullptr) return prm.sc32[rec];
+                const uint2 pk = prm.sc16[rec];
+                const float2 x0 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.x));
+                const float2 x1 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.y));
+                return make_float4(x0.x, x0.y, x1.x, x1.y);
+            };
+            float4 wsc_next = load_wsc(0);
+            for (int p = 0; p < prm.pairs && !dead; p++) {
+                const float4 wsc = wsc_next;
+                wsc_next = load_wsc(p + 1);
+                const int pj = p & (STAGE_PAIRS - 1);
+                if (pj == 0 && prm.dots == nullptr) {
+                    if (!mbar_wait_abortable(abort_flag, &sc_full[sc.idx], sc.phase, 64u, 64u)) INKQ_GIVE_UP();
                 }
-                if (*abort_flag) { dead = true; break; }
-                if (!mbar_wait_abortable(abort_flag, &acc_full[acc.idx], acc.phase)) {
-                    *abort_flag = 1;
-                    atomicExch(prm.flag, 1);
-                    dead = true;
-                    break;
-                }
-                tc_fence_after_sync();
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc.idx * ACC_COLS + half * CW;
-                const float dw = (b & 1) ? sc.y : sc.x;
-                const float *da_row = prm.d_a + static_cast<size_t>(b) * prm.M_ld;
-                const float *sa_row = prm.s_a + static_cast<size_t>(b) * prm.M_ld;
+                const float *sd_lo = reinterpret_cast<const float *>(sc_base + sc.idx * SC_STAGE_BYTES) + (2 * pj) * BLOCK_M + col0;
 #pragma unroll
-                for (int c8 = 0; c8 < CW / 8; c8++) {
-                    uint32_t raw[8];
-                    tmem_ld_x8(taddr + c8 * 8, raw);
-                    tmem_ld_wait();
-                    if (c8 == CW / 8 - 1) {
-                        // the whole accumulator is in registers: hand the TMEM buffer back
-                        tc_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&acc_empty[acc.idx]);
-                    }
-                    const int m0 = m_base + c8 * 8;
-                    if (prm.dots != nullptr) {
+                for (int hi = 0; hi < 2; hi++) {   // the two blocks of the pair: low nibbles, then high nibbles
+                    if (!mbar_wait_abortable(abort_flag, &acc_full[acc.idx], acc.phase, 64u, 64u)) INKQ_GIVE_UP();
+                    tc_fence_after_sync();
+                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc.idx * ACC_COLS + col0;
+                    const float dw = hi ? wsc.y : wsc.x;
+                    const float *sd = sd_lo + hi * BLOCK_M;          // d_a of this block
+                    const float *ss_lo = sd_lo + SC_PLANE_BYTES / 4; // s_a of the low block; the high block's follows
+                    const int b = 2 * p + hi;
 #pragma unroll
-                        for (int j = 0; j < 8; j++)
-                            if (m0 + j < prm.M && n < prm.rows)
-                                prm.dots[(static_cast<size_t>(m0 + j) * prm.rows + n) * nbk + b] = static_cast<int32_t>(raw[j]);
-                        continue;
-                    }
+                    for (int c = 0; c < NCH; c++) {
+                        uint32_t raw[CH];
+                        if (c == NCH - 1) tmem_ld_cols<CH_LAST>(taddr + c * CH, raw);
+                        else tmem_ld_cols<CH>(taddr + c * CH, raw);
+                        tmem_ld_wait();
+                        if (c == NCH - 1) {
+                            // the whole accumulator is in registers: hand the TMEM buffer back
+                            tc_fence_before_sync();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&acc_empty[acc.idx]);
+                        }
+                        const int ncols = (c == NCH - 1) ? CH_LAST : CH;
+                        if (prm.dots != nullptr) {
 #pragma unroll
-                    for (int j4 = 0; j4 < 8; j4 += 4) {
-                        const int m = m0 + j4;
-                        float4 da = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (m < prm.M_ld) da = *reinterpret_cast<const float4 *>(da_row + m);
-                        const float dav[4] = {da.x, da.y, da.z, da.w};
-#pragma unroll
-                        for (int j = 0; j < 4; j++)
-                            accf[c8 * 8 + j4 + j] = fmaf(static_cast<float>(static_cast<int32_t>(raw[j4 + j])), __fmul_rn(dav[j], dw), accf[c8 * 8 + j4 + j]);
-                        if (HAS_MIN && (b & 1)) {
-                            float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
-                            if (m < prm.M_ld) {
-                                s0 = *reinterpret_cast<const float4 *>(sa_row - prm.M_ld + m);
-                                s1 = *reinterpret_cast<const float4 *>(sa_row + m);
+                            for (int j = 0; j < CH; j++) {
+                                const int m = tm * BLOCK_M + col0 + c * CH + j;
+                                if (j < ncols && m < prm.M && n < prm.rows)
+                                    prm.dots[(static_cast<size_t>(m) * prm.rows + n) * nbk + b] = static_cast<int32_t>(raw[j]);
                             }
-                            const float s0v[4] = {s0.x, s0.y, s0.z, s0.w}, s1v[4] = {s1.x, s1.y, s1.z, s1.w};
+                            continue;
+                        }
 #pragma unroll
-                            for (int j = 0; j < 4; j++) {
-                                accf[c8 * 8 + j4 + j] = fmaf(sc.z, s0v[j], accf[c8 * 8 + j4 + j]);
-                                accf[c8 * 8 + j4 + j] = fmaf(sc.w, s1v[j], accf[c8 * 8 + j4 + j]);
+                        for (int j4 = 0; j4 < CH; j4 += 4) {
+                            if (j4 < ncols) {
+                                const float4 da = *reinterpret_cast<const float4 *>(sd + c * CH + j4);
+#ifndef INKQ_SCALAR_EPILOGUE
+                                const unsigned long long dw2 = pack2(dw, dw);
+                                const int a0 = (c * CH + j4) / 2;
+                                accp[a0] =
+                                    fma2(pack2(s32_to_f32_exact(raw[j4]), s32_to_f32_exact(raw[j4 + 1])), mul2(pack2(da.x, da.y), dw2), accp[a0]);
+                                accp[a0 + 1] = fma2(pack2(s32_to_f32_exact(raw[j4 + 2]), s32_to_f32_exact(raw[j4 + 3])), mul2(pack2(da.z, da.w), dw2),
+                                                    accp[a0 + 1]);
+                                if (HAS_MIN && hi) {
+                                    const float4 s0 = *reinterpret_cast<const float4 *>(ss_lo + c * CH + j4);
+                                    const float4 s1 = *reinterpret_cast<const float4 *>(ss_lo + BLOCK_M + c * CH + j4);
+                                    const unsigned long long mlo = pack2(wsc.z, wsc.z), mhi = pack2(wsc.w, wsc.w);
+                                    accp[a0] = fma2(mlo, pack2(s0.x, s0.y), accp[a0]);
+                                    accp[a0] = fma2(mhi, pack2(s1.x, s1.y), accp[a0]);
+                                    accp[a0 + 1] = fma2(mlo, pack2(s0.z, s0.w), accp[a0 + 1]);
+                                    accp[a0 + 1] = fma2(mhi, pack2(s1.z, s1.w), accp[a0 + 1]);
+                                }
+#else
+                                const float dav[4] = {da.x, da.y, da.z, da.w};
+#pragma unroll
+                                for (int j = 0; j < 4; j++)
+                                    accf[c * CH + j4 + j] = fmaf(s32_to_f32_exact(raw[j4 + j]), __fmul_rn(dav[j], dw), accf[c * CH + j4 + j]);
+                                if (HAS_MIN && hi) {
+                                    const float4 s0 = *reinterpret_cast<const float4 *>(ss_lo + c * CH + j4);
+                                    const float4 s1 = *reinterpret_cast<const float4 *>(ss_lo + BLOCK_M + c * CH + j4);
+                                    const float s0v[4] = {s0.x, s0.y, s0.z, s0.w}, s1v[4] = {s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                                    for (int j = 0; j < 4; j++) {
+                                        accf[c * CH + j4 + j] = fmaf(wsc.z, s0v[j], accf[c * CH + j4 + j]);
+                                        accf[c * CH + j4 + j] = fmaf(wsc.w, s1v[j], accf[c * CH + j4 + j]);
+                                    }
+                                }
+#endif
                             }
                         }
                     }
+                    acc.advance();
                 }
-                acc.advance();
+                if (dead) break;
+                if (prm.dots == nullptr && (pj == STAGE_PAIRS - 1 || p == prm.pairs - 1)) {
+                    // this warp is done with the stage's scales
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sc_empty[sc.idx]);
+                    sc.advance();
+                }
             }
             if (!dead && prm.dots == nullptr && n < prm.rows) {
+#ifndef INKQ_SCALAR_EPILOGUE
+                float accf[CW];
+#pragma unroll
+                for (int j = 0; j < CW / 2; j++) unpack2(accp[j], accf[2 * j], accf[2 * j + 1]);
+#endif
 #pragma unroll
                 for (int j = 0; j < CW; j++) {
-                    const int m = m_base + j;
+                    const int m = tm * BLOCK_M + col0 + j;
                     if (m < prm.M) prm.C[static_cast<size_t>(m) * prm.ldc + n] = accf[j];
                 }
             }
         }
     }
+#undef INKQ_GIVE_UP
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 2) {
@@ -364,7 +492,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 template <int CW, bool HAS_MIN>
-static int launch_one(inkq_ctx *ctx, const CUtensorMap &map, const TcParams &prm, int grid)
+static int launch_one(inkq_ctx *ctx, const CUtensorMap *maps, const TcParams &prm, int grid)
 {
     static bool configured = false;
     if (!configured) {
@@ -372,24 +500,38 @@ static int launch_one(inkq_ctx *ctx, const CUtensorMap &map, const TcParams &prm
         if (e != cudaSuccess) return fail(ctx, INKQ_ERR_CUDA, std::string("cudaFuncSetAttribute(k_qgemm_tc): ") + cudaGetErrorString(e));
         configured = true;
     }
-    k_qgemm_tc<CW, HAS_MIN><<<grid, TC_THREADS, TC_SMEM_BYTES, ctx->stream>>>(map, prm);
+    k_qgemm_tc<CW, HAS_MIN><<<grid, TC_THREADS, TC_SMEM_BYTES, ctx->stream>>>(maps[0], maps[1], maps[2], prm);
     return after_launch(ctx, "k_qgemm_tc");
 }
 
 template <bool HAS_MIN>
-static int launch_cw(inkq_ctx *ctx, int cw, const CUtensorMap &map, const TcParams &prm, int grid)
+static int launch_cw(inkq_ctx *ctx, int cw, const CUtensorMap *maps, const TcParams &prm, int grid)
 {
     switch (cw) {
-        case 8: return launch_one<8, HAS_MIN>(ctx, map, prm, grid);
-        case 16: return launch_one<16, HAS_MIN>(ctx, map, prm, grid);
-        case 24: return launch_one<24, HAS_MIN>(ctx, map, prm, grid);
-        case 32: return launch_one<32, HAS_MIN>(ctx, map, prm, grid);
-        case 40: return launch_one<40, HAS_MIN>(ctx, map, prm, grid);
-        case 48: return launch_one<48, HAS_MIN>(ctx, map, prm, grid);
-        case 56: return launch_one<56, HAS_MIN>(ctx, map, prm, grid);
-        case 64: return launch_one<64, HAS_MIN>(ctx, map, prm, grid);
+        case 4: return launch_one<4, HAS_MIN>(ctx, maps, prm, grid);
+        case 8: return launch_one<8, HAS_MIN>(ctx, maps, prm, grid);
+        case 12: return launch_one<12, HAS_MIN>(ctx, maps, prm, grid);
+        case 16: return launch_one<16, HAS_MIN>(ctx, maps, prm, grid);
+        case 20: return launch_one<20, HAS_MIN>(ctx, maps, prm, grid);
+        case 24: return launch_one<24, HAS_MIN>(ctx, maps, prm, grid);
+        case 28: return launch_one<28, HAS_MIN>(ctx, maps, prm, grid);
+        case 32: return launch_one<32, HAS_MIN>(ctx, maps, prm, grid);
     }
     return fail(ctx, INKQ_ERR_INVALID, "internal: bad column width");
+}
+
+static int encode2d(inkq_ctx *ctx, CUtensorMap *map, CUtensorMapDataType dt, int elem_bytes, const void *base, uint64_t dim0, uint64_t dim1,
+                    uint32_t box0, uint32_t box1, CUtensorMapSwizzle swz)
+{
+    const cuuint64_t gdim[2] = {dim0, dim1};
+    const cuuint64_t gstride[1] = {dim0 * static_cast<uint64_t>(elem_bytes)};
+    const cuuint32_t box[2] = {box0, box1};
+    const cuuint32_t estr[2] = {1u, 1u};
+    CUresult cr = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled)(map, dt, 2, const_cast<void *>(base), gdim, gstride, box, estr,
+                                                                     CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return fail(ctx, INKQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(cr)));
+    return INKQ_OK;
 }
 
 int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc, int32_t *dots)
@@ -398,24 +540,19 @@ int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int l
     const int M = a->M;
     const int tiles_m = (M + 127) / 128;
     const int block_m = (((M + tiles_m - 1) / tiles_m) + 15) & ~15;  // even split, multiple of 16, <= 128
+    const int nb = a->K / QK;
 
-    CUtensorMap map;
-    const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(a->K), static_cast<cuuint64_t>(M)};
-    const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(a->K)};
-    const cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(block_m)};
-    const cuuint32_t estr[2] = {1u, 1u};
-    CUresult cr = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled)(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->q, gdim, gstride, box, estr,
-                                                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                                                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (cr != CUDA_SUCCESS) return fail(ctx, INKQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(cr)));
+    CUtensorMap maps[3];
+    int rc = encode2d(ctx, &maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->q, a->K, M, 128u, block_m, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!rc) rc = encode2d(ctx, &maps[1], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a->d, a->M_ld, nb, block_m, STAGE_BLOCKS, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (!rc) rc = encode2d(ctx, &maps[2], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a->s, a->M_ld, nb, block_m, STAGE_BLOCKS, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
 
     TcParams prm;
     prm.nibT = w->nibT;
     prm.sc32 = w->sc32;
     prm.sc16 = w->sc16;
     prm.zpT = w->zpT;
-    prm.d_a = a->d;
-    prm.s_a = a->s;
     prm.C = C;
     prm.dots = dots;
     prm.flag = ctx->dev_flag;
@@ -428,12 +565,10 @@ int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int l
     prm.tiles_m = tiles_m;
     prm.block_m = block_m;
     prm.ldc = ldc;
-    const char *dbg = getenv("INKQ_TC_DESC_SWAP");
-    prm.desc_swap = (dbg != nullptr && dbg[0] == '1') ? 1 : 0;
     const int total = prm.tiles_n * prm.tiles_m;
     const int grid = total < ctx->num_sms ? total : ctx->num_sms;
-    if (w->scheme == INKQ_A81W41) return launch_cw<true>(ctx, block_m / 2, map, prm, grid);
-    return launch_cw<false>(ctx, block_m / 2, map, prm, grid);
+    if (w->scheme == INKQ_A81W41) return launch_cw<true>(ctx, block_m / 4, maps, prm, grid);
+    return launch_cw<false>(ctx, block_m / 4, maps, prm, grid);
 }
 
 }  // namespace inkq
