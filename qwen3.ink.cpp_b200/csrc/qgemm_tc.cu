@@ -32,7 +32,7 @@
 //               block's int32 tile, s32->f32, scale, accumulate in registers in exactly the
 //               reference's order; at the end of a tile the fp32 accumulators are stored to C.
 //               Warp w reads TMEM lanes 32*(w%4).. and a quarter of the columns.
-// Rings: 4 raw stages, 2 unpacked stages, 4 scale stages, 4 TMEM accumulators of 128 columns.
+// Rings: 5 raw stages, 3 unpacked stages, 4 scale stages, 4 TMEM accumulators of 128 columns.
 // Every mbarrier wait is bounded; on expiry the kernel sets a device flag and all
 // roles drain and leave (the context stays usable, the host reports INKQ_ERR_TIMEOUT).
 //
@@ -52,8 +52,8 @@ constexpr int TC_THREADS = 768;
 constexpr int EPI_WARPS = 16;
 constexpr int STAGE_PAIRS = 2;                         // pairs per stage
 constexpr int STAGE_BLOCKS = 2 * STAGE_PAIRS;          // 4 MMAs per stage
-constexpr int RAW_STAGES = 4;
-constexpr int U8_STAGES = 2;
+constexpr int RAW_STAGES = 5;
+constexpr int U8_STAGES = 3;
 constexpr int ACC_STAGES = 4;
 constexpr int SC_STAGES = 4;
 constexpr int SC_PLANE_BYTES = STAGE_BLOCKS * 128 * 4;    // one plane of a scale stage: [4 blocks][128 rows] fp32
@@ -77,7 +77,18 @@ struct TcParams {
     int32_t *dots;   // non-null: dump raw int32 block dots [M][rows][K/32] instead of computing C
     int *flag;
     int M, M_ld, rows, K, pairs, tiles_n, tiles_m, block_m, ldc;
+#ifdef INKQ_ROLE_TIMERS
+    long long *timers;   // [gridDim.x][16] cycle counters, development only
+#endif
 };
+
+#ifdef INKQ_ROLE_TIMERS
+#define T_BEGIN() const long long t_begin__ = clock64()
+#define T_ADD(slot) tacc[slot] += clock64() - t_begin__
+#else
+#define T_BEGIN()
+#define T_ADD(slot)
+#endif
 
 struct Ring {
     uint32_t idx = 0, phase = 0;
@@ -221,7 +232,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
                 const int tn = tile / prm.tiles_m, tm = tile % prm.tiles_m;
                 for (int ks = 0; ks < k_stages; ks++) {
-                    if (!mbar_wait_abortable(abort_flag, &raw_empty[raw.idx], raw.phase ^ 1, 1000u)) INKQ_GIVE_UP();
+                    if (!mbar_wait_abortable(abort_flag, &raw_empty[raw.idx], raw.phase ^ 1, 128u)) INKQ_GIVE_UP();
                     const int np = min(STAGE_PAIRS, prm.pairs - ks * STAGE_PAIRS);
                     unsigned char *st = raw_base + raw.idx * RAW_STAGE_BYTES;
                     const uint32_t tx = BLOCK_M * 128 + np * (TILE_N * 32) + np * (TILE_N * 2);
@@ -246,7 +257,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
                 const int tm = tile % prm.tiles_m;
                 for (int ks = 0; ks < k_stages; ks++) {
-                    if (!mbar_wait_abortable(abort_flag, &sc_empty[sc.idx], sc.phase ^ 1, 1000u)) INKQ_GIVE_UP();
+                    if (!mbar_wait_abortable(abort_flag, &sc_empty[sc.idx], sc.phase ^ 1, 128u)) INKQ_GIVE_UP();
                     unsigned char *st = sc_base + sc.idx * SC_STAGE_BYTES;
                     const uint32_t plane = STAGE_BLOCKS * BLOCK_M * 4;  // the box is always full size; out-of-range parts arrive as zeros
                     mbar_arrive_expect_tx(&sc_full[sc.idx], HAS_MIN ? 2 * plane : plane);
@@ -263,17 +274,31 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             const uint32_t idesc = umma_idesc_i8(TILE_N, BLOCK_M);
             Ring raw(RAW_STAGES), u8(U8_STAGES), acc(ACC_STAGES);
             bool dead = false;
+#ifdef INKQ_ROLE_TIMERS
+            long long tacc[3] = {0, 0, 0};
+#endif
             for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
                 for (int ks = 0; ks < k_stages && !dead; ks++) {
-                    if (!mbar_wait_abortable(abort_flag, &raw_full[raw.idx], raw.phase) ||
-                        !mbar_wait_abortable(abort_flag, &u8_full[u8.idx], u8.phase))
-                        INKQ_GIVE_UP();
+                    {
+                        T_BEGIN();
+                        if (!mbar_wait_abortable(abort_flag, &raw_full[raw.idx], raw.phase, 32u)) INKQ_GIVE_UP();
+                        T_ADD(0);
+                    }
+                    {
+                        T_BEGIN();
+                        if (!mbar_wait_abortable(abort_flag, &u8_full[u8.idx], u8.phase, 32u)) INKQ_GIVE_UP();
+                        T_ADD(1);
+                    }
                     tc_fence_after_sync();
                     const int nblk = 2 * min(STAGE_PAIRS, prm.pairs - ks * STAGE_PAIRS);
                     const uint32_t a_smem = smem_u32(u8_base + u8.idx * U8_STAGE_BYTES);
                     const uint32_t b_smem = smem_u32(raw_base + raw.idx * RAW_STAGE_BYTES);
                     for (int j = 0; j < nblk; j++) {
-                        if (!mbar_wait_abortable(abort_flag, &acc_empty[acc.idx], acc.phase ^ 1)) INKQ_GIVE_UP();
+                        {
+                            T_BEGIN();
+                            if (!mbar_wait_abortable(abort_flag, &acc_empty[acc.idx], acc.phase ^ 1, 32u)) INKQ_GIVE_UP();
+                            T_ADD(2);
+                        }
                         tc_fence_after_sync();
                         // A: unpacked weights of block j, no swizzle: element (row r, k) at
                         //    (k / 16) * 2048 + r * 16 + (k % 16): the two K halves 2048 B apart
@@ -293,6 +318,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     u8.advance();
                 }
             }
+#ifdef INKQ_ROLE_TIMERS
+            for (int i = 0; i < 3; i++) prm.timers[blockIdx.x * 16 + i] = tacc[i];
+#endif
         }
         __syncwarp();
     } else if (warp >= 4 && warp < 8) {
@@ -305,11 +333,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         const int chunk = (lane >> 3) & 1;
         Ring raw(RAW_STAGES), u8(U8_STAGES);
         bool dead = false;
+#ifdef INKQ_ROLE_TIMERS
+        long long tacc[3] = {0, 0, 0};
+        const long long t_role0 = clock64();
+#endif
         for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
             for (int ks = 0; ks < k_stages; ks++) {
-                if (!mbar_wait_abortable(abort_flag, &raw_full[raw.idx], raw.phase) ||
-                    !mbar_wait_abortable(abort_flag, &u8_empty[u8.idx], u8.phase ^ 1))
-                    INKQ_GIVE_UP();
+                {
+                    T_BEGIN();
+                    if (!mbar_wait_abortable(abort_flag, &raw_full[raw.idx], raw.phase, 64u)) INKQ_GIVE_UP();
+                    T_ADD(0);
+                }
+                {
+                    T_BEGIN();
+                    if (!mbar_wait_abortable(abort_flag, &u8_empty[u8.idx], u8.phase ^ 1, 64u)) INKQ_GIVE_UP();
+                    T_ADD(1);
+                }
                 const int np = min(STAGE_PAIRS, prm.pairs - ks * STAGE_PAIRS);
                 const unsigned char *wsrc = raw_base + raw.idx * RAW_STAGE_BYTES + RAW_A_BYTES;
                 const unsigned char *zsrc = wsrc + RAW_W_BYTES;
@@ -342,6 +381,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 u8.advance();
             }
         }
+#ifdef INKQ_ROLE_TIMERS
+        if (threadIdx.x == 128) {
+            prm.timers[blockIdx.x * 16 + 4] = tacc[0];
+            prm.timers[blockIdx.x * 16 + 5] = tacc[1];
+            prm.timers[blockIdx.x * 16 + 6] = clock64() - t_role0;
+        }
+#endif
     } else if (warp >= 8) {
         // ------------------------------ epilogue ------------------------------
         constexpr int CH = (CW >= 16) ? 16 : CW;   // columns per TMEM load step
@@ -353,6 +399,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         const int nbk = 2 * prm.pairs;
         Ring acc(ACC_STAGES), sc(SC_STAGES);
         bool dead = false;
+#ifdef INKQ_ROLE_TIMERS
+        long long tacc[4] = {0, 0, 0, 0};
+        const long long t_role0 = clock64();
+#endif
         for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
             const int tn = tile / prm.tiles_m, tm = tile % prm.tiles_m;
             const int n = tn * TILE_N + row;
@@ -381,13 +431,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 wsc_next = load_wsc(p + 1);
                 const int pj = p & (STAGE_PAIRS - 1);
                 if (pj == 0 && prm.dots == nullptr) {
-                    if (!mbar_wait_abortable(abort_flag, &sc_full[sc.idx], sc.phase, 64u, 64u)) INKQ_GIVE_UP();
+                    T_BEGIN();
+                    if (!mbar_wait_abortable(abort_flag, &sc_full[sc.idx], sc.phase, 32u, 4u)) INKQ_GIVE_UP();
+                    T_ADD(0);
                 }
                 const float *sd_lo = reinterpret_cast<const float *>(sc_base + sc.idx * SC_STAGE_BYTES) + (2 * pj) * BLOCK_M + col0;
 #pragma unroll
                 for (int hi = 0; hi < 2; hi++) {   // the two blocks of the pair: low nibbles, then high nibbles
-                    if (!mbar_wait_abortable(abort_flag, &acc_full[acc.idx], acc.phase, 64u, 64u)) INKQ_GIVE_UP();
+                    {
+                        T_BEGIN();
+                        if (!mbar_wait_abortable(abort_flag, &acc_full[acc.idx], acc.phase, 32u, 4u)) INKQ_GIVE_UP();
+                        T_ADD(1);
+                    }
                     tc_fence_after_sync();
+#ifdef INKQ_ROLE_TIMERS
+                    const long long t_ld0 = clock64();
+#endif
                     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc.idx * ACC_COLS + col0;
                     const float dw = hi ? wsc.y : wsc.x;
                     const float *sd = sd_lo + hi * BLOCK_M;          // d_a of this block
@@ -404,6 +463,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                             tc_fence_before_sync();
                             __syncwarp();
                             if (lane == 0) mbar_arrive(&acc_empty[acc.idx]);
+#ifdef INKQ_ROLE_TIMERS
+                            tacc[2] += clock64() - t_ld0;
+#endif
                         }
                         const int ncols = (c == NCH - 1) ? CH_LAST : CH;
                         if (prm.dots != nullptr) {
@@ -477,6 +539,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 }
             }
         }
+#ifdef INKQ_ROLE_TIMERS
+        if (threadIdx.x == 256 || threadIdx.x == 256 + 12 * 32) {
+            const int o = (threadIdx.x == 256) ? 8 : 12;
+            prm.timers[blockIdx.x * 16 + o + 0] = tacc[0];
+            prm.timers[blockIdx.x * 16 + o + 1] = tacc[1];
+            prm.timers[blockIdx.x * 16 + o + 2] = tacc[2];
+            prm.timers[blockIdx.x * 16 + o + 3] = clock64() - t_role0;
+        }
+#endif
     }
 #undef INKQ_GIVE_UP
     tc_fence_before_sync();
@@ -565,10 +636,28 @@ int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int l
     prm.tiles_m = tiles_m;
     prm.block_m = block_m;
     prm.ldc = ldc;
+#ifdef INKQ_ROLE_TIMERS
+    static long long *timers_dev = nullptr;
+    if (timers_dev == nullptr) cudaMalloc(reinterpret_cast<void **>(&timers_dev), 256 * 16 * sizeof(long long));
+    prm.timers = timers_dev;
+#endif
     const int total = prm.tiles_n * prm.tiles_m;
     const int grid = total < ctx->num_sms ? total : ctx->num_sms;
-    if (w->scheme == INKQ_A81W41) return launch_cw<true>(ctx, block_m / 4, maps, prm, grid);
-    return launch_cw<false>(ctx, block_m / 4, maps, prm, grid);
+    int rc2 = (w->scheme == INKQ_A81W41) ? launch_cw<true>(ctx, block_m / 4, maps, prm, grid) : launch_cw<false>(ctx, block_m / 4, maps, prm, grid);
+#ifdef INKQ_ROLE_TIMERS
+    {
+        static long long host_t[256 * 16];
+        cudaMemcpy(host_t, prm.timers, sizeof(host_t), cudaMemcpyDeviceToHost);
+        const char *names[16] = {"mma.wait_raw_full", "mma.wait_u8_full", "mma.wait_acc_empty", "-", "unpack.wait_raw_full", "unpack.wait_u8_empty", "unpack.total", "-",
+                                 "epi0.wait_sc_full", "epi0.wait_acc_full", "epi0.tmem_ld", "epi0.total", "epi12.wait_sc_full", "epi12.wait_acc_full", "epi12.tmem_ld", "epi12.total"};
+        for (int i = 0; i < 16; i++) {
+            double sum = 0;
+            for (int b = 0; b < grid; b++) sum += static_cast<double>(host_t[b * 16 + i]);
+            fprintf(stderr, "[role timers] %-24s %12.0f cycles avg per CTA\n", names[i], sum / grid);
+        }
+    }
+#endif
+    return rc2;
 }
 
 }  // namespace inkq
