@@ -134,6 +134,17 @@ int inkq_debug_block_dots_tc(inkq_ctx *ctx, const inkq_act *act, const inkq_weig
 int inkq_linear(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, int M, float *C_dev, int ldc);
 int inkq_linear_host(inkq_ctx *ctx, const inkq_weight *w, const float *x_host, int M, float *C_host, int ldc);
 
+/* ---- decode forward without any allocation ---------------------------------------
+ * No counterpart in the reference.  For hosts that may not call cudaMalloc while
+ * serving (a latency-bound decode loop, a process whose device heap belongs to
+ * another allocator): the M == 1 forward of inkq_linear with its scratch - one
+ * quantized activation row - in a fixed 20 KiB device array inside the library
+ * instead of the context's growable buffer.  K <= 16384, else INKQ_ERR_UNSUPPORTED.
+ * The first call on a device resolves the array's address; make it before any
+ * stream capture.  All calls on a device share the array: calls that overlap on
+ * the GPU race, order them.  Never allocates or frees device memory. */
+int inkq_linear_m1_static(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, float *C_dev);
+
 /* ---- weight-only W41 (fp16 activations) and fp16 lm_head ---------------------
  * No C++ kernel exists in the reference for these two; they follow
  * notebooks/evaluate-qwen3_8b_W4.ipynb cell 13 and, for lm_head, the fp32 GEMV

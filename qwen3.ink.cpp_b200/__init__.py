@@ -31,7 +31,7 @@ SYMBOLS = [
     "inkq_launch_count", "inkq_weight_create", "inkq_weight_create_dev", "inkq_weight_destroy", "inkq_weight_info",
     "inkq_weight_export", "inkq_act_create", "inkq_act_destroy", "inkq_quantize", "inkq_act_export", "inkq_gemm",
     "inkq_gemv", "inkq_gemm_simt", "inkq_debug_block_dots", "inkq_debug_block_dots_tc", "inkq_linear",
-    "inkq_linear_host", "inkq_gemm_w41_f16act", "inkq_f16w_create", "inkq_f16w_create_dev", "inkq_f16w_destroy",
+    "inkq_linear_host", "inkq_linear_m1_static", "inkq_gemm_w41_f16act", "inkq_f16w_create", "inkq_f16w_create_dev", "inkq_f16w_destroy",
     "inkq_f16w_matmul",
 ]
 
@@ -179,6 +179,10 @@ class Context:
         xp = x_host.ctypes.data_as(C.c_void_p) if isinstance(x_host, np.ndarray) else C.c_void_p(x_host.data_ptr())
         cp = C_host.ctypes.data_as(C.c_void_p) if isinstance(C_host, np.ndarray) else C.c_void_p(C_host.data_ptr())
         self.check(self.L.inkq_linear_host(self.h, w.h, xp, M, cp, ldc))
+
+    def linear_m1_static(self, w, x, Cdev):
+        """M == 1 forward that never allocates: scratch in the library's fixed device array (K <= 16384)."""
+        self.check(self.L.inkq_linear_m1_static(self.h, w.h, _dp(x), _dp(Cdev)))
 
     def gemm_w41_f16act(self, a16, M: int, w, Cdev, ldc: int):
         self.check(self.L.inkq_gemm_w41_f16act(self.h, _dp(a16), M, w.h, _dp(Cdev), ldc))
