@@ -189,6 +189,20 @@ __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t *r)
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// Per-warpgroup register re-balancing; all four warps of a warpgroup execute the same one.
+// inc blocks until the CTA's other warpgroups have released enough registers with dec: the
+// caller must make sure the requests never exceed the releases.
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc()
+{
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec()
+{
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // ---- misc -----------------------------------------------------------------------------
 __device__ __forceinline__ uint4 ldg_stream_v4(const void *p)
 {

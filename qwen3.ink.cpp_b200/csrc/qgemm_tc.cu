@@ -50,6 +50,12 @@ namespace inkq {
 
 constexpr int TC_THREADS = 768;
 constexpr int EPI_WARPS = 16;
+// Register re-balancing after the roles split (setmaxnreg).  The kernel is launched with LAUNCH_REGS per
+// thread (checked on the host before the first launch); the two non-epilogue warpgroups release
+// 128*(80-40) + 128*(80-48) = 9216 registers, the four epilogue warpgroups take 512*(96-80) = 8192 of them.
+// A request larger than what was released would block forever, hence the static check.
+constexpr int LAUNCH_REGS = 80, CTRL_REGS = 40, UNPACK_REGS = 48, EPI_REGS = 96;
+static_assert(128 * (LAUNCH_REGS - CTRL_REGS) + 128 * (LAUNCH_REGS - UNPACK_REGS) >= 512 * (EPI_REGS - LAUNCH_REGS), "setmaxnreg budget");
 constexpr int STAGE_PAIRS = 2;                         // pairs per stage
 constexpr int STAGE_BLOCKS = 2 * STAGE_PAIRS;          // 4 MMAs per stage
 constexpr int RAW_STAGES = 5;
@@ -160,7 +166,7 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t *r)
 }
 
 // CW = columns of the accumulator handled by one epilogue warp (BLOCK_M / 4).
-template <int CW, bool HAS_MIN>
+template <int CW, bool HAS_MIN, bool DUMP>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     k_qgemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_s,
                const TcParams prm)
@@ -223,6 +229,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         break;                    \
     }
 
+    if (warp < 4) setmaxnreg_dec<CTRL_REGS>();
+    if (warp >= 4 && warp < 8) setmaxnreg_dec<UNPACK_REGS>();
     if (warp == 0) {
         // ------------------------------ operand TMA producer ------------------------------
         if (lane == 0) {
@@ -249,7 +257,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         __syncwarp();
     } else if (warp == 3) {
         // ------------------------------ scale TMA producer ------------------------------
-        if (lane == 0 && prm.dots == nullptr) {  // the block-dot dump applies no scales
+        if (lane == 0 && !DUMP) {  // the block-dot dump applies no scales
             tma_prefetch_desc(&map_d);
             if (HAS_MIN) tma_prefetch_desc(&map_s);
             Ring sc(SC_STAGES);
@@ -276,6 +284,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             bool dead = false;
 #ifdef INKQ_ROLE_TIMERS
             long long tacc[3] = {0, 0, 0};
+            long long mma_lat = 0, mma_cnt = 0;
 #endif
             for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
                 for (int ks = 0; ks < k_stages && !dead; ks++) {
@@ -307,8 +316,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                         // B: activations, 128-byte swizzled rows of 128 B; block j is the j-th
                         //    32-byte slice of the row; 8-row groups are 1024 B apart.
                         const uint64_t b_desc = umma_smem_desc(b_smem + j * 32, 16, 1024, 2);
+#ifdef INKQ_ROLE_TIMERS
+                        const long long t_issue = clock64();
+#endif
                         umma_i8(tmem_base + acc.idx * ACC_COLS, a_desc, b_desc, idesc, 0u);
                         umma_commit(&acc_full[acc.idx]);
+#ifdef INKQ_ROLE_TIMERS
+                        if (tile == blockIdx.x && ks < 8) {   // development only: issue -> completion latency of one MMA
+                            while (!mbar_try_wait(&acc_full[acc.idx], acc.phase)) {}
+                            mma_lat += clock64() - t_issue;
+                            mma_cnt++;
+                        }
+#endif
                         acc.advance();
                     }
                     if (dead) break;
@@ -320,6 +339,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             }
 #ifdef INKQ_ROLE_TIMERS
             for (int i = 0; i < 3; i++) prm.timers[blockIdx.x * 16 + i] = tacc[i];
+            prm.timers[blockIdx.x * 16 + 3] = mma_cnt ? mma_lat / mma_cnt : 0;
 #endif
         }
         __syncwarp();
@@ -353,7 +373,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 const unsigned char *wsrc = raw_base + raw.idx * RAW_STAGE_BYTES + RAW_A_BYTES;
                 const unsigned char *zsrc = wsrc + RAW_W_BYTES;
                 unsigned char *dst = u8_base + u8.idx * U8_STAGE_BYTES;
+#ifdef INKQ_EXP_NOUNPACK
+                for (int pp = 0; pp < 0; pp++) {
+#else
                 for (int pp = 0; pp < np; pp++) {
+#endif
 #pragma unroll
                     for (int it = 0; it < 2; it++) {
                         const int r = (it * 4 + uw) * 16 + rr;
@@ -390,13 +414,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 #endif
     } else if (warp >= 8) {
         // ------------------------------ epilogue ------------------------------
-        constexpr int CH = (CW >= 16) ? 16 : CW;   // columns per TMEM load step
-        constexpr int NCH = (CW + CH - 1) / CH;    // 1 or 2 steps (CW <= 32); the last one may be shorter
+        // Software pipeline: the accumulator columns of a block are read in NCH chunks; while the
+        // arithmetic of one chunk runs, the tcgen05.ld of the next chunk (of this block or of the
+        // next one) is in flight into the other register buffer, so the TMEM round trip and the
+        // probe of the accumulator barrier are off the critical path.
+        setmaxnreg_inc<EPI_REGS>();
+        constexpr int CH = (CW > 16) ? 16 : CW;    // columns per chunk
+        constexpr int NCH = (CW + CH - 1) / CH;    // 1 or 2 chunks (CW <= 32); the last one may be shorter
         constexpr int CH_LAST = CW - (NCH - 1) * CH;
         const int quad = warp & 3;             // TMEM lane quadrant this warp may read
         const int cq = (warp - 8) >> 2;        // which quarter of the accumulator columns
         const int row = quad * 32 + lane;      // weight row inside the tile = TMEM lane
         const int nbk = 2 * prm.pairs;
+        const int col0 = cq * CW;              // first column of this warp inside the tile
         Ring acc(ACC_STAGES), sc(SC_STAGES);
         bool dead = false;
 #ifdef INKQ_ROLE_TIMERS
@@ -406,16 +436,33 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
             const int tn = tile / prm.tiles_m, tm = tile % prm.tiles_m;
             const int n = tn * TILE_N + row;
-            const int col0 = cq * CW;            // first column of this warp inside the tile
-#ifndef INKQ_SCALAR_EPILOGUE
             unsigned long long accp[CW / 2];
 #pragma unroll
             for (int j = 0; j < CW / 2; j++) accp[j] = 0ull;
-#else
-            float accf[CW];
-#pragma unroll
-            for (int j = 0; j < CW; j++) accf[j] = 0.0f;
-#endif
+            uint32_t rbuf[2][CH];                 // the two chunk buffers
+            uint32_t taddr_blk = 0;               // TMEM address of the block whose chunks are being loaded
+            uint32_t acc_loading = 0;             // its slot in the accumulator ring
+
+            // waits for block `acc` of the ring to be computed and starts the load of its first chunk
+            auto begin_block = [&](uint32_t *dst) -> bool {
+                if (!mbar_wait_abortable(abort_flag, &acc_full[acc.idx], acc.phase, 32u, 8u)) return false;
+                tc_fence_after_sync();
+                taddr_blk = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc.idx * ACC_COLS + col0;
+                acc_loading = acc.idx;
+                acc.advance();
+                if (NCH == 1) tmem_ld_cols<CH_LAST>(taddr_blk, dst);
+                else tmem_ld_cols<CH>(taddr_blk, dst);
+                return true;
+            };
+            // completes the outstanding load; when it was the block's last chunk, hands the TMEM buffer back
+            auto finish_load = [&](bool last_chunk_of_block) {
+                tmem_ld_wait();
+                if (last_chunk_of_block) {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[acc_loading]);
+                }
+            };
             // this row's weight scales {d_lo, d_hi, m_lo, m_hi} of a pair, fetched one pair ahead
             auto load_wsc = [&](int pair) -> float4 {
                 const size_t rec = (static_cast<size_t>(tn) * prm.pairs + min(pair, prm.pairs - 1)) * TILE_N + row;
@@ -425,113 +472,88 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 const float2 x1 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.y));
                 return make_float4(x0.x, x0.y, x1.x, x1.y);
             };
+
+            // pipeline prologue: first chunk of the tile's first block
+            if (!begin_block(rbuf[0])) INKQ_GIVE_UP();
+            finish_load(NCH == 1);
             float4 wsc_next = load_wsc(0);
+
             for (int p = 0; p < prm.pairs && !dead; p++) {
                 const float4 wsc = wsc_next;
                 wsc_next = load_wsc(p + 1);
                 const int pj = p & (STAGE_PAIRS - 1);
-                if (pj == 0 && prm.dots == nullptr) {
-                    T_BEGIN();
-                    if (!mbar_wait_abortable(abort_flag, &sc_full[sc.idx], sc.phase, 32u, 4u)) INKQ_GIVE_UP();
-                    T_ADD(0);
+                if (pj == 0 && !DUMP) {
+                    if (!mbar_wait_abortable(abort_flag, &sc_full[sc.idx], sc.phase, 32u, 8u)) INKQ_GIVE_UP();
                 }
                 const float *sd_lo = reinterpret_cast<const float *>(sc_base + sc.idx * SC_STAGE_BYTES) + (2 * pj) * BLOCK_M + col0;
+                const float *ss_lo = sd_lo + SC_PLANE_BYTES / 4;   // s_a of the low block; the high block's follows
 #pragma unroll
                 for (int hi = 0; hi < 2; hi++) {   // the two blocks of the pair: low nibbles, then high nibbles
-                    {
-                        T_BEGIN();
-                        if (!mbar_wait_abortable(abort_flag, &acc_full[acc.idx], acc.phase, 32u, 4u)) INKQ_GIVE_UP();
-                        T_ADD(1);
-                    }
-                    tc_fence_after_sync();
-#ifdef INKQ_ROLE_TIMERS
-                    const long long t_ld0 = clock64();
-#endif
-                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc.idx * ACC_COLS + col0;
+                    const int b = 2 * p + hi;
                     const float dw = hi ? wsc.y : wsc.x;
                     const float *sd = sd_lo + hi * BLOCK_M;          // d_a of this block
-                    const float *ss_lo = sd_lo + SC_PLANE_BYTES / 4; // s_a of the low block; the high block's follows
-                    const int b = 2 * p + hi;
 #pragma unroll
                     for (int c = 0; c < NCH; c++) {
-                        uint32_t raw[CH];
-                        if (c == NCH - 1) tmem_ld_cols<CH_LAST>(taddr + c * CH, raw);
-                        else tmem_ld_cols<CH>(taddr + c * CH, raw);
-                        tmem_ld_wait();
-                        if (c == NCH - 1) {
-                            // the whole accumulator is in registers: hand the TMEM buffer back
-                            tc_fence_before_sync();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(&acc_empty[acc.idx]);
-#ifdef INKQ_ROLE_TIMERS
-                            tacc[2] += clock64() - t_ld0;
-#endif
+                        // item (b, c) sits in rbuf[cur]; start the load of the item after it into rbuf[nxt]
+                        const int cur = (hi * NCH + c) & 1, nxt = cur ^ 1;
+                        bool loading = false, loading_last = false;
+                        if (c + 1 < NCH) {   // next chunk of the same block
+                            tmem_ld_cols<CH_LAST>(taddr_blk + (c + 1) * CH, rbuf[nxt]);
+                            loading = true;
+                            loading_last = true;
+                        } else if (b + 1 < nbk) {   // first chunk of the next block
+                            if (!begin_block(rbuf[nxt])) INKQ_GIVE_UP();
+                            loading = true;
+                            loading_last = (NCH == 1);
                         }
+                        const uint32_t *raw = rbuf[cur];
                         const int ncols = (c == NCH - 1) ? CH_LAST : CH;
-                        if (prm.dots != nullptr) {
+                        if (DUMP) {
 #pragma unroll
                             for (int j = 0; j < CH; j++) {
                                 const int m = tm * BLOCK_M + col0 + c * CH + j;
                                 if (j < ncols && m < prm.M && n < prm.rows)
                                     prm.dots[(static_cast<size_t>(m) * prm.rows + n) * nbk + b] = static_cast<int32_t>(raw[j]);
                             }
-                            continue;
-                        }
+                        } else {
 #pragma unroll
-                        for (int j4 = 0; j4 < CH; j4 += 4) {
-                            if (j4 < ncols) {
-                                const float4 da = *reinterpret_cast<const float4 *>(sd + c * CH + j4);
-#ifndef INKQ_SCALAR_EPILOGUE
-                                const unsigned long long dw2 = pack2(dw, dw);
-                                const int a0 = (c * CH + j4) / 2;
-                                accp[a0] =
-                                    fma2(pack2(s32_to_f32_exact(raw[j4]), s32_to_f32_exact(raw[j4 + 1])), mul2(pack2(da.x, da.y), dw2), accp[a0]);
-                                accp[a0 + 1] = fma2(pack2(s32_to_f32_exact(raw[j4 + 2]), s32_to_f32_exact(raw[j4 + 3])), mul2(pack2(da.z, da.w), dw2),
-                                                    accp[a0 + 1]);
-                                if (HAS_MIN && hi) {
-                                    const float4 s0 = *reinterpret_cast<const float4 *>(ss_lo + c * CH + j4);
-                                    const float4 s1 = *reinterpret_cast<const float4 *>(ss_lo + BLOCK_M + c * CH + j4);
-                                    const unsigned long long mlo = pack2(wsc.z, wsc.z), mhi = pack2(wsc.w, wsc.w);
-                                    accp[a0] = fma2(mlo, pack2(s0.x, s0.y), accp[a0]);
-                                    accp[a0] = fma2(mhi, pack2(s1.x, s1.y), accp[a0]);
-                                    accp[a0 + 1] = fma2(mlo, pack2(s0.z, s0.w), accp[a0 + 1]);
-                                    accp[a0 + 1] = fma2(mhi, pack2(s1.z, s1.w), accp[a0 + 1]);
-                                }
-#else
-                                const float dav[4] = {da.x, da.y, da.z, da.w};
-#pragma unroll
-                                for (int j = 0; j < 4; j++)
-                                    accf[c * CH + j4 + j] = fmaf(s32_to_f32_exact(raw[j4 + j]), __fmul_rn(dav[j], dw), accf[c * CH + j4 + j]);
-                                if (HAS_MIN && hi) {
-                                    const float4 s0 = *reinterpret_cast<const float4 *>(ss_lo + c * CH + j4);
-                                    const float4 s1 = *reinterpret_cast<const float4 *>(ss_lo + BLOCK_M + c * CH + j4);
-                                    const float s0v[4] = {s0.x, s0.y, s0.z, s0.w}, s1v[4] = {s1.x, s1.y, s1.z, s1.w};
-#pragma unroll
-                                    for (int j = 0; j < 4; j++) {
-                                        accf[c * CH + j4 + j] = fmaf(wsc.z, s0v[j], accf[c * CH + j4 + j]);
-                                        accf[c * CH + j4 + j] = fmaf(wsc.w, s1v[j], accf[c * CH + j4 + j]);
+                            for (int j4 = 0; j4 < CH; j4 += 4) {
+                                if (j4 < ncols) {
+                                    const float4 da = *reinterpret_cast<const float4 *>(sd + c * CH + j4);
+                                    const unsigned long long dw2 = pack2(dw, dw);
+                                    const int a0 = (c * CH + j4) / 2;
+                                    accp[a0] = fma2(pack2(s32_to_f32_exact(raw[j4]), s32_to_f32_exact(raw[j4 + 1])), mul2(pack2(da.x, da.y), dw2),
+                                                    accp[a0]);
+                                    accp[a0 + 1] = fma2(pack2(s32_to_f32_exact(raw[j4 + 2]), s32_to_f32_exact(raw[j4 + 3])),
+                                                        mul2(pack2(da.z, da.w), dw2), accp[a0 + 1]);
+                                    if (HAS_MIN && hi) {
+                                        const float4 s0 = *reinterpret_cast<const float4 *>(ss_lo + c * CH + j4);
+                                        const float4 s1 = *reinterpret_cast<const float4 *>(ss_lo + BLOCK_M + c * CH + j4);
+                                        const unsigned long long mlo = pack2(wsc.z, wsc.z), mhi = pack2(wsc.w, wsc.w);
+                                        accp[a0] = fma2(mlo, pack2(s0.x, s0.y), accp[a0]);
+                                        accp[a0] = fma2(mhi, pack2(s1.x, s1.y), accp[a0]);
+                                        accp[a0 + 1] = fma2(mlo, pack2(s0.z, s0.w), accp[a0 + 1]);
+                                        accp[a0 + 1] = fma2(mhi, pack2(s1.z, s1.w), accp[a0 + 1]);
                                     }
                                 }
-#endif
                             }
                         }
+                        if (loading) finish_load(loading_last);
                     }
-                    acc.advance();
+                    if (dead) break;
                 }
                 if (dead) break;
-                if (prm.dots == nullptr && (pj == STAGE_PAIRS - 1 || p == prm.pairs - 1)) {
+                if (!DUMP && (pj == STAGE_PAIRS - 1 || p == prm.pairs - 1)) {
                     // this warp is done with the stage's scales
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sc_empty[sc.idx]);
                     sc.advance();
                 }
             }
-            if (!dead && prm.dots == nullptr && n < prm.rows) {
-#ifndef INKQ_SCALAR_EPILOGUE
+            if (!dead && !DUMP && n < prm.rows) {
                 float accf[CW];
 #pragma unroll
                 for (int j = 0; j < CW / 2; j++) unpack2(accp[j], accf[2 * j], accf[2 * j + 1]);
-#endif
 #pragma unroll
                 for (int j = 0; j < CW; j++) {
                     const int m = tm * BLOCK_M + col0 + j;
@@ -562,31 +584,37 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-template <int CW, bool HAS_MIN>
+template <int CW, bool HAS_MIN, bool DUMP>
 static int launch_one(inkq_ctx *ctx, const CUtensorMap *maps, const TcParams &prm, int grid)
 {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(k_qgemm_tc<CW, HAS_MIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
+        cudaFuncAttributes attr;
+        cudaError_t e = cudaFuncGetAttributes(&attr, k_qgemm_tc<CW, HAS_MIN, DUMP>);
+        if (e != cudaSuccess) return fail(ctx, INKQ_ERR_CUDA, std::string("cudaFuncGetAttributes(k_qgemm_tc): ") + cudaGetErrorString(e));
+        if (attr.numRegs != LAUNCH_REGS)   // the in-kernel register re-balancing is sized for exactly this launch value
+            return fail(ctx, INKQ_ERR_UNSUPPORTED, "k_qgemm_tc was compiled to " + std::to_string(attr.numRegs) + " registers per thread, expected " +
+                                                       std::to_string(LAUNCH_REGS));
+        e = cudaFuncSetAttribute(k_qgemm_tc<CW, HAS_MIN, DUMP>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
         if (e != cudaSuccess) return fail(ctx, INKQ_ERR_CUDA, std::string("cudaFuncSetAttribute(k_qgemm_tc): ") + cudaGetErrorString(e));
         configured = true;
     }
-    k_qgemm_tc<CW, HAS_MIN><<<grid, TC_THREADS, TC_SMEM_BYTES, ctx->stream>>>(maps[0], maps[1], maps[2], prm);
+    k_qgemm_tc<CW, HAS_MIN, DUMP><<<grid, TC_THREADS, TC_SMEM_BYTES, ctx->stream>>>(maps[0], maps[1], maps[2], prm);
     return after_launch(ctx, "k_qgemm_tc");
 }
 
-template <bool HAS_MIN>
+template <bool HAS_MIN, bool DUMP>
 static int launch_cw(inkq_ctx *ctx, int cw, const CUtensorMap *maps, const TcParams &prm, int grid)
 {
     switch (cw) {
-        case 4: return launch_one<4, HAS_MIN>(ctx, maps, prm, grid);
-        case 8: return launch_one<8, HAS_MIN>(ctx, maps, prm, grid);
-        case 12: return launch_one<12, HAS_MIN>(ctx, maps, prm, grid);
-        case 16: return launch_one<16, HAS_MIN>(ctx, maps, prm, grid);
-        case 20: return launch_one<20, HAS_MIN>(ctx, maps, prm, grid);
-        case 24: return launch_one<24, HAS_MIN>(ctx, maps, prm, grid);
-        case 28: return launch_one<28, HAS_MIN>(ctx, maps, prm, grid);
-        case 32: return launch_one<32, HAS_MIN>(ctx, maps, prm, grid);
+        case 4: return launch_one<4, HAS_MIN, DUMP>(ctx, maps, prm, grid);
+        case 8: return launch_one<8, HAS_MIN, DUMP>(ctx, maps, prm, grid);
+        case 12: return launch_one<12, HAS_MIN, DUMP>(ctx, maps, prm, grid);
+        case 16: return launch_one<16, HAS_MIN, DUMP>(ctx, maps, prm, grid);
+        case 20: return launch_one<20, HAS_MIN, DUMP>(ctx, maps, prm, grid);
+        case 24: return launch_one<24, HAS_MIN, DUMP>(ctx, maps, prm, grid);
+        case 28: return launch_one<28, HAS_MIN, DUMP>(ctx, maps, prm, grid);
+        case 32: return launch_one<32, HAS_MIN, DUMP>(ctx, maps, prm, grid);
     }
     return fail(ctx, INKQ_ERR_INVALID, "internal: bad column width");
 }
@@ -643,7 +671,10 @@ int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int l
 #endif
     const int total = prm.tiles_n * prm.tiles_m;
     const int grid = total < ctx->num_sms ? total : ctx->num_sms;
-    int rc2 = (w->scheme == INKQ_A81W41) ? launch_cw<true>(ctx, block_m / 4, maps, prm, grid) : launch_cw<false>(ctx, block_m / 4, maps, prm, grid);
+    int rc2;
+    if (dots != nullptr) rc2 = launch_cw<false, true>(ctx, block_m / 4, maps, prm, grid);
+    else if (w->scheme == INKQ_A81W41) rc2 = launch_cw<true, false>(ctx, block_m / 4, maps, prm, grid);
+    else rc2 = launch_cw<false, false>(ctx, block_m / 4, maps, prm, grid);
 #ifdef INKQ_ROLE_TIMERS
     {
         static long long host_t[256 * 16];
