@@ -51,8 +51,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 }
 // Bounded wait.  Returns false when the limit ran out, or as soon as *abort (a
 // shared-memory word another role sets when its own wait ran out) is non-zero.
-// After `eager` failed probes the thread sleeps `sleep_ns` between probes, so a
-// role that is far ahead of its consumer does not take issue slots from the warps
+// After `eager` failed probes the thread sleeps `sleep_ns` between probes (0 = never:
+// for waits on the critical path, a sleep costs far more than the probes it saves), so
+// a role that is far ahead of its consumer does not take issue slots from the warps
 // doing the arithmetic; the clock is read only every 64 probes.
 __device__ __forceinline__ bool mbar_wait_abortable(volatile int *abort, uint64_t *bar, uint32_t parity, uint32_t sleep_ns = 256u,
                                                     uint32_t eager = 2u)
@@ -62,7 +63,7 @@ __device__ __forceinline__ bool mbar_wait_abortable(volatile int *abort, uint64_
 #pragma unroll 1
     for (uint32_t spin = 1;; spin++) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (spin > eager) __nanosleep(sleep_ns);
+        if (sleep_ns != 0u && spin > eager) __nanosleep(sleep_ns);
         if ((spin & 63u) == 0u && (*abort != 0 || clock64() - t0 > INKQ_SPIN_LIMIT_CYCLES)) return false;
     }
 }

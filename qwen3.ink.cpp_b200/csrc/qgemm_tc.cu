@@ -32,7 +32,8 @@
 //               block's int32 tile, s32->f32, scale, accumulate in registers in exactly the
 //               reference's order; at the end of a tile the fp32 accumulators are stored to C.
 //               Warp w reads TMEM lanes 32*(w%4).. and a quarter of the columns.
-// Rings: 5 raw stages, 3 unpacked stages, 4 scale stages, 4 TMEM accumulators of 128 columns.
+// Rings: 5 raw stages, 3 unpacked stages, 4 scale stages, 2 TMEM accumulator slots of 256 columns (one pair
+// of blocks each: two MMAs, one commit, one hand-shake per pair).
 // Every mbarrier wait is bounded; on expiry the kernel sets a device flag and all
 // roles drain and leave (the context stays usable, the host reports INKQ_ERR_TIMEOUT).
 //
@@ -60,11 +61,11 @@ constexpr int STAGE_PAIRS = 2;                         // pairs per stage
 constexpr int STAGE_BLOCKS = 2 * STAGE_PAIRS;          // 4 MMAs per stage
 constexpr int RAW_STAGES = 5;
 constexpr int U8_STAGES = 3;
-constexpr int ACC_STAGES = 4;
+constexpr int ACC_STAGES = 2;
 constexpr int SC_STAGES = 4;
 constexpr int SC_PLANE_BYTES = STAGE_BLOCKS * 128 * 4;    // one plane of a scale stage: [4 blocks][128 rows] fp32
 constexpr int SC_STAGE_BYTES = 2 * SC_PLANE_BYTES;       // d_a and s_a
-constexpr int ACC_COLS = 128;                          // TMEM columns per accumulator
+constexpr int ACC_COLS = 256;                          // TMEM columns per accumulator slot: one pair, low block at +0, high block at +128
 constexpr int RAW_A_BYTES = 128 * 128;                 // activations: up to 128 rows x 128 B
 constexpr int RAW_W_BYTES = STAGE_PAIRS * TILE_N * 32; // packed weights: 8192
 constexpr int RAW_Z_BYTES = STAGE_PAIRS * TILE_N * 2;  // zero points: 512
@@ -240,7 +241,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
                 const int tn = tile / prm.tiles_m, tm = tile % prm.tiles_m;
                 for (int ks = 0; ks < k_stages; ks++) {
-                    if (!mbar_wait_abortable(abort_flag, &raw_empty[raw.idx], raw.phase ^ 1, 128u)) INKQ_GIVE_UP();
+                    if (!mbar_wait_abortable(abort_flag, &raw_empty[raw.idx], raw.phase ^ 1, 1000u)) INKQ_GIVE_UP();
                     const int np = min(STAGE_PAIRS, prm.pairs - ks * STAGE_PAIRS);
                     unsigned char *st = raw_base + raw.idx * RAW_STAGE_BYTES;
                     const uint32_t tx = BLOCK_M * 128 + np * (TILE_N * 32) + np * (TILE_N * 2);
@@ -265,7 +266,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
                 const int tm = tile % prm.tiles_m;
                 for (int ks = 0; ks < k_stages; ks++) {
-                    if (!mbar_wait_abortable(abort_flag, &sc_empty[sc.idx], sc.phase ^ 1, 128u)) INKQ_GIVE_UP();
+                    if (!mbar_wait_abortable(abort_flag, &sc_empty[sc.idx], sc.phase ^ 1, 1000u)) INKQ_GIVE_UP();
                     unsigned char *st = sc_base + sc.idx * SC_STAGE_BYTES;
                     const uint32_t plane = STAGE_BLOCKS * BLOCK_M * 4;  // the box is always full size; out-of-range parts arrive as zeros
                     mbar_arrive_expect_tx(&sc_full[sc.idx], HAS_MIN ? 2 * plane : plane);
@@ -290,43 +291,45 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 for (int ks = 0; ks < k_stages && !dead; ks++) {
                     {
                         T_BEGIN();
-                        if (!mbar_wait_abortable(abort_flag, &raw_full[raw.idx], raw.phase, 32u)) INKQ_GIVE_UP();
+                        if (!mbar_wait_abortable(abort_flag, &raw_full[raw.idx], raw.phase, 0u)) INKQ_GIVE_UP();
                         T_ADD(0);
                     }
                     {
                         T_BEGIN();
-                        if (!mbar_wait_abortable(abort_flag, &u8_full[u8.idx], u8.phase, 32u)) INKQ_GIVE_UP();
+                        if (!mbar_wait_abortable(abort_flag, &u8_full[u8.idx], u8.phase, 0u)) INKQ_GIVE_UP();
                         T_ADD(1);
                     }
                     tc_fence_after_sync();
                     const int nblk = 2 * min(STAGE_PAIRS, prm.pairs - ks * STAGE_PAIRS);
-                    const uint32_t a_smem = smem_u32(u8_base + u8.idx * U8_STAGE_BYTES);
-                    const uint32_t b_smem = smem_u32(raw_base + raw.idx * RAW_STAGE_BYTES);
-                    for (int j = 0; j < nblk; j++) {
+                    // A: unpacked weights, no swizzle: element (row r, k) of a block at (k / 16) * 2048 + r * 16 + (k % 16):
+                    //    the two K halves 2048 B apart (leading offset), 8-row core matrices 128 B apart (stride offset);
+                    //    consecutive blocks of the stage are 4096 B apart.
+                    // B: activations, 128-byte swizzled rows of 128 B; block j is the j-th 32-byte slice of the row; 8-row
+                    //    groups are 1024 B apart.  The start-address field counts 16-byte units.
+                    const uint64_t a_desc0 = umma_smem_desc(smem_u32(u8_base + u8.idx * U8_STAGE_BYTES), 2048, 128, 0);
+                    const uint64_t b_desc0 = umma_smem_desc(smem_u32(raw_base + raw.idx * RAW_STAGE_BYTES), 16, 1024, 2);
+#pragma unroll
+                    for (int pp = 0; pp < STAGE_PAIRS; pp++) {
+                        if (2 * pp >= nblk) break;
                         {
                             T_BEGIN();
-                            if (!mbar_wait_abortable(abort_flag, &acc_empty[acc.idx], acc.phase ^ 1, 32u)) INKQ_GIVE_UP();
+                            if (!mbar_wait_abortable(abort_flag, &acc_empty[acc.idx], acc.phase ^ 1, 0u)) INKQ_GIVE_UP();
                             T_ADD(2);
                         }
                         tc_fence_after_sync();
-                        // A: unpacked weights of block j, no swizzle: element (row r, k) at
-                        //    (k / 16) * 2048 + r * 16 + (k % 16): the two K halves 2048 B apart
-                        //    (leading offset), 8-row core matrices 128 B apart (stride offset).
-                        const uint64_t a_desc = umma_smem_desc(a_smem + j * U8_BLOCK_BYTES, 2048, 128, 0);
-                        // B: activations, 128-byte swizzled rows of 128 B; block j is the j-th
-                        //    32-byte slice of the row; 8-row groups are 1024 B apart.
-                        const uint64_t b_desc = umma_smem_desc(b_smem + j * 32, 16, 1024, 2);
 #ifdef INKQ_ROLE_TIMERS
                         const long long t_issue = clock64();
 #endif
-                        umma_i8(tmem_base + acc.idx * ACC_COLS, a_desc, b_desc, idesc, 0u);
+#pragma unroll
+                        for (int hi = 0; hi < 2; hi++) {
+                            const int j = 2 * pp + hi;
+                            umma_i8(tmem_base + acc.idx * ACC_COLS + hi * 128, a_desc0 + static_cast<uint64_t>(j * (U8_BLOCK_BYTES >> 4)),
+                                    b_desc0 + static_cast<uint64_t>(j * (32 >> 4)), idesc, 0u);
+                        }
                         umma_commit(&acc_full[acc.idx]);
 #ifdef INKQ_ROLE_TIMERS
-                        if (tile == blockIdx.x && ks < 8) {   // development only: issue -> completion latency of one MMA
-                            while (!mbar_try_wait(&acc_full[acc.idx], acc.phase)) {}
-                            mma_lat += clock64() - t_issue;
-                            mma_cnt++;
-                        }
+                        mma_lat += clock64() - t_issue;   // development only: cycles the issue + commit hold the thread
+                        mma_cnt++;
 #endif
                         acc.advance();
                     }
@@ -361,12 +364,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             for (int ks = 0; ks < k_stages; ks++) {
                 {
                     T_BEGIN();
-                    if (!mbar_wait_abortable(abort_flag, &raw_full[raw.idx], raw.phase, 64u)) INKQ_GIVE_UP();
+                    if (!mbar_wait_abortable(abort_flag, &raw_full[raw.idx], raw.phase, 200u)) INKQ_GIVE_UP();
                     T_ADD(0);
                 }
                 {
                     T_BEGIN();
-                    if (!mbar_wait_abortable(abort_flag, &u8_empty[u8.idx], u8.phase ^ 1, 64u)) INKQ_GIVE_UP();
+                    if (!mbar_wait_abortable(abort_flag, &u8_empty[u8.idx], u8.phase ^ 1, 500u)) INKQ_GIVE_UP();
                     T_ADD(1);
                 }
                 const int np = min(STAGE_PAIRS, prm.pairs - ks * STAGE_PAIRS);
@@ -440,24 +443,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 #pragma unroll
             for (int j = 0; j < CW / 2; j++) accp[j] = 0ull;
             uint32_t rbuf[2][CH];                 // the two chunk buffers
-            uint32_t taddr_blk = 0;               // TMEM address of the block whose chunks are being loaded
+            uint32_t taddr_pair = 0;              // TMEM address of the pair whose chunks are being loaded
             uint32_t acc_loading = 0;             // its slot in the accumulator ring
 
-            // waits for block `acc` of the ring to be computed and starts the load of its first chunk
-            auto begin_block = [&](uint32_t *dst) -> bool {
-                if (!mbar_wait_abortable(abort_flag, &acc_full[acc.idx], acc.phase, 32u, 8u)) return false;
+            // waits for the next pair of the ring to be computed and starts the load of its first chunk
+            auto begin_pair = [&](uint32_t *dst) -> bool {
+                T_BEGIN();
+                if (!mbar_wait_abortable(abort_flag, &acc_full[acc.idx], acc.phase, 0u)) return false;
+                T_ADD(1);
                 tc_fence_after_sync();
-                taddr_blk = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc.idx * ACC_COLS + col0;
+                taddr_pair = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc.idx * ACC_COLS + col0;
                 acc_loading = acc.idx;
                 acc.advance();
-                if (NCH == 1) tmem_ld_cols<CH_LAST>(taddr_blk, dst);
-                else tmem_ld_cols<CH>(taddr_blk, dst);
+                if (NCH == 1) tmem_ld_cols<CH_LAST>(taddr_pair, dst);
+                else tmem_ld_cols<CH>(taddr_pair, dst);
                 return true;
             };
-            // completes the outstanding load; when it was the block's last chunk, hands the TMEM buffer back
-            auto finish_load = [&](bool last_chunk_of_block) {
+            // completes the outstanding load; when it was the pair's last chunk, hands the TMEM slot back
+            auto finish_load = [&](bool last_chunk_of_pair) {
+                T_BEGIN();
                 tmem_ld_wait();
-                if (last_chunk_of_block) {
+                T_ADD(2);
+                if (last_chunk_of_pair) {
                     tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[acc_loading]);
@@ -473,9 +480,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 return make_float4(x0.x, x0.y, x1.x, x1.y);
             };
 
-            // pipeline prologue: first chunk of the tile's first block
-            if (!begin_block(rbuf[0])) INKQ_GIVE_UP();
-            finish_load(NCH == 1);
+            // pipeline prologue: first chunk of the tile's first pair
+            if (!begin_pair(rbuf[0])) INKQ_GIVE_UP();
+            finish_load(false);
             float4 wsc_next = load_wsc(0);
 
             for (int p = 0; p < prm.pairs && !dead; p++) {
@@ -483,64 +490,64 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 wsc_next = load_wsc(p + 1);
                 const int pj = p & (STAGE_PAIRS - 1);
                 if (pj == 0 && !DUMP) {
-                    if (!mbar_wait_abortable(abort_flag, &sc_full[sc.idx], sc.phase, 32u, 8u)) INKQ_GIVE_UP();
+                    T_BEGIN();
+                    if (!mbar_wait_abortable(abort_flag, &sc_full[sc.idx], sc.phase, 0u)) INKQ_GIVE_UP();
+                    T_ADD(0);
                 }
                 const float *sd_lo = reinterpret_cast<const float *>(sc_base + sc.idx * SC_STAGE_BYTES) + (2 * pj) * BLOCK_M + col0;
                 const float *ss_lo = sd_lo + SC_PLANE_BYTES / 4;   // s_a of the low block; the high block's follows
+                const uint32_t taddr_cur = taddr_pair;             // the pair being consumed (begin_pair below re-targets taddr_pair)
 #pragma unroll
-                for (int hi = 0; hi < 2; hi++) {   // the two blocks of the pair: low nibbles, then high nibbles
+                for (int it = 0; it < 2 * NCH; it++) {   // items of the pair: (low, chunks...), (high, chunks...)
+                    const int hi = it / NCH, c = it % NCH;
                     const int b = 2 * p + hi;
                     const float dw = hi ? wsc.y : wsc.x;
                     const float *sd = sd_lo + hi * BLOCK_M;          // d_a of this block
+                    // item `it` sits in rbuf[it & 1]; start the load of the item after it into the other buffer
+                    const int cur = it & 1, nxt = cur ^ 1;
+                    bool loading = false;
+                    if (it + 1 < 2 * NCH) {   // next chunk of the same pair
+                        const int nhi = (it + 1) / NCH, nc = (it + 1) % NCH;
+                        if (nc == NCH - 1) tmem_ld_cols<CH_LAST>(taddr_cur + nhi * 128 + nc * CH, rbuf[nxt]);
+                        else tmem_ld_cols<CH>(taddr_cur + nhi * 128 + nc * CH, rbuf[nxt]);
+                        loading = true;
+                    } else if (p + 1 < prm.pairs) {   // first chunk of the next pair
+                        if (!begin_pair(rbuf[nxt])) INKQ_GIVE_UP();
+                        loading = true;
+                    }
+                    const uint32_t *raw = rbuf[cur];
+                    const int ncols = (c == NCH - 1) ? CH_LAST : CH;
+                    if (DUMP) {
 #pragma unroll
-                    for (int c = 0; c < NCH; c++) {
-                        // item (b, c) sits in rbuf[cur]; start the load of the item after it into rbuf[nxt]
-                        const int cur = (hi * NCH + c) & 1, nxt = cur ^ 1;
-                        bool loading = false, loading_last = false;
-                        if (c + 1 < NCH) {   // next chunk of the same block
-                            tmem_ld_cols<CH_LAST>(taddr_blk + (c + 1) * CH, rbuf[nxt]);
-                            loading = true;
-                            loading_last = true;
-                        } else if (b + 1 < nbk) {   // first chunk of the next block
-                            if (!begin_block(rbuf[nxt])) INKQ_GIVE_UP();
-                            loading = true;
-                            loading_last = (NCH == 1);
+                        for (int j = 0; j < CH; j++) {
+                            const int m = tm * BLOCK_M + col0 + c * CH + j;
+                            if (j < ncols && m < prm.M && n < prm.rows)
+                                prm.dots[(static_cast<size_t>(m) * prm.rows + n) * nbk + b] = static_cast<int32_t>(raw[j]);
                         }
-                        const uint32_t *raw = rbuf[cur];
-                        const int ncols = (c == NCH - 1) ? CH_LAST : CH;
-                        if (DUMP) {
+                    } else {
 #pragma unroll
-                            for (int j = 0; j < CH; j++) {
-                                const int m = tm * BLOCK_M + col0 + c * CH + j;
-                                if (j < ncols && m < prm.M && n < prm.rows)
-                                    prm.dots[(static_cast<size_t>(m) * prm.rows + n) * nbk + b] = static_cast<int32_t>(raw[j]);
-                            }
-                        } else {
-#pragma unroll
-                            for (int j4 = 0; j4 < CH; j4 += 4) {
-                                if (j4 < ncols) {
-                                    const float4 da = *reinterpret_cast<const float4 *>(sd + c * CH + j4);
-                                    const unsigned long long dw2 = pack2(dw, dw);
-                                    const int a0 = (c * CH + j4) / 2;
-                                    accp[a0] = fma2(pack2(s32_to_f32_exact(raw[j4]), s32_to_f32_exact(raw[j4 + 1])), mul2(pack2(da.x, da.y), dw2),
-                                                    accp[a0]);
-                                    accp[a0 + 1] = fma2(pack2(s32_to_f32_exact(raw[j4 + 2]), s32_to_f32_exact(raw[j4 + 3])),
-                                                        mul2(pack2(da.z, da.w), dw2), accp[a0 + 1]);
-                                    if (HAS_MIN && hi) {
-                                        const float4 s0 = *reinterpret_cast<const float4 *>(ss_lo + c * CH + j4);
-                                        const float4 s1 = *reinterpret_cast<const float4 *>(ss_lo + BLOCK_M + c * CH + j4);
-                                        const unsigned long long mlo = pack2(wsc.z, wsc.z), mhi = pack2(wsc.w, wsc.w);
-                                        accp[a0] = fma2(mlo, pack2(s0.x, s0.y), accp[a0]);
-                                        accp[a0] = fma2(mhi, pack2(s1.x, s1.y), accp[a0]);
-                                        accp[a0 + 1] = fma2(mlo, pack2(s0.z, s0.w), accp[a0 + 1]);
-                                        accp[a0 + 1] = fma2(mhi, pack2(s1.z, s1.w), accp[a0 + 1]);
-                                    }
+                        for (int j4 = 0; j4 < CH; j4 += 4) {
+                            if (j4 < ncols) {
+                                const float4 da = *reinterpret_cast<const float4 *>(sd + c * CH + j4);
+                                const unsigned long long dw2 = pack2(dw, dw);
+                                const int a0 = (c * CH + j4) / 2;
+                                accp[a0] = fma2(pack2(s32_to_f32_exact(raw[j4]), s32_to_f32_exact(raw[j4 + 1])), mul2(pack2(da.x, da.y), dw2),
+                                                accp[a0]);
+                                accp[a0 + 1] = fma2(pack2(s32_to_f32_exact(raw[j4 + 2]), s32_to_f32_exact(raw[j4 + 3])), mul2(pack2(da.z, da.w), dw2),
+                                                    accp[a0 + 1]);
+                                if (HAS_MIN && hi) {
+                                    const float4 s0 = *reinterpret_cast<const float4 *>(ss_lo + c * CH + j4);
+                                    const float4 s1 = *reinterpret_cast<const float4 *>(ss_lo + BLOCK_M + c * CH + j4);
+                                    const unsigned long long mlo = pack2(wsc.z, wsc.z), mhi = pack2(wsc.w, wsc.w);
+                                    accp[a0] = fma2(mlo, pack2(s0.x, s0.y), accp[a0]);
+                                    accp[a0] = fma2(mhi, pack2(s1.x, s1.y), accp[a0]);
+                                    accp[a0 + 1] = fma2(mlo, pack2(s0.z, s0.w), accp[a0 + 1]);
+                                    accp[a0 + 1] = fma2(mhi, pack2(s1.z, s1.w), accp[a0 + 1]);
                                 }
                             }
                         }
-                        if (loading) finish_load(loading_last);
                     }
-                    if (dead) break;
+                    if (loading) finish_load(it + 1 == 2 * NCH - 1);
                 }
                 if (dead) break;
                 if (!DUMP && (pj == STAGE_PAIRS - 1 || p == prm.pairs - 1)) {
