@@ -108,6 +108,14 @@ int inkq_quantize(inkq_ctx *ctx, int qmode, const float *x_dev, int M, int K, in
  * (s = 0 for Q8_0), isum s32 [M][K/32] (block sums of q).  Any output may be NULL. */
 int inkq_act_export(inkq_ctx *ctx, const inkq_act *act, int8_t *q, float *d, float *s, int32_t *isum);
 
+/* inkq_quantize with x in host memory (copied to the device inside the call). */
+int inkq_quantize_host(inkq_ctx *ctx, int qmode, const float *x_host, int M, int K, inkq_act *act);
+/* Uploads an already quantized activation matrix (host arrays: q s8 [M][K], d f32 [M][K/32],
+ * s f32 [M][K/32] or NULL for Q8_0) into the handle, as if inkq_quantize had produced it.  Used
+ * by the reference-named host entry points, whose callers hand over the reference's own
+ * quantized structs (q8_repack_1x2_fp16/_fp32, QwenOperator.h:56-80). */
+int inkq_act_import(inkq_ctx *ctx, inkq_act *act, int qmode, int M, const int8_t *q, const float *d, const float *s);
+
 /* ---- matmuls ---------------------------------------------------------------
  * inkq_gemm  : tcgen05 int8 tensor-core path, any M >= 1. Replaces
  *              gemm_repack_A81W41_fp32 / gemm_repack_A80W40 (QwenOperator.h:280-298).
@@ -119,6 +127,11 @@ int inkq_act_export(inkq_ctx *ctx, const inkq_act *act, int8_t *q, float *d, flo
 int inkq_gemm(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, float *C_dev, int ldc);
 int inkq_gemv(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, float *C_dev);
 int inkq_gemm_simt(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, float *C_dev, int ldc);
+/* inkq_gemm / inkq_gemv with the result delivered to host memory (C_host fp32 [M][ldc]); the
+ * call returns when the copy is complete.  These are what the reference-named host functions
+ * gemm_repack_* / gemv_repack_* (QwenOperator.h:280-304) are built on. */
+int inkq_gemm_host(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, float *C_host, int ldc);
+int inkq_gemv_host(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, float *C_host);
 /* Every int32 block dot, dots_dev s32 [M][rows][K/32]; for bit-exactness checks. */
 int inkq_debug_block_dots(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, int32_t *dots_dev);
 /* As inkq_debug_block_dots but produced by the tensor-core kernel's own MMA path. */

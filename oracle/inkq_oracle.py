@@ -195,8 +195,13 @@ class Reference:
                 return p, isa
         return None, None
 
-    def __init__(self):
-        p, isa = self.available_path()
+    def __init__(self, path=None):
+        """path: any shared library exporting the reference's function names (e.g. the
+        GPU-backed drop-in built from qwen3.ink.cpp_b200/host/ref_names.cc); default: oracle/_ref."""
+        if path is not None:
+            p, isa = path, "custom"
+        else:
+            p, isa = self.available_path()
         if p is None:
             raise FileNotFoundError("oracle/_ref/libinkref_*.so not built (run `make -C oracle ref` where the "
                                     "reference checkout is present) or host ISA unsupported")

@@ -29,7 +29,7 @@ OK, ERR_INVALID, ERR_CUDA, ERR_ALLOC, ERR_UNSUPPORTED, ERR_TIMEOUT = range(6)
 SYMBOLS = [
     "inkq_ctx_create", "inkq_ctx_destroy", "inkq_ctx_set_stream", "inkq_ctx_synchronize", "inkq_last_error",
     "inkq_launch_count", "inkq_weight_create", "inkq_weight_create_dev", "inkq_weight_destroy", "inkq_weight_info",
-    "inkq_weight_export", "inkq_act_create", "inkq_act_destroy", "inkq_quantize", "inkq_act_export", "inkq_gemm",
+    "inkq_weight_export", "inkq_act_create", "inkq_act_destroy", "inkq_quantize", "inkq_act_export", "inkq_act_import", "inkq_quantize_host", "inkq_gemm_host", "inkq_gemv_host", "inkq_gemm",
     "inkq_gemv", "inkq_gemm_simt", "inkq_debug_block_dots", "inkq_debug_block_dots_tc", "inkq_linear",
     "inkq_linear_host", "inkq_linear_m1_static", "inkq_gemm_w41_f16act", "inkq_f16w_create", "inkq_f16w_create_dev", "inkq_f16w_destroy",
     "inkq_f16w_matmul",
@@ -156,6 +156,12 @@ class Context:
     # ---- kernels ------------------------------------------------------------------
     def quantize(self, act: "Act", x, M: int, qmode: int):
         self.check(self.L.inkq_quantize(self.h, qmode, _dp(x), M, act.K, act.h))
+
+    def act_import(self, act: "Act", qmode: int, q, d, s=None):
+        q = np.ascontiguousarray(q, np.int8)
+        d = np.ascontiguousarray(d, np.float32)
+        s = None if s is None else np.ascontiguousarray(s, np.float32)
+        self.check(self.L.inkq_act_import(self.h, act.h, qmode, q.shape[0], _hp(q), _hp(d), _hp(s)))
 
     def gemm(self, act, w, Cdev, ldc: int):
         self.check(self.L.inkq_gemm(self.h, act.h, w.h, _dp(Cdev), ldc))

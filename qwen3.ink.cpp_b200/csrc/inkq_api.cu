@@ -6,6 +6,7 @@
 
 #include <mutex>
 #include <new>
+#include <vector>
 
 #include "inkq_internal.h"
 
@@ -399,6 +400,65 @@ int inkq_act_export(inkq_ctx *ctx, const inkq_act *act, int8_t *q, float *d, flo
     return INKQ_OK;
 }
 
+static int ensure_staging(inkq_ctx *ctx, size_t xn, size_t cn)
+{
+    int rc;
+    if (ctx->lin_x_cap < xn) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaFree(ctx->lin_x);
+        ctx->lin_x_cap = 0;
+        if ((rc = dev_alloc(ctx, &ctx->lin_x, xn))) return rc;
+        ctx->lin_x_cap = xn;
+    }
+    if (ctx->lin_c_cap < cn) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaFree(ctx->lin_c);
+        ctx->lin_c_cap = 0;
+        if ((rc = dev_alloc(ctx, &ctx->lin_c, cn))) return rc;
+        ctx->lin_c_cap = cn;
+    }
+    return INKQ_OK;
+}
+
+int inkq_quantize_host(inkq_ctx *ctx, int qmode, const float *x_host, int M, int K, inkq_act *act)
+{
+    int rc = use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, x_host != nullptr && M >= 1 && K >= 1, "null input or bad shape");
+    const size_t xn = static_cast<size_t>(M) * K;
+    if ((rc = ensure_staging(ctx, xn, 0))) return rc;
+    INKQ_CUDA(ctx, cudaMemcpyAsync(ctx->lin_x, x_host, xn * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    return inkq_quantize(ctx, qmode, ctx->lin_x, M, K, act);
+}
+
+int inkq_act_import(inkq_ctx *ctx, inkq_act *act, int qmode, int M, const int8_t *q, const float *d, const float *s)
+{
+    int rc = use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, act != nullptr && q != nullptr && d != nullptr, "null activation handle or input");
+    INKQ_REQUIRE(ctx, qmode >= INKQ_Q8_0_F16 && qmode <= INKQ_Q8_1_F32, "unknown quantizer mode");
+    INKQ_REQUIRE(ctx, qmode == INKQ_Q8_0_F16 || s != nullptr, "Q8_1 activations need the scaled sums");
+    INKQ_REQUIRE(ctx, M >= 1 && M <= act->max_rows, "M exceeds the activation handle's capacity");
+    const size_t nb = static_cast<size_t>(act->K) / QK, ld = (static_cast<size_t>(M) + 3) & ~static_cast<size_t>(3);
+    // planes are block-major [nb][M_ld] on the device: transpose while staging (a layout change, no arithmetic);
+    // the integer block sums are recomputed from q on the device
+    std::vector<float> dp(nb * ld, 0.0f), sp(nb * ld, 0.0f);
+    for (size_t m = 0; m < static_cast<size_t>(M); m++)
+        for (size_t b = 0; b < nb; b++) {
+            dp[b * ld + m] = d[m * nb + b];
+            if (s != nullptr) sp[b * ld + m] = s[m * nb + b];
+        }
+    INKQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    INKQ_CUDA(ctx, cudaMemcpy(act->q, q, static_cast<size_t>(M) * act->K, cudaMemcpyHostToDevice));
+    INKQ_CUDA(ctx, cudaMemcpy(act->d, dp.data(), nb * ld * sizeof(float), cudaMemcpyHostToDevice));
+    INKQ_CUDA(ctx, cudaMemcpy(act->s, sp.data(), nb * ld * sizeof(float), cudaMemcpyHostToDevice));
+    if ((rc = launch_block_isum(ctx, act, M, static_cast<int>(ld)))) return rc;
+    act->M = M;
+    act->M_ld = static_cast<int>(ld);
+    act->qmode = qmode;
+    return INKQ_OK;
+}
+
 // ---- matmuls -----------------------------------------------------------------------
 static int check_mm(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, const void *C)
 {
@@ -437,6 +497,27 @@ int inkq_gemv(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, float *C
     if ((rc = check_mm(ctx, act, w, C_dev))) return rc;
     INKQ_REQUIRE(ctx, act->M == 1, "inkq_gemv takes a single activation row");
     return launch_gemv(ctx, act, w, C_dev);
+}
+
+static int matmul_host(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, float *C_host, int ldc, bool gemv)
+{
+    int rc = use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, act != nullptr && w != nullptr && C_host != nullptr, "null handle or output");
+    INKQ_REQUIRE(ctx, ldc >= w->rows, "ldc is smaller than the number of weight rows");
+    const size_t cn = static_cast<size_t>(act->M) * w->rows;
+    if ((rc = ensure_staging(ctx, 0, cn))) return rc;
+    rc = gemv ? inkq_gemv(ctx, act, w, ctx->lin_c) : inkq_gemm(ctx, act, w, ctx->lin_c, w->rows);
+    if (rc) return rc;
+    INKQ_CUDA(ctx, cudaMemcpy2DAsync(C_host, static_cast<size_t>(ldc) * sizeof(float), ctx->lin_c, static_cast<size_t>(w->rows) * sizeof(float),
+                                     static_cast<size_t>(w->rows) * sizeof(float), act->M, cudaMemcpyDeviceToHost, ctx->stream));
+    return inkq_ctx_synchronize(ctx);
+}
+
+int inkq_gemm_host(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, float *C_host, int ldc) { return matmul_host(ctx, act, w, C_host, ldc, false); }
+int inkq_gemv_host(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, float *C_host)
+{
+    return matmul_host(ctx, act, w, C_host, w != nullptr ? w->rows : 0, true);
 }
 
 int inkq_debug_block_dots(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, int32_t *dots_dev)
@@ -502,20 +583,7 @@ int inkq_linear_host(inkq_ctx *ctx, const inkq_weight *w, const float *x_host, i
     INKQ_REQUIRE(ctx, M >= 1, "M must be at least 1");
     INKQ_REQUIRE(ctx, ldc >= w->rows, "ldc is smaller than the number of weight rows");
     const size_t xn = static_cast<size_t>(M) * w->K, cn = static_cast<size_t>(M) * w->rows;
-    if (ctx->lin_x_cap < xn) {
-        cudaStreamSynchronize(ctx->stream);
-        cudaFree(ctx->lin_x);
-        ctx->lin_x_cap = 0;
-        if ((rc = dev_alloc(ctx, &ctx->lin_x, xn))) return rc;
-        ctx->lin_x_cap = xn;
-    }
-    if (ctx->lin_c_cap < cn) {
-        cudaStreamSynchronize(ctx->stream);
-        cudaFree(ctx->lin_c);
-        ctx->lin_c_cap = 0;
-        if ((rc = dev_alloc(ctx, &ctx->lin_c, cn))) return rc;
-        ctx->lin_c_cap = cn;
-    }
+    if ((rc = ensure_staging(ctx, xn, cn))) return rc;
     INKQ_CUDA(ctx, cudaMemcpyAsync(ctx->lin_x, x_host, xn * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
     if ((rc = inkq_linear(ctx, w, ctx->lin_x, M, ctx->lin_c, w->rows))) return rc;
     INKQ_CUDA(ctx, cudaMemcpy2DAsync(C_host, static_cast<size_t>(ldc) * sizeof(float), ctx->lin_c, static_cast<size_t>(w->rows) * sizeof(float),

@@ -149,6 +149,24 @@ __device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigne
     return r;
 }
 
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b)
+{
+    unsigned long long r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+// Two block dots -> packed fp32 pair, exactly.
+__device__ __forceinline__ unsigned long long cvt2_exact(uint32_t v0, uint32_t v1)
+{
+#if defined(INKQ_CVT_MAGIC2)
+    // integer add on the ALU pipe, one packed float add for both halves
+    return add2(pack2(__int_as_float(static_cast<int>(v0 + 0x4B400000u)), __int_as_float(static_cast<int>(v1 + 0x4B400000u))),
+                pack2(-12582912.0f, -12582912.0f));
+#else
+    return pack2(s32_to_f32_exact(v0), s32_to_f32_exact(v1));
+#endif
+}
+
 // Loads N consecutive TMEM columns of this thread's lane; N a multiple of 4 up to 16.
 template <int N>
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t *r)
@@ -531,9 +549,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                                 const float4 da = *reinterpret_cast<const float4 *>(sd + c * CH + j4);
                                 const unsigned long long dw2 = pack2(dw, dw);
                                 const int a0 = (c * CH + j4) / 2;
-                                accp[a0] = fma2(pack2(s32_to_f32_exact(raw[j4]), s32_to_f32_exact(raw[j4 + 1])), mul2(pack2(da.x, da.y), dw2),
+                                accp[a0] = fma2(cvt2_exact(raw[j4], raw[j4 + 1]), mul2(pack2(da.x, da.y), dw2),
                                                 accp[a0]);
-                                accp[a0 + 1] = fma2(pack2(s32_to_f32_exact(raw[j4 + 2]), s32_to_f32_exact(raw[j4 + 3])), mul2(pack2(da.z, da.w), dw2),
+                                accp[a0 + 1] = fma2(cvt2_exact(raw[j4 + 2], raw[j4 + 3]), mul2(pack2(da.z, da.w), dw2),
                                                     accp[a0 + 1]);
                                 if (HAS_MIN && hi) {
                                     const float4 s0 = *reinterpret_cast<const float4 *>(ss_lo + c * CH + j4);

@@ -75,6 +75,29 @@ __global__ void __launch_bounds__(256) k_quantize_q8(const float4 *__restrict__ 
     }
 }
 
+// Integer block sums of an imported (already quantized) activation matrix: isum[b][m] = sum_e q[m][32b+e].
+__global__ void __launch_bounds__(256) k_block_isum(const int8_t *__restrict__ q, int M, int K, int M_ld, int32_t *__restrict__ isum)
+{
+    const int nb = K / QK;
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<long long>(M_ld) * nb) return;
+    const int m = static_cast<int>(idx / nb), b = static_cast<int>(idx % nb);
+    int acc = 0;
+    if (m < M) {
+        const int *src = reinterpret_cast<const int *>(q + static_cast<size_t>(m) * K + static_cast<size_t>(b) * QK);
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc = __dp4a(src[i], 0x01010101, acc);
+    }
+    isum[static_cast<size_t>(b) * M_ld + m] = acc;
+}
+
+int launch_block_isum(inkq_ctx *ctx, Act *a, int M, int M_ld)
+{
+    const long long total = static_cast<long long>(M_ld) * (a->K / QK);
+    k_block_isum<<<static_cast<unsigned>((total + 255) / 256), 256, 0, ctx->stream>>>(a->q, M, a->K, M_ld, a->isum);
+    return after_launch(ctx, "k_block_isum");
+}
+
 int launch_quantize(inkq_ctx *ctx, int qmode, const float *x, int M, int K, Act *a)
 {
     const int M_ld = (M + 3) & ~3;

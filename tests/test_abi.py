@@ -54,3 +54,15 @@ def test_synth_nibble_packing_round_trip(pkg):
     # byte[32g+e] = q[64g+e] | q[64g+32+e] << 4  (notebooks/quantize_methods.py:120-123)
     assert nib[3, 32 + 5] == (q[3, 64 + 5] | (q[3, 64 + 32 + 5] << 4))
     assert np.array_equal(pkg.synth.unpack_nibbles(nib), q)
+
+
+def test_reference_named_shim_exports_the_reference_symbols(pkg):
+    """The GPU-backed drop-in exports the same (C++-mangled) names as the compiled reference."""
+    import ctypes
+    from oracle.inkq_oracle import Reference
+    pkg.build()
+    path = os.path.join(ROOT, "qwen3.ink.cpp_b200", "libinkq_refshim.so")
+    assert os.path.exists(path)
+    L = ctypes.CDLL(path)
+    for mangled in Reference.SYMS.values():
+        assert hasattr(L, mangled), mangled
