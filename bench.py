@@ -250,9 +250,8 @@ def run_ours(args, rank, world, local_rank):
     wl = args.workload
     M = {"qgemm_pp322": M_PP, "qgemm_m2048": 2048, "qgemm_m8192": 8192, "qgemv_sweep": M_PP}[wl]
     K, N = K_PP, N_PP
-    assert N % (world * 8) == 0
-    n_loc = N // world
-    n0, n1 = rank * n_loc, (rank + 1) * n_loc
+    n0, n1 = pkg.tp.shard_range(N, world, rank)
+    n_loc = n1 - n0
     x_host = pkg.synth.activations(M, K)
     wt = pkg.synth.weights(N, K)
 
@@ -262,9 +261,8 @@ def run_ours(args, rank, world, local_rank):
     ws = [ctx.weight(pkg.A81W41, pkg.SCALES_F32, wt["nib"], wt["d"], wt["m"], None, n0, n1) for _ in range(sets)]
     xs = [torch.from_numpy(x_host).cuda() for _ in range(sets)]
     if world > 1:
-        gathered = torch.empty((world, M, n_loc), device="cuda")        # all-gather target, rank-major
-        Cfull = torch.empty((M, N), device="cuda")
-        Cs = [gathered[rank]]
+        cg = pkg.tp.ColumnGather(dist, M, N, world, rank, "cuda", torch.float32)   # in-place all-gather target
+        Cs = [cg.local]
     else:
         Cs = [torch.empty((M, n_loc), device="cuda") for _ in range(2)]
 
@@ -273,8 +271,7 @@ def run_ours(args, rank, world, local_rank):
         C = Cs[i % len(Cs)]
         ctx.linear(w, xs[i % sets], M, C, n_loc)                        # quantizer + QGEMM (Qwen_Linear_with_bias_Int4::forward)
         if world > 1:
-            dist.all_gather_into_tensor(gathered.view(-1), gathered[rank].reshape(-1))
-            Cfull.view(M, world, n_loc).copy_(gathered.permute(1, 0, 2))  # [P][M][N/P] -> [M][N]
+            cg.gather()                                                 # NCCL all-gather + [P][M][N/P] -> [M][N]
 
     for i in range(args.warmup):
         step(i)

@@ -15,6 +15,7 @@ import numpy as np
 
 from . import build as _build
 from . import synth  # noqa: F401  (re-exported)
+from . import tp  # noqa: F401
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libinkq.so")

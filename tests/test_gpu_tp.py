@@ -1,0 +1,57 @@
+"""GPU, 2 ranks over NCCL (skipped on a single-GPU box): the column-sharded CUDA linear layer,
+gathered, equals the unsharded 1-GPU result bit for bit."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+from conftest import ROOT
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    ctx = pkg.Context(rank, torch.cuda.current_stream().cuda_stream)
+    M, N, K = 322, 2048, 512
+    x = torch.from_numpy(pkg.synth.activations(M, K, 8)).cuda()
+    w = pkg.synth.weights(N, K, 8)
+    n0, n1 = pkg.tp.shard_range(N, world, rank)
+    wh = ctx.weight(pkg.A81W41, pkg.SCALES_F32, w["nib"], w["d"], w["m"], None, n0, n1)
+    cg = pkg.tp.ColumnGather(dist, M, N, world, rank, "cuda", torch.float32)
+    ctx.linear(wh, x, M, cg.local, n1 - n0)
+    full = cg.gather()
+    whole = ctx.weight(pkg.A81W41, pkg.SCALES_F32, w["nib"], w["d"], w["m"])
+    ref = torch.empty((M, N), device="cuda")
+    ctx.linear(whole, x, M, ref, N)
+    ctx.synchronize()
+    ok = bool(torch.equal(full, ref))
+    with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+        f.write("ok" if ok else "mismatch")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_shards_equal_single_gpu(tmp_path):
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        assert open(tmp_path / f"rank{r}.txt").read() == "ok"
