@@ -5,17 +5,18 @@
 // follows the same order with q_w = nibble - zp.  Scales are the fp16-rounded ones,
 // as in those reference kernels.
 //
-// Work split: a CTA owns 32 consecutive weight rows (lane = row) and its 8 warps
-// own 8 contiguous K-slices.  For one pair (64 K-elements) a warp reads 32 rows x
+// Work split: a CTA owns 32 consecutive weight rows (lane = row) and its 8 or 16 warps
+// own as many contiguous K-slices.  For one pair (64 K-elements) a warp reads 32 rows x
 // 32 bytes = 1 KB contiguous with two 128-bit loads per lane, plus 8 bytes of
-// fp16 {d_lo, d_hi, m_lo, m_hi} per lane.  Four pairs are in flight per lane
-// (8 x 128-bit loads) before any is consumed.  The activation row (int8 + block
-// scales) is staged once per CTA in shared memory and read as broadcasts.
+// fp16 {d_lo, d_hi, m_lo, m_hi} per lane.  Two batches of two pairs (8 x 128-bit loads)
+// are in flight per lane, the first two issued before the activation row (int8 + block
+// scales) is staged in shared memory, so that staging hides behind the weight latency.
 //
 // Reduction order (fixed, documented): inside a K-slice the reference's order is
 // kept exactly - per pair fma(I_lo, d_a*d_w), fma(I_hi, ...), fma(m_lo, s_lo),
-// fma(m_hi, s_hi), pairs ascending from a zero accumulator; the 8 slice partials
-// are then added in ascending slice order ((p0 + p1) + p2) ... + p7.  Every int32
+// fma(m_hi, s_hi), pairs ascending from a zero accumulator; the slice partials
+// are then added in ascending slice order ((p0 + p1) + p2) + ...  (8 slices, or 16 for
+// narrow or long-row layers: the choice depends only on the layer's shape).  Every int32
 // block dot is exact.
 //
 // Algorithmic bytes per launch: rows*K/2 nibbles + rows*(K/32)*4 scale bytes
@@ -28,8 +29,7 @@
 
 namespace inkq {
 
-constexpr int GEMV_WARPS = 8;
-constexpr int GEMV_UNROLL = 4;
+constexpr int GEMV_UNROLL = 2;   // pairs per batch; two batches are in flight per lane
 
 __device__ __forceinline__ void dots_of_pair(const uint4 c0, const uint4 c1, const uint32_t *__restrict__ a_lo,
                                              const uint32_t *__restrict__ a_hi, int &ilo, int &ihi)
@@ -44,8 +44,64 @@ __device__ __forceinline__ void dots_of_pair(const uint4 c0, const uint4 c1, con
     }
 }
 
+// One batch of GEMV_UNROLL pairs of this lane's row, as loaded.
+struct PairBatch {
+    uint4 ca[GEMV_UNROLL], cb[GEMV_UNROLL];
+    uint2 sc[GEMV_UNROLL];
+    uchar2 z[GEMV_UNROLL];
+};
+
 template <bool HAS_MIN>
-__global__ void __launch_bounds__(GEMV_WARPS * 32) k_qgemv_a8w4(const uint8_t *__restrict__ nibT, const uint2 *__restrict__ sc16,
+__device__ __forceinline__ void load_batch(PairBatch &b, const uint8_t *__restrict__ nibT, const uint2 *__restrict__ sc16,
+                                           const uchar2 *__restrict__ zpT, size_t slab, int r, int p0, int p_end)
+{
+#pragma unroll
+    for (int u = 0; u < GEMV_UNROLL; u++) {
+        const int p = min(p0 + u, p_end - 1);  // clamped duplicates are loaded but never used
+        const size_t rec = (slab + p) * TILE_N + r;
+        const uint8_t *src = nibT + rec * 32;
+        b.ca[u] = ldg_stream_v4(src);
+        b.cb[u] = ldg_stream_v4(src + 16);
+        b.sc[u] = ldg_stream_v2(sc16 + rec);
+        if (!HAS_MIN) b.z[u] = zpT[rec];
+    }
+}
+
+template <bool HAS_MIN>
+__device__ __forceinline__ float consume_batch(const PairBatch &b, float acc, bool swz, const uint32_t *__restrict__ qa, const float *__restrict__ da,
+                                               const float *__restrict__ sa, int p0, int p_end)
+{
+#pragma unroll
+    for (int u = 0; u < GEMV_UNROLL; u++) {
+        const int p = p0 + u;
+        if (p < p_end) {
+            int ilo, ihi;
+            dots_of_pair(swz ? b.cb[u] : b.ca[u], swz ? b.ca[u] : b.cb[u], qa + p * 16, qa + p * 16 + 8, ilo, ihi);
+            const float2 dw = __half22float2(*reinterpret_cast<const __half2 *>(&b.sc[u].x));
+            const float da_lo = da[2 * p], da_hi = da[2 * p + 1];
+            if (HAS_MIN) {
+                const float2 mw = __half22float2(*reinterpret_cast<const __half2 *>(&b.sc[u].y));
+                acc = fmaf(static_cast<float>(ilo), __fmul_rn(da_lo, dw.x), acc);
+                acc = fmaf(static_cast<float>(ihi), __fmul_rn(da_hi, dw.y), acc);
+                acc = fmaf(mw.x, sa[2 * p], acc);
+                acc = fmaf(mw.y, sa[2 * p + 1], acc);
+            } else {
+                const int32_t *is = reinterpret_cast<const int32_t *>(sa);
+                ilo -= static_cast<int>(b.z[u].x) * is[2 * p];
+                ihi -= static_cast<int>(b.z[u].y) * is[2 * p + 1];
+                acc = fmaf(static_cast<float>(ilo), __fmul_rn(da_lo, dw.x), acc);
+                acc = fmaf(static_cast<float>(ihi), __fmul_rn(da_hi, dw.y), acc);
+            }
+        }
+    }
+    return acc;
+}
+
+// WARPS = K-slices per CTA: 8 for wide layers, 16 for narrow ones (more bytes in flight per SM when
+// the grid alone cannot fill the machine).  The register budget keeps 3 (resp. 2) CTAs per SM resident so
+// that every Qwen3-8B shape runs as a single wave.
+template <bool HAS_MIN, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_a8w4(const uint8_t *__restrict__ nibT, const uint2 *__restrict__ sc16,
                                                                const uchar2 *__restrict__ zpT, const int8_t *__restrict__ q,
                                                                const float *__restrict__ d, const float *__restrict__ s,
                                                                const int32_t *__restrict__ isum, int M_ld, float *__restrict__ C,
@@ -56,7 +112,20 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) k_qgemv_a8w4(const uint8_t *_
     uint32_t *qa = reinterpret_cast<uint32_t *>(smem_raw);          // K/4 words
     float *da = reinterpret_cast<float *>(smem_raw + K);            // nb
     float *sa = da + nb;                                            // nb (sums, or integer sums for the A80 schemes)
-    float *part = sa + nb;                                          // [GEMV_WARPS][32]
+    float *part = sa + nb;                                          // [WARPS][32]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x >> 2;
+    const int r = ((blockIdx.x & 3) << 5) + lane;
+    const bool swz = ((r >> 2) & 1) != 0;
+    const int p_begin = (warp * pairs) / WARPS, p_end = ((warp + 1) * pairs) / WARPS;
+    const size_t slab = static_cast<size_t>(t) * pairs;
+
+    // The weight stream does not depend on the activations: put the first two batches in flight
+    // before anything else, so the staging of the activation row hides behind their latency.
+    PairBatch b0, b1;
+    if (p_begin < p_end) load_batch<HAS_MIN>(b0, nibT, sc16, zpT, slab, r, p_begin, p_end);
+    if (p_begin + GEMV_UNROLL < p_end) load_batch<HAS_MIN>(b1, nibT, sc16, zpT, slab, r, p_begin + GEMV_UNROLL, p_end);
 
     for (int i = threadIdx.x; i < K / 16; i += blockDim.x)
         reinterpret_cast<uint4 *>(qa)[i] = reinterpret_cast<const uint4 *>(q)[i];
@@ -67,50 +136,14 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) k_qgemv_a8w4(const uint8_t *_
     }
     __syncthreads();
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x >> 2;
-    const int r = ((blockIdx.x & 3) << 5) + lane;
-    const bool swz = ((r >> 2) & 1) != 0;
-    const int p_begin = (warp * pairs) / GEMV_WARPS, p_end = ((warp + 1) * pairs) / GEMV_WARPS;
-    const size_t slab = static_cast<size_t>(t) * pairs;
+    // two batches per trip: while one is consumed the other (and its successor) are in flight
     float acc = 0.0f;
-
-    for (int p0 = p_begin; p0 < p_end; p0 += GEMV_UNROLL) {
-        uint4 ca[GEMV_UNROLL], cb[GEMV_UNROLL];
-        uint2 sc[GEMV_UNROLL];
-        uchar2 z[GEMV_UNROLL];
-#pragma unroll
-        for (int u = 0; u < GEMV_UNROLL; u++) {
-            const int p = min(p0 + u, p_end - 1);  // clamped duplicates are loaded but never used
-            const size_t rec = (slab + p) * TILE_N + r;
-            const uint8_t *src = nibT + rec * 32;
-            ca[u] = ldg_stream_v4(src);
-            cb[u] = ldg_stream_v4(src + 16);
-            sc[u] = ldg_stream_v2(sc16 + rec);
-            if (!HAS_MIN) z[u] = zpT[rec];
-        }
-#pragma unroll
-        for (int u = 0; u < GEMV_UNROLL; u++) {
-            const int p = p0 + u;
-            if (p < p_end) {
-                int ilo, ihi;
-                dots_of_pair(swz ? cb[u] : ca[u], swz ? ca[u] : cb[u], qa + p * 16, qa + p * 16 + 8, ilo, ihi);
-                const float2 dw = __half22float2(*reinterpret_cast<const __half2 *>(&sc[u].x));
-                const float da_lo = da[2 * p], da_hi = da[2 * p + 1];
-                if (HAS_MIN) {
-                    const float2 mw = __half22float2(*reinterpret_cast<const __half2 *>(&sc[u].y));
-                    acc = fmaf(static_cast<float>(ilo), __fmul_rn(da_lo, dw.x), acc);
-                    acc = fmaf(static_cast<float>(ihi), __fmul_rn(da_hi, dw.y), acc);
-                    acc = fmaf(mw.x, sa[2 * p], acc);
-                    acc = fmaf(mw.y, sa[2 * p + 1], acc);
-                } else {
-                    const int32_t *is = reinterpret_cast<const int32_t *>(sa);
-                    ilo -= static_cast<int>(z[u].x) * is[2 * p];
-                    ihi -= static_cast<int>(z[u].y) * is[2 * p + 1];
-                    acc = fmaf(static_cast<float>(ilo), __fmul_rn(da_lo, dw.x), acc);
-                    acc = fmaf(static_cast<float>(ihi), __fmul_rn(da_hi, dw.y), acc);
-                }
-            }
+    for (int p0 = p_begin; p0 < p_end; p0 += 2 * GEMV_UNROLL) {
+        acc = consume_batch<HAS_MIN>(b0, acc, swz, qa, da, sa, p0, p_end);
+        if (p0 + 2 * GEMV_UNROLL < p_end) load_batch<HAS_MIN>(b0, nibT, sc16, zpT, slab, r, p0 + 2 * GEMV_UNROLL, p_end);
+        if (p0 + GEMV_UNROLL < p_end) {
+            acc = consume_batch<HAS_MIN>(b1, acc, swz, qa, da, sa, p0 + GEMV_UNROLL, p_end);
+            if (p0 + 3 * GEMV_UNROLL < p_end) load_batch<HAS_MIN>(b1, nibT, sc16, zpT, slab, r, p0 + 3 * GEMV_UNROLL, p_end);
         }
     }
     part[warp * 32 + lane] = acc;
@@ -118,26 +151,31 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) k_qgemv_a8w4(const uint8_t *_
     if (warp == 0) {
         float tot = part[lane];
 #pragma unroll
-        for (int w2 = 1; w2 < GEMV_WARPS; w2++) tot = __fadd_rn(tot, part[w2 * 32 + lane]);
+        for (int w2 = 1; w2 < WARPS; w2++) tot = __fadd_rn(tot, part[w2 * 32 + lane]);
         const int n = t * TILE_N + r;
         if (n < rows) C[n] = tot;
     }
 }
 
+template <bool HAS_MIN, int WARPS>
+static void launch_gemv_variant(inkq_ctx *ctx, const Act *a, const Weight *w, float *C)
+{
+    const size_t smem = static_cast<size_t>(w->K) + 2 * sizeof(float) * (w->K / QK) + sizeof(float) * WARPS * 32;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k_qgemv_a8w4<HAS_MIN, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    k_qgemv_a8w4<HAS_MIN, WARPS><<<static_cast<unsigned>(w->tiles) * 4, WARPS * 32, smem, ctx->stream>>>(w->nibT, w->sc16, w->zpT, a->q, a->d, a->s, a->isum,
+                                                                                                        a->M_ld, C, w->rows, w->K, w->pairs);
+}
+
 int launch_gemv(inkq_ctx *ctx, const Act *a, const Weight *w, float *C)
 {
-    const size_t smem = static_cast<size_t>(w->K) + 2 * sizeof(float) * (w->K / QK) + sizeof(float) * GEMV_WARPS * 32;
-    const unsigned grid = static_cast<unsigned>(w->tiles) * 4;
+    // narrow layers (few CTAs) or long rows: 16 K-slices per CTA
+    const bool wide_cta = (w->tiles * 4 <= 2 * ctx->num_sms) || (w->pairs >= 128);
     if (w->scheme == INKQ_A81W41) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(k_qgemv_a8w4<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        k_qgemv_a8w4<true><<<grid, GEMV_WARPS * 32, smem, ctx->stream>>>(w->nibT, w->sc16, w->zpT, a->q, a->d, a->s, a->isum, a->M_ld, C,
-                                                                          w->rows, w->K, w->pairs);
+        if (wide_cta) launch_gemv_variant<true, 16>(ctx, a, w, C);
+        else launch_gemv_variant<true, 8>(ctx, a, w, C);
     } else {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(k_qgemv_a8w4<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        k_qgemv_a8w4<false><<<grid, GEMV_WARPS * 32, smem, ctx->stream>>>(w->nibT, w->sc16, w->zpT, a->q, a->d, a->s, a->isum, a->M_ld, C,
-                                                                           w->rows, w->K, w->pairs);
+        if (wide_cta) launch_gemv_variant<false, 16>(ctx, a, w, C);
+        else launch_gemv_variant<false, 8>(ctx, a, w, C);
     }
     return after_launch(ctx, "k_qgemv_a8w4");
 }
