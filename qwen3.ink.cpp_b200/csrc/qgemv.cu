@@ -126,6 +126,12 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_a8w4(c
     PairBatch b0, b1;
     if (p_begin < p_end) load_batch<HAS_MIN>(b0, nibT, sc16, zpT, slab, r, p_begin, p_end);
     if (p_begin + GEMV_UNROLL < p_end) load_batch<HAS_MIN>(b1, nibT, sc16, zpT, slab, r, p_begin + GEMV_UNROLL, p_end);
+    // Programmatic dependent launch: this grid may have started while its predecessor in the stream
+    // (normally the quantizer that produces q, d, s) was still running.  The weights above are
+    // independent of it; everything below is not, so wait for the predecessor to complete here, and
+    // let the successor start its own weight prefetch right away.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     for (int i = threadIdx.x; i < K / 16; i += blockDim.x)
         reinterpret_cast<uint4 *>(qa)[i] = reinterpret_cast<const uint4 *>(q)[i];
@@ -162,8 +168,21 @@ static void launch_gemv_variant(inkq_ctx *ctx, const Act *a, const Weight *w, fl
 {
     const size_t smem = static_cast<size_t>(w->K) + 2 * sizeof(float) * (w->K / QK) + sizeof(float) * WARPS * 32;
     if (smem > 48 * 1024) cudaFuncSetAttribute(k_qgemv_a8w4<HAS_MIN, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    k_qgemv_a8w4<HAS_MIN, WARPS><<<static_cast<unsigned>(w->tiles) * 4, WARPS * 32, smem, ctx->stream>>>(w->nibT, w->sc16, w->zpT, a->q, a->d, a->s, a->isum,
-                                                                                                        a->M_ld, C, w->rows, w->K, w->pairs);
+    // launched with programmatic stream serialization: the grid may begin (and prefetch weights) before the
+    // previous kernel in the stream has finished; it waits for that kernel inside (griddepcontrol.wait)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(w->tiles) * 4);
+    cfg.blockDim = dim3(WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, k_qgemv_a8w4<HAS_MIN, WARPS>, static_cast<const uint8_t *>(w->nibT), static_cast<const uint2 *>(w->sc16),
+                       static_cast<const uchar2 *>(w->zpT), static_cast<const int8_t *>(a->q), static_cast<const float *>(a->d),
+                       static_cast<const float *>(a->s), static_cast<const int32_t *>(a->isum), a->M_ld, C, w->rows, w->K, w->pairs);
 }
 
 int launch_gemv(inkq_ctx *ctx, const Act *a, const Weight *w, float *C)

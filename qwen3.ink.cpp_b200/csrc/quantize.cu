@@ -23,6 +23,9 @@ __global__ void __launch_bounds__(256) k_quantize_q8(const float4 *__restrict__ 
                                                      int8_t *__restrict__ q, float *__restrict__ d, float *__restrict__ s,
                                                      int32_t *__restrict__ isum)
 {
+    // lets a dependent kernel launched with programmatic stream serialization (the decode QGEMV) start
+    // its weight prefetch while this grid runs; it still waits for this grid's completion before reading
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int nb = K / QK;
     const long long gthread = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     const long long blk = gthread >> 3;  // global block index over [M_ld][nb]
