@@ -9,15 +9,26 @@
 // Both divisions are IEEE round-to-nearest, the product x*id is a plain fp32
 // multiply (never contracted), the rounding is to nearest-even.
 //
-// Mapping: 8 lanes own one block (one float4 each, 128 contiguous bytes), so a
-// warp covers 4 consecutive blocks with one coalesced 512-byte read; max and sum
-// are 3-step xor-shuffles inside the 8-lane group.  HBM-bound: 4 bytes read and
-// 1.375 bytes written per element.
+// Mapping: 2 lanes own one block (four interleaved float4 each), so the two IEEE
+// divisions are done twice per block, not eight times, four 128-bit loads are in
+// flight per lane and every load instruction of a warp touches whole 32-byte
+// sectors; max and sum need one xor-shuffle.  HBM-bound: 4 bytes read and 1.375
+// bytes written per element.
 #include <cuda_fp16.h>
 
 #include "inkq_internal.h"
 
 namespace inkq {
+
+__device__ __forceinline__ uint32_t pack_sat_s8x4(int a, int b, int c, int d)
+{
+    // two cvt.pack instructions: saturate four s32 to s8 and pack them into one word (a in the low byte).
+    // cvt.pack d, x, y, z gives (z << 16) | (sat(x) << 8) | sat(y).
+    uint32_t hi, out;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(d), "r"(c), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(b), "r"(a), "r"(hi));
+    return out;
+}
 
 __global__ void __launch_bounds__(256) k_quantize_q8(const float4 *__restrict__ x, int M, int K, int M_ld, int mode,
                                                      int8_t *__restrict__ q, float *__restrict__ d, float *__restrict__ s,
@@ -28,44 +39,50 @@ __global__ void __launch_bounds__(256) k_quantize_q8(const float4 *__restrict__ 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int nb = K / QK;
     const long long gthread = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    const long long blk = gthread >> 3;  // global block index over [M_ld][nb]
-    const int sub = threadIdx.x & 7;
-    const unsigned gmask = 0xffu << (threadIdx.x & 24);  // the 8 lanes of this block
-    if (blk >= static_cast<long long>(M_ld) * nb) return;  // whole 8-lane groups leave together
-    const int m = static_cast<int>(blk / nb);
-    const int b = static_cast<int>(blk % nb);
+    const long long blk = gthread >> 1;  // global block index over [M_ld][nb]; two lanes per block
+    const int half = threadIdx.x & 1;
+    const unsigned gmask = 0x3u << (threadIdx.x & 30);  // the two lanes of this block
+    if (blk >= static_cast<long long>(M_ld) * nb) return;  // both lanes of a block leave together
+    // consecutive lane pairs take consecutive rows m of the same block column b: the scale planes are
+    // [nb][M_ld], so a warp writes 16 consecutive entries of each plane (64 contiguous bytes) instead of
+    // 16 scattered words, and still reads one full 128-byte line of x per pair
+    const int b = static_cast<int>(blk / M_ld);
+    const int m = static_cast<int>(blk % M_ld);
     const size_t plane = static_cast<size_t>(b) * M_ld + m;
     if (m >= M) {  // padding rows of the scale planes read as zero
-        if (sub == 0) {
+        if (half == 0) {
             d[plane] = 0.0f;
             s[plane] = 0.0f;
             isum[plane] = 0;
         }
         return;
     }
-    const float4 v = x[(static_cast<size_t>(m) * K + static_cast<size_t>(b) * QK) / 4 + sub];
-    float mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-    // the 8 lanes of a block are aligned inside the warp: xor 1, 2, 4 stays in the group,
-    // and a group always takes the same branches, so the group mask is exact
+    // lane `half` takes the float4s 2j + half of the block: each load instruction of the warp touches
+    // 16 blocks x 32 contiguous bytes (whole sectors), four loads in flight per lane
+    const float4 *src = x + (static_cast<size_t>(m) * K + static_cast<size_t>(b) * QK) / 4 + half;
+    float4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) v[j] = src[2 * j];
+    float mx = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
+    // the two lanes of a block always take the same branches, so the pair mask is exact
     mx = fmaxf(mx, __shfl_xor_sync(gmask, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(gmask, mx, 2));
-    mx = fmaxf(mx, __shfl_xor_sync(gmask, mx, 4));
     const float dd = __fdiv_rn(mx, 127.0f);
     const float id = (mx != 0.0f) ? __fdiv_rn(127.0f, mx) : 0.0f;
-    const int i0 = __float2int_rn(__fmul_rn(v.x, id));
-    const int i1 = __float2int_rn(__fmul_rn(v.y, id));
-    const int i2 = __float2int_rn(__fmul_rn(v.z, id));
-    const int i3 = __float2int_rn(__fmul_rn(v.w, id));
-    int sum = (i0 + i1) + (i2 + i3);
+    int sum = 0;
+    uint32_t *dst = reinterpret_cast<uint32_t *>(q) + (static_cast<size_t>(m) * K + static_cast<size_t>(b) * QK) / 4 + half;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int i0 = __float2int_rn(__fmul_rn(v[j].x, id));
+        const int i1 = __float2int_rn(__fmul_rn(v[j].y, id));
+        const int i2 = __float2int_rn(__fmul_rn(v[j].z, id));
+        const int i3 = __float2int_rn(__fmul_rn(v[j].w, id));
+        sum += (i0 + i1) + (i2 + i3);   // the unsaturated values, as the reference sums them before packing
+        dst[2 * j] = pack_sat_s8x4(i0, i1, i2, i3);
+    }
     sum += __shfl_xor_sync(gmask, sum, 1);
-    sum += __shfl_xor_sync(gmask, sum, 2);
-    sum += __shfl_xor_sync(gmask, sum, 4);
-    const int c0 = max(-128, min(127, i0)), c1 = max(-128, min(127, i1));
-    const int c2 = max(-128, min(127, i2)), c3 = max(-128, min(127, i3));
-    const uint32_t packed = (static_cast<uint32_t>(c0) & 0xffu) | ((static_cast<uint32_t>(c1) & 0xffu) << 8) |
-                            ((static_cast<uint32_t>(c2) & 0xffu) << 16) | ((static_cast<uint32_t>(c3) & 0xffu) << 24);
-    reinterpret_cast<uint32_t *>(q)[(static_cast<size_t>(m) * K + static_cast<size_t>(b) * QK) / 4 + sub] = packed;
-    if (sub == 0) {
+    if (half == 0) {
         const float ss = __fmul_rn(dd, static_cast<float>(sum));
         if (mode == INKQ_Q8_1_F32) {
             d[plane] = dd;
@@ -104,7 +121,7 @@ int launch_block_isum(inkq_ctx *ctx, Act *a, int M, int M_ld)
 int launch_quantize(inkq_ctx *ctx, int qmode, const float *x, int M, int K, Act *a)
 {
     const int M_ld = (M + 3) & ~3;
-    const long long threads = static_cast<long long>(M_ld) * (K / QK) * 8;
+    const long long threads = static_cast<long long>(M_ld) * (K / QK) * 2;
     const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
     k_quantize_q8<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<const float4 *>(x), M, K, M_ld, qmode, a->q, a->d, a->s, a->isum);
     a->M = M;
