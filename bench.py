@@ -235,6 +235,48 @@ def gemv_sweep(pkg, torch, ctx, peak_gbs, iters=200):
     return out
 
 
+# --------------------------------------------------------------------------- synthetic Qwen3-8B forward (pp322 / tg128)
+def model_pp_tg(pkg, torch, ctx, prompt_len=322, new_tokens=128, reps=3):
+    """Prompt prefill and greedy decode of the synthetic Qwen3-8B (random-init A81W41 weights with fp16 block
+    scales, fp16 lm_head, fp16 KV cache), activations resident on the GPU.  pp = prompt tokens / prefill time,
+    tg = generated tokens / time of the decode steps (one captured CUDA graph replayed per token)."""
+    cfg = pkg.qwen3_forward.Qwen3Config(max_pos=prompt_len + new_tokens + 32)
+    model = pkg.qwen3_forward.Qwen3Synthetic(pkg, ctx, cfg, seed=7)
+    prompt = torch.from_numpy(pkg.synth.tokens(prompt_len, cfg.vocab)).cuda()
+    model.reset()
+    model.prefill(prompt)
+    model.decode_step()
+    model.capture_decode()
+    torch.cuda.synchronize()
+    pp_ms, tg_ms = [], []
+    for _ in range(reps):
+        model.reset()
+        a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        a.record()
+        model.prefill(prompt)
+        b.record()
+        for _ in range(new_tokens):
+            model.graph.replay()
+        c.record()
+        torch.cuda.synchronize()
+        pp_ms.append(a.elapsed_time(b))
+        tg_ms.append(b.elapsed_time(c))
+    n_gen = len(model.generated_tokens())
+    pp, tg = prompt_len / (min(pp_ms) * 1e-3), new_tokens / (min(tg_ms) * 1e-3)
+    w_bytes = cfg.layers * ((cfg.nq + 2 * cfg.nkv) * 128 * cfg.hidden + cfg.hidden * cfg.nq * 128 + 3 * cfg.hidden * cfg.ffn) * 0.625 \
+        + cfg.vocab * cfg.hidden * 2
+    out = {"pp322_tok_s": pp, "tg128_tok_s": tg, "prefill_ms": min(pp_ms), "decode_ms_per_token": min(tg_ms) / new_tokens,
+           "tokens_generated_last_rep": int(n_gen), "decode_weight_bytes_per_token": w_bytes,
+           "decode_GBs": w_bytes / (min(tg_ms) / new_tokens * 1e-3) / 1e9,
+           "published_reference_cpu": {"pp322_tok_s": 134.35, "tg128_tok_s": 9.26, "hardware": "Intel i5-13600KF, 16 threads (reference README)"},
+           "vs_published": {"pp322": pp / 134.35, "tg128": tg / 9.26},
+           "config": "Qwen3-8B shape: 36 layers, hidden 4096, 32q/8kv heads x128, ffn 12288, vocab 151936; A81W41 fp16 scales, fp16 lm_head and KV cache; "
+                     "synthetic weights and tokens"}
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
 # --------------------------------------------------------------------------- our arm
 def run_ours(args, rank, world, local_rank):
     import torch
@@ -347,6 +389,11 @@ def run_ours(args, rank, world, local_rank):
                 h.close()
             ws = []
             line["gemv"] = gemv_sweep(pkg, torch, ctx, pk["hbm_gbs"])
+        if world == 1 and args.model:
+            try:
+                line["model"] = model_pp_tg(pkg, torch, ctx)
+            except Exception as e:   # the headline metric above stands on its own
+                line["model"] = {"error": repr(e)[:300]}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -361,6 +408,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="qgemm_pp322", choices=["qgemm_pp322", "qgemv_sweep", "qgemm_m2048", "qgemm_m8192"])
     ap.add_argument("--no-gemv", dest="gemv", action="store_false", help="skip the decode QGEMV sweep figures")
+    ap.add_argument("--no-model", dest="model", action="store_false", help="skip the synthetic Qwen3-8B pp322/tg128 figures")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
     rank = int(os.environ.get("RANK", "0"))

@@ -1,0 +1,49 @@
+/*
+ * inkq_glue.h - device-resident stand-ins for the operators between the quantized linear
+ * layers of a Qwen3 decoder (C ABI, same conventions as inkq.h).
+ *
+ * They exist so that a whole synthetic Qwen3-8B forward can be timed with its activations on
+ * the GPU (prompt prefill + greedy decode); they are simple and correct, not tuned, and they
+ * are not part of the quantized-matmul path itself.  Each cites the reference code whose
+ * behaviour it follows.  Activations are fp32 row-major [tokens][features]; `pos0_dev` points
+ * to the position of the call's first token in device memory, so a captured CUDA graph of one
+ * decode step can be replayed for every step.
+ */
+#ifndef INKQ_GLUE_H
+#define INKQ_GLUE_H
+
+#include "inkq.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* out[t][:] = table[tokens[t]][:]  (fp16 table).  qwen3/src/ops/embedding.cc:11-26 */
+int inkq_glue_embedding(inkq_ctx *ctx, const uint16_t *table16_dev, const int *tokens_dev, int T, int dim, float *out_dev);
+/* y = x * rsqrt(mean(x^2) + eps) * w per row.  Qwen3RMSNorm::forward, qwen3/src/qwen/QwenOperator.cc:24-53 */
+int inkq_glue_rmsnorm(inkq_ctx *ctx, const float *x_dev, const float *w_dev, int rows, int dim, float eps, float *y_dev);
+/* Fused qkv output [T][(nq + 2 nkv) * 128] -> per-head RMSNorm of q and k, RoPE (rotate-half form,
+ * cos/sin tables [max_pos][128]) at positions pos0 + t, q to q_out [T][nq][128] fp32, k and v
+ * appended to the fp16 caches [nkv][max_pos][128].  qwen3/src/qwen/QwenAttention.cc:78-121,
+ * qwen3/src/ops/RotaryPosEmb.cc:6-79 */
+int inkq_glue_qknorm_rope_cache(inkq_ctx *ctx, const float *qkv_dev, const float *q_norm_w, const float *k_norm_w, const float *cos_dev,
+                                const float *sin_dev, const int *pos0_dev, int T, int nq, int nkv, int max_pos, float eps, float *q_out_dev,
+                                uint16_t *k_cache_dev, uint16_t *v_cache_dev);
+/* Causal grouped-query attention of T query tokens over cache positions 0 .. pos0 + t, softmax in
+ * fp32; out [T][nq * 128].  qwen3/src/qwen/QwenAttention.cc:154-190, qwen3/src/ops/softmax.cc:53-85 */
+int inkq_glue_attention(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev, int T,
+                        int nq, int nkv, int max_pos, float scale, float *out_dev);
+/* out = silu(gate) * up.  Qwen3SiLuMul, qwen3/src/qwen/QwenOperator.cc:697-722 */
+int inkq_glue_silu_mul(inkq_ctx *ctx, const float *gate_dev, const float *up_dev, long long n, float *out_dev);
+/* a += b (residual).  qwen3/src/qwen/QwenDecoderLayer.cc:73,105 */
+int inkq_glue_add_inplace(inkq_ctx *ctx, float *a_dev, const float *b_dev, long long n);
+/* Greedy sampling: *token_out = argmax(logits) (first index on ties), appended to generated
+ * (generated[0] = count, tokens follow; may be NULL), then *pos += advance.
+ * qwen3/src/qwen/Pipeline.cc:54-62 */
+int inkq_glue_argmax_advance(inkq_ctx *ctx, const float *logits_dev, int n, int *token_out_dev, int *pos_dev, int advance, int *generated_dev,
+                             int gen_cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INKQ_GLUE_H */

@@ -16,6 +16,7 @@ import numpy as np
 from . import build as _build
 from . import synth  # noqa: F401  (re-exported)
 from . import tp  # noqa: F401
+from . import qwen3_forward  # noqa: F401
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libinkq.so")
@@ -35,6 +36,11 @@ SYMBOLS = [
     "inkq_linear_host", "inkq_linear_m1_static", "inkq_gemm_w41_f16act", "inkq_f16w_create", "inkq_f16w_create_dev", "inkq_f16w_destroy",
     "inkq_f16w_matmul",
 ]
+
+
+# every symbol include/inkq_glue.h declares
+GLUE_SYMBOLS = ["inkq_glue_embedding", "inkq_glue_rmsnorm", "inkq_glue_qknorm_rope_cache", "inkq_glue_attention", "inkq_glue_silu_mul",
+                "inkq_glue_add_inplace", "inkq_glue_argmax_advance"]
 
 
 class InkqError(RuntimeError):
@@ -57,7 +63,7 @@ def lib() -> C.CDLL:
         L.inkq_last_error.argtypes = [C.c_void_p]
         L.inkq_launch_count.restype = C.c_uint64
         L.inkq_launch_count.argtypes = [C.c_void_p]
-        for name in SYMBOLS:
+        for name in SYMBOLS + GLUE_SYMBOLS:
             fn = getattr(L, name)
             if name not in ("inkq_last_error", "inkq_launch_count"):
                 fn.restype = C.c_int

@@ -1,0 +1,346 @@
+// Thin device-resident stand-ins for the non-GEMM operators around the quantized linear layers
+// of a Qwen3 decoder, so that a whole synthetic forward (prompt prefill + greedy decode) can keep
+// its activations on the GPU between the 181 quantized linears of a token.  Correct and simple,
+// not tuned: the named hot path is the quantized matmul, these only connect its calls.
+//
+// Reference behaviour followed (paths inside the reference project):
+//   embedding gather           qwen3/src/ops/embedding.cc:11-26
+//   RMSNorm (eps 1e-6)         qwen3/src/qwen/QwenOperator.cc:24-53
+//   per-head q/k RMSNorm, RoPE qwen3/src/qwen/QwenAttention.cc:85-92, qwen3/src/ops/RotaryPosEmb.cc:6-79
+//                              (rotate_half form: x*cos + rotate_half(x)*sin, tables [pos][head_dim])
+//   KV cache append            qwen3/src/qwen/QwenAttention.cc:105-121   (fp16 here, fp32 there)
+//   causal GQA attention       qwen3/src/qwen/QwenAttention.cc:154-190, qwen3/src/ops/softmax.cc:53-85
+//   SiLU(gate) * up            qwen3/src/qwen/QwenOperator.cc:697-722
+//   residual add               qwen3/src/qwen/QwenDecoderLayer.cc:73,105
+//   greedy argmax              qwen3/src/qwen/Pipeline.cc:54-62
+// Activations are fp32 row-major [tokens][features].  The position of the first token of a call
+// is read from device memory so that one captured CUDA graph serves every decode step.
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include "inkq_glue.h"
+#include "inkq_internal.h"
+
+namespace inkq {
+
+constexpr int HEAD_DIM = 128;
+
+__global__ void __launch_bounds__(256) k_embedding(const __half *__restrict__ table, const int *__restrict__ tokens, int T, int dim,
+                                                   float *__restrict__ out)
+{
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<long long>(T) * dim / 2) return;
+    const int t = static_cast<int>(idx / (dim / 2)), c = static_cast<int>(idx % (dim / 2));
+    const float2 v = __half22float2(reinterpret_cast<const __half2 *>(table + static_cast<size_t>(tokens[t]) * dim)[c]);
+    reinterpret_cast<float2 *>(out + static_cast<size_t>(t) * dim)[c] = v;
+}
+
+// one warp per row
+__global__ void __launch_bounds__(256) k_rmsnorm(const float *__restrict__ x, const float *__restrict__ w, int rows, int dim, float eps,
+                                                 float *__restrict__ y)
+{
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float4 *xr = reinterpret_cast<const float4 *>(x + static_cast<size_t>(row) * dim);
+    float ss = 0.0f;
+    for (int i = lane; i < dim / 4; i += 32) {
+        const float4 v = xr[i];
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = 1.0f / sqrtf(ss / static_cast<float>(dim) + eps);
+    float4 *yr = reinterpret_cast<float4 *>(y + static_cast<size_t>(row) * dim);
+    const float4 *wr = reinterpret_cast<const float4 *>(w);
+    for (int i = lane; i < dim / 4; i += 32) {
+        const float4 v = xr[i], g = wr[i];
+        yr[i] = make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+    }
+}
+
+// One warp per (token, head) of the fused qkv output [T][(nq + 2*nkv) * 128]:
+//   q heads : per-head RMSNorm, RoPE, written to q_out [T][nq][128] fp32
+//   k heads : per-head RMSNorm, RoPE, written to k_cache [nkv][max_pos][128] fp16 at position pos0 + t
+//   v heads : copied to v_cache likewise
+// Lane l holds elements l, l+32, l+64, l+96: the rotate_half partners (j, j+64) sit in one lane.
+__global__ void __launch_bounds__(256) k_qknorm_rope_cache(const float *__restrict__ qkv, const float *__restrict__ q_norm_w,
+                                                           const float *__restrict__ k_norm_w, const float *__restrict__ cos_t,
+                                                           const float *__restrict__ sin_t, const int *__restrict__ pos0_dev, int T, int nq,
+                                                           int nkv, int max_pos, float eps, float *__restrict__ q_out,
+                                                           __half *__restrict__ k_cache, __half *__restrict__ v_cache)
+{
+    const int heads = nq + 2 * nkv;
+    const int item = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= T * heads) return;
+    const int t = item / heads, h = item % heads;
+    const int pos = *pos0_dev + t;
+    if (pos >= max_pos) return;
+    const float *src = qkv + static_cast<size_t>(t) * heads * HEAD_DIM + static_cast<size_t>(h) * HEAD_DIM;
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) v[i] = src[lane + 32 * i];
+    if (h >= nq + nkv) {  // value head: straight to the cache
+        __half *dst = v_cache + (static_cast<size_t>(h - nq - nkv) * max_pos + pos) * HEAD_DIM;
+#pragma unroll
+        for (int i = 0; i < 4; i++) dst[lane + 32 * i] = __float2half_rn(v[i]);
+        return;
+    }
+    float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = 1.0f / sqrtf(ss / static_cast<float>(HEAD_DIM) + eps);
+    const float *nw = (h < nq) ? q_norm_w : k_norm_w;
+#pragma unroll
+    for (int i = 0; i < 4; i++) v[i] = v[i] * inv * nw[lane + 32 * i];
+    const float *cs = cos_t + static_cast<size_t>(pos) * HEAD_DIM, *sn = sin_t + static_cast<size_t>(pos) * HEAD_DIM;
+    float r[4];
+    // out[j] = x[j]*cos[j] + rot[j]*sin[j], rot[j] = -x[j+64] for j < 64, x[j-64] otherwise
+    r[0] = v[0] * cs[lane] - v[2] * sn[lane];
+    r[1] = v[1] * cs[lane + 32] - v[3] * sn[lane + 32];
+    r[2] = v[2] * cs[lane + 64] + v[0] * sn[lane + 64];
+    r[3] = v[3] * cs[lane + 96] + v[1] * sn[lane + 96];
+    if (h < nq) {
+        float *dst = q_out + (static_cast<size_t>(t) * nq + h) * HEAD_DIM;
+#pragma unroll
+        for (int i = 0; i < 4; i++) dst[lane + 32 * i] = r[i];
+    } else {
+        __half *dst = k_cache + (static_cast<size_t>(h - nq) * max_pos + pos) * HEAD_DIM;
+#pragma unroll
+        for (int i = 0; i < 4; i++) dst[lane + 32 * i] = __float2half_rn(r[i]);
+    }
+}
+
+// One CTA (128 threads) per (query token t, query head h).  Keys 0 .. pos0 + t (causal), the kv
+// head is h / (nq / nkv).  Pass 1: one thread per key computes the scaled dot product into shared
+// memory; block max and sum; pass 2: warp w accumulates the values of keys j = w mod 4, lanes over
+// the 128 dimensions; the four partials are added in warp order.
+__global__ void __launch_bounds__(128) k_attention(const float *__restrict__ q, const __half *__restrict__ k_cache,
+                                                   const __half *__restrict__ v_cache, const int *__restrict__ pos0_dev, int T, int nq, int nkv,
+                                                   int max_pos, float scale, float *__restrict__ out)
+{
+    extern __shared__ float sm[];
+    float *qs = sm;                  // 128
+    float *part = sm + HEAD_DIM;     // 4 * 128
+    float *red = part + 4 * HEAD_DIM;  // 8
+    float *sc = red + 8;             // scores, nkeys
+    const int t = blockIdx.x / nq, h = blockIdx.x % nq;
+    const int kvh = h / (nq / nkv);
+    const int nkeys = min(*pos0_dev + t + 1, max_pos);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    qs[tid] = q[(static_cast<size_t>(t) * nq + h) * HEAD_DIM + tid];
+    __syncthreads();
+    const __half *kb = k_cache + static_cast<size_t>(kvh) * max_pos * HEAD_DIM;
+    const __half *vb = v_cache + static_cast<size_t>(kvh) * max_pos * HEAD_DIM;
+    float lmax = -INFINITY;
+    for (int j = tid; j < nkeys; j += 128) {
+        const uint4 *kr = reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(j) * HEAD_DIM);
+        float acc = 0.0f;
+#pragma unroll 4
+        for (int c = 0; c < HEAD_DIM / 8; c++) {
+            const uint4 pk = kr[c];
+            const uint32_t wd[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&wd[i]));
+                acc = fmaf(qs[c * 8 + 2 * i], f.x, acc);
+                acc = fmaf(qs[c * 8 + 2 * i + 1], f.y, acc);
+            }
+        }
+        acc *= scale;
+        sc[j] = acc;
+        lmax = fmaxf(lmax, acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
+    if (lane == 0) red[warp] = lmax;
+    __syncthreads();
+    const float gmax = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    float lsum = 0.0f;
+    for (int j = tid; j < nkeys; j += 128) {
+        const float e = __expf(sc[j] - gmax);
+        sc[j] = e;
+        lsum += e;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+    if (lane == 0) red[4 + warp] = lsum;
+    __syncthreads();
+    const float inv = 1.0f / (red[4] + red[5] + red[6] + red[7]);
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int j = warp; j < nkeys; j += 4) {
+        const float p = sc[j];
+        const uint2 pk = reinterpret_cast<const uint2 *>(vb + static_cast<size_t>(j) * HEAD_DIM)[lane];
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.x));
+        const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.y));
+        a[0] = fmaf(p, f0.x, a[0]);
+        a[1] = fmaf(p, f0.y, a[1]);
+        a[2] = fmaf(p, f1.x, a[2]);
+        a[3] = fmaf(p, f1.y, a[3]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) part[warp * HEAD_DIM + lane * 4 + i] = a[i];
+    __syncthreads();
+    const float o = (part[tid] + part[HEAD_DIM + tid] + part[2 * HEAD_DIM + tid] + part[3 * HEAD_DIM + tid]) * inv;
+    out[(static_cast<size_t>(t) * nq + h) * HEAD_DIM + tid] = o;
+}
+
+__global__ void __launch_bounds__(256) k_silu_mul(const float4 *__restrict__ gate, const float4 *__restrict__ up, long long n4,
+                                                  float4 *__restrict__ out)
+{
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    const float4 g = gate[i], u = up[i];
+    auto f = [](float a, float b) { return a / (1.0f + __expf(-a)) * b; };
+    out[i] = make_float4(f(g.x, u.x), f(g.y, u.y), f(g.z, u.z), f(g.w, u.w));
+}
+
+__global__ void __launch_bounds__(256) k_add_inplace(float4 *__restrict__ a, const float4 *__restrict__ b, long long n4)
+{
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    const float4 x = a[i], y = b[i];
+    a[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+}
+
+// Single CTA: argmax of one logits row (first index on ties), written to *token_out and appended to
+// generated[*pos - prompt_len] when generated is given; then the position advances by `advance`.
+__global__ void __launch_bounds__(1024) k_argmax_advance(const float *__restrict__ logits, int n, int *__restrict__ token_out,
+                                                        int *__restrict__ pos_dev, int advance, int *__restrict__ generated, int gen_cap)
+{
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = logits[i];
+        if (v > best || (v == best && i < idx)) {
+            best = v;
+            idx = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) {
+            best = ov;
+            idx = oi;
+        }
+    }
+    if ((threadIdx.x & 31) == 0) {
+        bv[threadIdx.x >> 5] = best;
+        bi[threadIdx.x >> 5] = idx;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 32; w++)
+            if (bv[w] > best || (bv[w] == best && bi[w] < idx)) {
+                best = bv[w];
+                idx = bi[w];
+            }
+        *token_out = idx;
+        if (generated != nullptr) {
+            const int slot = generated[0];   // generated[0] counts the tokens stored so far, the tokens follow
+            if (slot + 1 < gen_cap) {
+                generated[slot + 1] = idx;
+                generated[0] = slot + 1;
+            }
+        }
+        *pos_dev += advance;
+    }
+}
+
+}  // namespace inkq
+
+using namespace inkq;
+
+static int glue_use(inkq_ctx *ctx)
+{
+    if (ctx == nullptr) return fail(nullptr, INKQ_ERR_INVALID, "null context");
+    INKQ_CUDA(ctx, cudaSetDevice(ctx->device));
+    return INKQ_OK;
+}
+
+extern "C" {
+
+int inkq_glue_embedding(inkq_ctx *ctx, const uint16_t *table16_dev, const int *tokens_dev, int T, int dim, float *out_dev)
+{
+    int rc = glue_use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, table16_dev && tokens_dev && out_dev && T >= 1 && dim % 2 == 0, "bad embedding arguments");
+    const long long n = static_cast<long long>(T) * dim / 2;
+    k_embedding<<<static_cast<unsigned>((n + 255) / 256), 256, 0, ctx->stream>>>(reinterpret_cast<const __half *>(table16_dev), tokens_dev, T, dim, out_dev);
+    return after_launch(ctx, "k_embedding");
+}
+
+int inkq_glue_rmsnorm(inkq_ctx *ctx, const float *x_dev, const float *w_dev, int rows, int dim, float eps, float *y_dev)
+{
+    int rc = glue_use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, x_dev && w_dev && y_dev && rows >= 1 && dim % 4 == 0, "bad rmsnorm arguments");
+    k_rmsnorm<<<(rows + 7) / 8, 256, 0, ctx->stream>>>(x_dev, w_dev, rows, dim, eps, y_dev);
+    return after_launch(ctx, "k_rmsnorm");
+}
+
+int inkq_glue_qknorm_rope_cache(inkq_ctx *ctx, const float *qkv_dev, const float *q_norm_w, const float *k_norm_w, const float *cos_dev,
+                                const float *sin_dev, const int *pos0_dev, int T, int nq, int nkv, int max_pos, float eps, float *q_out_dev,
+                                uint16_t *k_cache_dev, uint16_t *v_cache_dev)
+{
+    int rc = glue_use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, qkv_dev && q_norm_w && k_norm_w && cos_dev && sin_dev && pos0_dev && q_out_dev && k_cache_dev && v_cache_dev, "null argument");
+    INKQ_REQUIRE(ctx, T >= 1 && nq >= 1 && nkv >= 1 && nq % nkv == 0 && max_pos >= 1, "bad head configuration");
+    const int items = T * (nq + 2 * nkv);
+    k_qknorm_rope_cache<<<(items + 7) / 8, 256, 0, ctx->stream>>>(qkv_dev, q_norm_w, k_norm_w, cos_dev, sin_dev, pos0_dev, T, nq, nkv, max_pos, eps,
+                                                               q_out_dev, reinterpret_cast<__half *>(k_cache_dev),
+                                                               reinterpret_cast<__half *>(v_cache_dev));
+    return after_launch(ctx, "k_qknorm_rope_cache");
+}
+
+int inkq_glue_attention(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev, int T,
+                        int nq, int nkv, int max_pos, float scale, float *out_dev)
+{
+    int rc = glue_use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, q_dev && k_cache_dev && v_cache_dev && pos0_dev && out_dev, "null argument");
+    INKQ_REQUIRE(ctx, T >= 1 && nq % nkv == 0 && max_pos >= 1, "bad head configuration");
+    const size_t smem = sizeof(float) * (HEAD_DIM + 4 * HEAD_DIM + 8 + static_cast<size_t>(max_pos));
+    INKQ_REQUIRE(ctx, smem <= 200 * 1024, "context too long for the simple attention kernel");
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    k_attention<<<T * nq, 128, smem, ctx->stream>>>(q_dev, reinterpret_cast<const __half *>(k_cache_dev), reinterpret_cast<const __half *>(v_cache_dev),
+                                                    pos0_dev, T, nq, nkv, max_pos, scale, out_dev);
+    return after_launch(ctx, "k_attention");
+}
+
+int inkq_glue_silu_mul(inkq_ctx *ctx, const float *gate_dev, const float *up_dev, long long n, float *out_dev)
+{
+    int rc = glue_use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, gate_dev && up_dev && out_dev && n % 4 == 0, "bad silu_mul arguments");
+    k_silu_mul<<<static_cast<unsigned>((n / 4 + 255) / 256), 256, 0, ctx->stream>>>(reinterpret_cast<const float4 *>(gate_dev),
+                                                                                  reinterpret_cast<const float4 *>(up_dev), n / 4,
+                                                                                  reinterpret_cast<float4 *>(out_dev));
+    return after_launch(ctx, "k_silu_mul");
+}
+
+int inkq_glue_add_inplace(inkq_ctx *ctx, float *a_dev, const float *b_dev, long long n)
+{
+    int rc = glue_use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, a_dev && b_dev && n % 4 == 0, "bad add arguments");
+    k_add_inplace<<<static_cast<unsigned>((n / 4 + 255) / 256), 256, 0, ctx->stream>>>(reinterpret_cast<float4 *>(a_dev),
+                                                                                     reinterpret_cast<const float4 *>(b_dev), n / 4);
+    return after_launch(ctx, "k_add_inplace");
+}
+
+int inkq_glue_argmax_advance(inkq_ctx *ctx, const float *logits_dev, int n, int *token_out_dev, int *pos_dev, int advance, int *generated_dev,
+                             int gen_cap)
+{
+    int rc = glue_use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, logits_dev && token_out_dev && pos_dev && n >= 1, "bad argmax arguments");
+    k_argmax_advance<<<1, 1024, 0, ctx->stream>>>(logits_dev, n, token_out_dev, pos_dev, advance, generated_dev, gen_cap);
+    return after_launch(ctx, "k_argmax_advance");
+}
+
+}  // extern "C"

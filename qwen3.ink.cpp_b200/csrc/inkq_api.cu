@@ -143,6 +143,7 @@ int inkq_ctx_create(int device, void *stream, inkq_ctx **out)
     ctx->stream = static_cast<cudaStream_t>(stream);
     ctx->launches = 0;
     ctx->scratch_act = nullptr;
+    ctx->scratch_elems = 0;
     ctx->lin_x = ctx->lin_c = nullptr;
     ctx->lin_x_cap = ctx->lin_c_cap = 0;
     ctx->pin_x = ctx->pin_c = nullptr;
@@ -539,21 +540,46 @@ int inkq_debug_block_dots_tc(inkq_ctx *ctx, const inkq_act *act, const inkq_weig
 }
 
 // ---- linear forward ---------------------------------------------------------------------
+// The context's activation scratch (the reference's ModelContext::activation_buffer, sized once for the
+// largest layer, QwenForCausalLM.cc:101-113): one allocation that serves every (M, K) whose M*K fits.  It
+// only grows, so a model's layers with different K (4096 / 12288) share it without re-allocating, and a
+// warmed-up context allocates nothing more (which also keeps inkq_linear capturable in a CUDA graph).
 static int ensure_scratch_act(inkq_ctx *ctx, int M, int K)
 {
+    const size_t need = static_cast<size_t>(M) * K;
     Act *a = ctx->scratch_act;
-    if (a != nullptr && a->K == K && a->max_rows >= M) return INKQ_OK;
-    if (a != nullptr) {
-        cudaStreamSynchronize(ctx->stream);
-        free_act(a);
-        delete static_cast<inkq_act *>(a);
-        ctx->scratch_act = nullptr;
+    if (a == nullptr || ctx->scratch_elems < need) {
+        if (a != nullptr) {
+            cudaStreamSynchronize(ctx->stream);
+            free_act(a);
+            delete static_cast<inkq_act *>(a);
+            ctx->scratch_act = nullptr;
+            ctx->scratch_elems = 0;
+        }
+        size_t elems = need < (static_cast<size_t>(512) * 12288) ? static_cast<size_t>(512) * 12288 : need;
+        inkq_act *na = new (std::nothrow) inkq_act();
+        if (na == nullptr) return fail(ctx, INKQ_ERR_ALLOC, "host allocation failed");
+        na->ctx = ctx;
+        na->q = nullptr;
+        na->d = na->s = nullptr;
+        na->isum = nullptr;
+        const size_t planes = elems / QK + 65536;   // [K/32][round_up(M, 4)] fits for every M*K <= elems with K <= 2^21
+        int rc = dev_alloc(ctx, &na->q, elems);
+        if (!rc) rc = dev_alloc(ctx, &na->d, planes);
+        if (!rc) rc = dev_alloc(ctx, &na->s, planes);
+        if (!rc) rc = dev_alloc(ctx, &na->isum, planes);
+        if (rc) {
+            free_act(na);
+            delete na;
+            return rc;
+        }
+        ctx->scratch_act = na;
+        ctx->scratch_elems = elems;
+        a = na;
     }
-    inkq_act *na = nullptr;
-    int rows = M < 512 ? 512 : M;
-    int rc = inkq_act_create(ctx, rows, K, &na);
-    if (rc) return rc;
-    ctx->scratch_act = na;
+    a->K = K;
+    a->max_rows = static_cast<int>(ctx->scratch_elems / K);
+    a->M = 0;
     return INKQ_OK;
 }
 

@@ -78,6 +78,7 @@ struct inkq_ctx {
     int num_sms;
     int *dev_flag;        // device word set by a kernel whose bounded wait ran out
     inkq::Act *scratch_act;  // activation scratch of inkq_linear (grown on demand)
+    size_t scratch_elems;    // its capacity in activation elements (M * K)
     float *lin_x, *lin_c;    // device staging of inkq_linear_host
     size_t lin_x_cap, lin_c_cap;
     float *pin_x, *pin_c;    // pinned host staging of inkq_linear_host

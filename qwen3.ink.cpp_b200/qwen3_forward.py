@@ -1,0 +1,160 @@
+"""Synthetic Qwen3 decoder forward on one GPU: the caller of the quantized linear layers.
+
+It exists to *report* prompt-prefill and decode throughput of the A8W4 path inside the model
+it was written for (Qwen3-8B: 36 layers, hidden 4096, 32 query / 8 KV heads of 128, SwiGLU
+12288, vocabulary 151936, RoPE theta 1e6, per-head q/k RMSNorm), with random-init weights
+generated directly on the device.  Structure follows the reference's model code
+(qwen3/src/qwen/QwenForCausalLM.cc:11-122, QwenDecoder.cc:53-142, QwenDecoderLayer.cc:39-119,
+QwenAttention.cc:52-207): fused qkv projection, last-token lm_head, greedy argmax.  Every
+linear goes through Context.linear (Qwen_Linear_with_bias_Int4::forward: quantize + QGEMM for
+a prompt, + QGEMV for a single token); everything between them is the thin glue of
+csrc/glue_ops.cu.  One decode step is captured once as a CUDA graph and replayed.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import dataclasses
+
+import numpy as np
+
+
+@dataclasses.dataclass
+class Qwen3Config:
+    layers: int = 36
+    hidden: int = 4096
+    nq: int = 32
+    nkv: int = 8
+    head_dim: int = 128
+    ffn: int = 12288
+    vocab: int = 151936
+    rope_theta: float = 1e6
+    eps: float = 1e-6
+    max_pos: int = 512
+    lm_head_fp16: bool = True     # fp16 lm_head (benchmark config); False: A81W41 like the reference
+
+
+def _p(t):
+    return C.c_void_p(t.data_ptr())
+
+
+class Qwen3Synthetic:
+    def __init__(self, pkg, ctx, cfg: Qwen3Config, seed: int = 0):
+        import torch
+        assert cfg.head_dim == 128, "the glue kernels are written for head_dim 128"
+        self.pkg, self.ctx, self.cfg, self.torch = pkg, ctx, cfg, torch
+        self.L = pkg.lib()
+        g = torch.Generator(device="cuda")
+        g.manual_seed(seed)
+        H, F, V = cfg.hidden, cfg.ffn, cfg.vocab
+        qkv_n = (cfg.nq + 2 * cfg.nkv) * cfg.head_dim
+
+        def qlinear(N, K):
+            # nibbles uniform, d ~ U(0.002, 0.02), m ~ U(-0.1, 0) rounded to fp16: as the benchmark configs state
+            nib = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device="cuda", generator=g)
+            d = (torch.rand((N, K // 32), device="cuda", generator=g) * 0.018 + 0.002).half().float()
+            m = (torch.rand((N, K // 32), device="cuda", generator=g) * -0.1).half().float()
+            w = ctx.weight_dev(pkg.A81W41, pkg.SCALES_F16, N, K, nib, d, m)
+            return w
+
+        self.layers = []
+        for _ in range(cfg.layers):
+            self.layers.append(dict(
+                ln1=torch.ones(H, device="cuda"), ln2=torch.ones(H, device="cuda"),
+                qn=torch.ones(cfg.head_dim, device="cuda"), kn=torch.ones(cfg.head_dim, device="cuda"),
+                qkv=qlinear(qkv_n, H), o=qlinear(H, cfg.nq * cfg.head_dim), gate=qlinear(F, H), up=qlinear(F, H), down=qlinear(H, F),
+                k_cache=torch.zeros((cfg.nkv, cfg.max_pos, cfg.head_dim), dtype=torch.float16, device="cuda"),
+                v_cache=torch.zeros((cfg.nkv, cfg.max_pos, cfg.head_dim), dtype=torch.float16, device="cuda")))
+        self.final_norm = torch.ones(H, device="cuda")
+        self.embed = (torch.randn((V, H), device="cuda", generator=g) * 0.02).half()
+        if cfg.lm_head_fp16:
+            head = (torch.randn((V, H), device="cuda", generator=g) * 0.02).half()
+            self.lm_head = ctx.f16w_dev(head, V, H)
+            del head
+        else:
+            self.lm_head = qlinear(V, H)
+        inv = 1.0 / (cfg.rope_theta ** (np.arange(0, cfg.head_dim, 2, dtype=np.float64) / cfg.head_dim))
+        ang = np.outer(np.arange(cfg.max_pos, dtype=np.float64), inv)
+        ang = np.concatenate([ang, ang], axis=1)                       # [max_pos][head_dim], both halves equal (HF layout)
+        self.cos = torch.from_numpy(np.cos(ang).astype(np.float32)).cuda()
+        self.sin = torch.from_numpy(np.sin(ang).astype(np.float32)).cuda()
+        self.pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.token = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.generated = torch.zeros(4096, dtype=torch.int32, device="cuda")
+        self.bufs = {}
+        self.graph = None
+
+    # ------------------------------------------------------------------ buffers
+    def _buffers(self, T):
+        torch, cfg = self.torch, self.cfg
+        if T not in self.bufs:
+            qkv_n = (cfg.nq + 2 * cfg.nkv) * cfg.head_dim
+            z = lambda *s: torch.empty(s, device="cuda", dtype=torch.float32)
+            self.bufs[T] = dict(x=z(T, cfg.hidden), xn=z(T, cfg.hidden), qkv=z(T, qkv_n), q=z(T, cfg.nq * cfg.head_dim),
+                                attn=z(T, cfg.nq * cfg.head_dim), proj=z(T, cfg.hidden), gate=z(T, cfg.ffn), up=z(T, cfg.ffn),
+                                act=z(T, cfg.ffn), logits=z(1, cfg.vocab))
+        return self.bufs[T]
+
+    def _chk(self, rc):
+        self.ctx.check(rc)
+
+    # ------------------------------------------------------------------ one forward over T tokens (tokens_dev int32 [T])
+    def forward(self, tokens_dev, T, advance):
+        """Runs the T tokens at positions pos .. pos+T-1 through the model, takes the last token's logits,
+        stores their argmax in self.token (and the generated list) and advances pos by `advance`."""
+        cfg, L, h, b = self.cfg, self.L, self.ctx.h, self._buffers(T)
+        H, F = cfg.hidden, cfg.ffn
+        scale = 1.0 / float(np.sqrt(cfg.head_dim))
+        self._chk(L.inkq_glue_embedding(h, _p(self.embed), _p(tokens_dev), T, H, _p(b["x"])))
+        for ly in self.layers:
+            self._chk(L.inkq_glue_rmsnorm(h, _p(b["x"]), _p(ly["ln1"]), T, H, C.c_float(cfg.eps), _p(b["xn"])))
+            self.ctx.linear(ly["qkv"], b["xn"], T, b["qkv"], b["qkv"].shape[1])
+            self._chk(L.inkq_glue_qknorm_rope_cache(h, _p(b["qkv"]), _p(ly["qn"]), _p(ly["kn"]), _p(self.cos), _p(self.sin), _p(self.pos), T,
+                                                    cfg.nq, cfg.nkv, cfg.max_pos, C.c_float(cfg.eps), _p(b["q"]), _p(ly["k_cache"]),
+                                                    _p(ly["v_cache"])))
+            self._chk(L.inkq_glue_attention(h, _p(b["q"]), _p(ly["k_cache"]), _p(ly["v_cache"]), _p(self.pos), T, cfg.nq, cfg.nkv, cfg.max_pos,
+                                            C.c_float(scale), _p(b["attn"])))
+            self.ctx.linear(ly["o"], b["attn"], T, b["proj"], H)
+            self._chk(L.inkq_glue_add_inplace(h, _p(b["x"]), _p(b["proj"]), C.c_longlong(T * H)))
+            self._chk(L.inkq_glue_rmsnorm(h, _p(b["x"]), _p(ly["ln2"]), T, H, C.c_float(cfg.eps), _p(b["xn"])))
+            self.ctx.linear(ly["gate"], b["xn"], T, b["gate"], F)
+            self.ctx.linear(ly["up"], b["xn"], T, b["up"], F)
+            self._chk(L.inkq_glue_silu_mul(h, _p(b["gate"]), _p(b["up"]), C.c_longlong(T * F), _p(b["act"])))
+            self.ctx.linear(ly["down"], b["act"], T, b["proj"], H)
+            self._chk(L.inkq_glue_add_inplace(h, _p(b["x"]), _p(b["proj"]), C.c_longlong(T * H)))
+        last = b["x"][T - 1:T]
+        self._chk(L.inkq_glue_rmsnorm(h, _p(last), _p(self.final_norm), 1, H, C.c_float(cfg.eps), _p(b["xn"])))
+        if cfg.lm_head_fp16:
+            self.ctx.f16w_matmul(self.lm_head, b["xn"], 1, b["logits"], cfg.vocab)
+        else:
+            self.ctx.linear(self.lm_head, b["xn"], 1, b["logits"], cfg.vocab)
+        self._chk(L.inkq_glue_argmax_advance(h, _p(b["logits"]), cfg.vocab, _p(self.token), _p(self.pos), advance, _p(self.generated),
+                                             self.generated.numel()))
+        return b["logits"]
+
+    def reset(self):
+        self.pos.zero_()
+        self.generated.zero_()
+
+    def prefill(self, prompt_dev):
+        return self.forward(prompt_dev, int(prompt_dev.numel()), int(prompt_dev.numel()))
+
+    def decode_step(self):
+        return self.forward(self.token, 1, 1)
+
+    def capture_decode(self):
+        """Captures one decode step as a CUDA graph on a side stream (call after a prefill and one eager
+        decode step, so that every scratch buffer already exists)."""
+        torch = self.torch
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(s):
+            self.ctx.set_stream(s.cuda_stream)
+            with torch.cuda.graph(self.graph, stream=s):
+                self.decode_step()
+        self.ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+        torch.cuda.current_stream().wait_stream(s)
+
+    def generated_tokens(self):
+        g = self.generated.cpu().numpy()
+        return g[1:1 + int(g[0])]

@@ -7,20 +7,21 @@ import re
 from conftest import ROOT
 
 
-def declared_symbols():
-    src = open(os.path.join(ROOT, "include", "inkq.h")).read()
+def declared_symbols(header="inkq.h"):
+    src = open(os.path.join(ROOT, "include", header)).read()
     src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
     return sorted(set(re.findall(r"\b(inkq_[a-z0-9_]+)\s*\(", src)))
 
 
 def test_header_and_binding_agree(pkg):
     assert declared_symbols() == sorted(pkg.SYMBOLS)
+    assert declared_symbols("inkq_glue.h") == sorted(pkg.GLUE_SYMBOLS)
 
 
 def test_library_exports_every_declared_symbol(pkg):
     pkg.build()
     L = pkg.lib()
-    for name in declared_symbols():
+    for name in declared_symbols() + declared_symbols("inkq_glue.h"):
         assert hasattr(L, name), name
 
 

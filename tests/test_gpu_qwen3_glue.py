@@ -1,0 +1,102 @@
+"""GPU: the thin device-resident glue around the quantized linears (csrc/glue_ops.cu) and the
+synthetic Qwen3 forward built from it, on a small configuration.
+ - the whole forward against the same graph written with plain PyTorch fp32 ops (the quantized
+   linears are the library's own in both, they are checked elsewhere)
+ - the decode path (one token, KV cache, captured CUDA graph) against the prefill path
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def small_cfg(pkg):
+    return pkg.qwen3_forward.Qwen3Config(layers=2, hidden=256, nq=4, nkv=2, head_dim=128, ffn=512, vocab=1024, max_pos=64, lm_head_fp16=True)
+
+
+def torch_forward(torch, model, tokens):
+    """Same graph with PyTorch ops (fp32), K/V rounded to fp16 as the cache holds them."""
+    cfg, ctx = model.cfg, model.ctx
+    T = tokens.numel()
+    x = model.embed[tokens.long()].float()
+
+    def rms(v, w):
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.eps) * w
+
+    def lin(w, inp, N):
+        out = torch.empty((inp.shape[0], N), device="cuda")
+        ctx.linear(w, inp.contiguous(), inp.shape[0], out, N)
+        return out
+
+    def rope(v):    # v [T][heads][128]
+        cos, sin = model.cos[:T, None, :], model.sin[:T, None, :]
+        rot = torch.cat((-v[..., 64:], v[..., :64]), dim=-1)
+        return v * cos + rot * sin
+
+    for ly in model.layers:
+        h = rms(x, ly["ln1"])
+        qkv = lin(ly["qkv"], h, (cfg.nq + 2 * cfg.nkv) * 128).view(T, cfg.nq + 2 * cfg.nkv, 128)
+        q = rope(rms(qkv[:, :cfg.nq], ly["qn"]))
+        k = rope(rms(qkv[:, cfg.nq:cfg.nq + cfg.nkv], ly["kn"])).half().float()
+        v = qkv[:, cfg.nq + cfg.nkv:].half().float()
+        rep = cfg.nq // cfg.nkv
+        k, v = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
+        s = torch.einsum("thd,shd->hts", q, k) / np.sqrt(128.0)
+        s = s.masked_fill(torch.triu(torch.ones(T, T, device="cuda", dtype=torch.bool), 1), float("-inf"))
+        a = torch.einsum("hts,shd->thd", torch.softmax(s, dim=-1), v).reshape(T, cfg.nq * 128)
+        x = x + lin(ly["o"], a, cfg.hidden)
+        h = rms(x, ly["ln2"])
+        act = torch.nn.functional.silu(lin(ly["gate"], h, cfg.ffn)) * lin(ly["up"], h, cfg.ffn)
+        x = x + lin(ly["down"], act, cfg.hidden)
+    last = rms(x[T - 1:T], model.final_norm)
+    return last
+
+
+def test_forward_matches_pytorch_graph(pkg, gpu):
+    import torch
+    model = pkg.qwen3_forward.Qwen3Synthetic(pkg, gpu, small_cfg(pkg), seed=1)
+    tokens = torch.from_numpy(pkg.synth.tokens(13, 1024, 5)).cuda()
+    model.reset()
+    logits = model.prefill(tokens).clone()
+    gpu.synchronize()
+    last = torch_forward(torch, model, tokens)                       # final-normed hidden state of the last token
+    ref = torch.empty((1, 1024), device="cuda")
+    gpu.f16w_matmul(model.lm_head, last.contiguous(), 1, ref, 1024)
+    gpu.synchronize()
+    err = (logits - ref).abs().max().item() / ref.abs().max().item()
+    assert err < 2e-3, err
+    assert int(model.token.item()) == int(ref.argmax().item())
+    assert int(model.pos.item()) == 13
+
+
+def test_decode_path_and_graph_agree_with_prefill(pkg, gpu):
+    import torch
+    model = pkg.qwen3_forward.Qwen3Synthetic(pkg, gpu, small_cfg(pkg), seed=2)
+    toks = torch.from_numpy(pkg.synth.tokens(9, 1024, 6)).cuda()
+    # prefill all 9 tokens
+    model.reset()
+    full = model.prefill(toks).clone()
+    # prefill 8, then feed the 9th through the decode path (M == 1 linears, cache append at position 8)
+    model.reset()
+    model.prefill(toks[:8])
+    model.token.copy_(toks[8:9])
+    step = model.decode_step().clone()
+    gpu.synchronize()
+    rel = (step - full).abs().max().item() / full.abs().max().item()
+    assert rel < 3e-2, rel            # the single-token path quantizes with fp16 activation scales and uses the QGEMV order
+    assert int(model.pos.item()) == 9
+    # greedy generation: eager steps and replays of the captured graph give the same tokens
+    model.reset()
+    model.prefill(toks)
+    for _ in range(5):
+        model.decode_step()
+    gpu.synchronize()
+    eager = model.generated_tokens().copy()
+    model.reset()
+    model.prefill(toks)
+    model.decode_step()
+    model.capture_decode()
+    for _ in range(4):
+        model.graph.replay()
+    torch.cuda.synchronize()
+    assert np.array_equal(model.generated_tokens(), eager) and len(eager) == 6
