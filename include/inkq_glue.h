@@ -18,8 +18,8 @@
 extern "C" {
 #endif
 
-/* out[t][:] = table[tokens[t]][:]  (fp16 table).  qwen3/src/ops/embedding.cc:11-26 */
-int inkq_glue_embedding(inkq_ctx *ctx, const uint16_t *table16_dev, const int *tokens_dev, int T, int dim, float *out_dev);
+/* out[t][:] = table[tokens[t]][:]  (fp16 table [vocab][dim]; ids are clamped to the table).  qwen3/src/ops/embedding.cc:11-26 */
+int inkq_glue_embedding(inkq_ctx *ctx, const uint16_t *table16_dev, const int *tokens_dev, int T, int dim, int vocab, float *out_dev);
 /* y = x * rsqrt(mean(x^2) + eps) * w per row.  Qwen3RMSNorm::forward, qwen3/src/qwen/QwenOperator.cc:24-53 */
 int inkq_glue_rmsnorm(inkq_ctx *ctx, const float *x_dev, const float *w_dev, int rows, int dim, float eps, float *y_dev);
 /* Fused qkv output [T][(nq + 2 nkv) * 128] -> per-head RMSNorm of q and k, RoPE (rotate-half form,

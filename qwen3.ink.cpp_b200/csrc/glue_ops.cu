@@ -25,13 +25,14 @@ namespace inkq {
 
 constexpr int HEAD_DIM = 128;
 
-__global__ void __launch_bounds__(256) k_embedding(const __half *__restrict__ table, const int *__restrict__ tokens, int T, int dim,
+__global__ void __launch_bounds__(256) k_embedding(const __half *__restrict__ table, const int *__restrict__ tokens, int T, int dim, int vocab,
                                                    float *__restrict__ out)
 {
     const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= static_cast<long long>(T) * dim / 2) return;
     const int t = static_cast<int>(idx / (dim / 2)), c = static_cast<int>(idx % (dim / 2));
-    const float2 v = __half22float2(reinterpret_cast<const __half2 *>(table + static_cast<size_t>(tokens[t]) * dim)[c]);
+    const int tok = min(max(tokens[t], 0), vocab - 1);   // a token id outside the table (e.g. from NaN logits) must not become an address
+    const float2 v = __half22float2(reinterpret_cast<const __half2 *>(table + static_cast<size_t>(tok) * dim)[c]);
     reinterpret_cast<float2 *>(out + static_cast<size_t>(t) * dim)[c] = v;
 }
 
@@ -210,7 +211,7 @@ __global__ void __launch_bounds__(1024) k_argmax_advance(const float *__restrict
     __shared__ float bv[32];
     __shared__ int bi[32];
     float best = -INFINITY;
-    int idx = 0x7fffffff;
+    int idx = n - 1;   // stays a valid index even when every logit is NaN
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const float v = logits[i];
         if (v > best || (v == best && i < idx)) {
@@ -263,13 +264,13 @@ static int glue_use(inkq_ctx *ctx)
 
 extern "C" {
 
-int inkq_glue_embedding(inkq_ctx *ctx, const uint16_t *table16_dev, const int *tokens_dev, int T, int dim, float *out_dev)
+int inkq_glue_embedding(inkq_ctx *ctx, const uint16_t *table16_dev, const int *tokens_dev, int T, int dim, int vocab, float *out_dev)
 {
     int rc = glue_use(ctx);
     if (rc) return rc;
-    INKQ_REQUIRE(ctx, table16_dev && tokens_dev && out_dev && T >= 1 && dim % 2 == 0, "bad embedding arguments");
+    INKQ_REQUIRE(ctx, table16_dev && tokens_dev && out_dev && T >= 1 && dim % 2 == 0 && vocab >= 1, "bad embedding arguments");
     const long long n = static_cast<long long>(T) * dim / 2;
-    k_embedding<<<static_cast<unsigned>((n + 255) / 256), 256, 0, ctx->stream>>>(reinterpret_cast<const __half *>(table16_dev), tokens_dev, T, dim, out_dev);
+    k_embedding<<<static_cast<unsigned>((n + 255) / 256), 256, 0, ctx->stream>>>(reinterpret_cast<const __half *>(table16_dev), tokens_dev, T, dim, vocab, out_dev);
     return after_launch(ctx, "k_embedding");
 }
 
