@@ -286,6 +286,8 @@ def run_ours(args, rank, world, local_rank):
     dist = None
     if world > 1:
         import torch.distributed as dist
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":    # its banner would share stdout with the JSON line
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ctx = pkg.Context(local_rank, torch.cuda.current_stream().cuda_stream)
 
@@ -302,18 +304,28 @@ def run_ours(args, rank, world, local_rank):
     sets = int(max(3, min(16, 1.5 * L2_BYTES // w_bytes_one + 2)))
     ws = [ctx.weight(pkg.A81W41, pkg.SCALES_F32, wt["nib"], wt["d"], wt["m"], None, n0, n1) for _ in range(sets)]
     xs = [torch.from_numpy(x_host).cuda() for _ in range(sets)]
+    scatter, exchange = None, "single GPU"
     if world > 1:
         cg = pkg.tp.ColumnGather(dist, M, N, world, rank, "cuda", torch.float32)   # in-place all-gather target
         Cs = [cg.local]
+        try:
+            scatter = pkg.tp.PeerScatter(pkg, ctx, dist, M, N, world, rank, slots=2)
+            exchange = f"tp{world}: N-sharded, QGEMM epilogue stores into every rank's [M][N] over NVLink + barrier kernel"
+        except RuntimeError as e:
+            exchange = f"tp{world}: N-sharded, NCCL all-gather (peer mapping unavailable: {str(e)[:120]})"
     else:
         Cs = [torch.empty((M, n_loc), device="cuda") for _ in range(2)]
 
-    def step(i):
-        w = ws[i % sets]
-        C = Cs[i % len(Cs)]
-        ctx.linear(w, xs[i % sets], M, C, n_loc)                        # quantizer + QGEMM (Qwen_Linear_with_bias_Int4::forward)
+    def step_gather(i):
+        ctx.linear(ws[i % sets], xs[i % sets], M, Cs[i % len(Cs)], n_loc)   # quantizer + QGEMM (Qwen_Linear_with_bias_Int4::forward)
         if world > 1:
             cg.gather()                                                 # NCCL all-gather + [P][M][N/P] -> [M][N]
+
+    def step_scatter(i):
+        scatter.linear(ws[i % sets], xs[i % sets], i % 2)               # quantizer + QGEMM, C stored on every rank
+        scatter.barrier()
+
+    step = step_scatter if scatter is not None else step_gather
 
     for i in range(args.warmup):
         step(i)
@@ -335,15 +347,29 @@ def run_ours(args, rank, world, local_rank):
     clocks = sampler.stop()
     ops = 2.0 * M * N * K
     tops = ops * args.steps / (ms * 1e-3) / 1e12
+    gather_tops = None
+    if scatter is not None:          # the library-collective variant of the same step, for comparison
+        for i in range(args.warmup):
+            step_gather(i)
+        torch.cuda.synchronize()
+        dist.barrier()
+        ms2 = cuda_time_ms(torch, step_gather, args.steps)
+        t = torch.tensor([ms2], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        gather_tops = ops * args.steps / (float(t.item()) * 1e-3) / 1e12
+        dist.barrier()
+        ctx.synchronize()
 
     line = {"metric": "qgemm_int8_tops_pp322" if wl in ("qgemm_pp322", "qgemv_sweep") else f"qgemm_int8_tops_{wl.split('_')[1]}",
             "value": tops, "unit": "TOPS", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "s8 x u4 -> s32 block dots (tcgen05 kind::i8), fp32 scale/accumulate", "data": "synthetic",
             "config": {"workload": wl if wl != "qgemv_sweep" else "qgemm_pp322", "M": M, "N": N, "K": K, "scheme": "A81W41",
-                       "weight_scales": "fp32", "parallelism": f"tp{world} (N-sharded, NCCL all-gather)" if world > 1 else "single GPU",
+                       "weight_scales": "fp32", "parallelism": exchange,
                        "l2": f"{sets} distinct weight sets ({sets * w_bytes_one / 1e6:.0f} MB per rank) rotated between steps, > 126 MB L2"},
             "clocks": clocks, "gpu_launches": int(launches)}
+    if gather_tops is not None:
+        line["config"]["same_step_with_nccl_all_gather_tops"] = gather_tops
 
     if rank == 0:
         # ---- kernel-only figures for the roofline (dominant kernel: the tensor-core QGEMM) ----
@@ -395,6 +421,8 @@ def run_ours(args, rank, world, local_rank):
             except Exception as e:   # the headline metric above stands on its own
                 line["model"] = {"error": repr(e)[:300]}
         print(json.dumps(line), flush=True)
+    if scatter is not None:
+        scatter.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -158,6 +158,38 @@ int inkq_linear_host(inkq_ctx *ctx, const inkq_weight *w, const float *x_host, i
  * the GPU race, order them.  Never allocates or frees device memory. */
 int inkq_linear_m1_static(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, float *C_dev);
 
+/* ---- column-sharded layer with the exchange step inside the matmul ------------------
+ * No counterpart in the reference (one process, CPU threads; its kernels parallelise
+ * over 8-column groups, qwen3/src/qwen/quantized_gemx_kernels.cc:364-365, which is the
+ * independence this sharding uses).  Rank r of P holds the weight rows [r*N/P, (r+1)*N/P)
+ * (inkq_weight_create with that range); inkq_linear_scatter runs the forward of
+ * inkq_linear and stores every output element into the buffer of EVERY rank of a peer
+ * set at the same byte offset, straight from the kernel's epilogue over NVLink;
+ * inkq_peer_barrier then tells every peer that this rank's stores are complete and waits
+ * for the same from each of them (bounded: after timeout_ms the kernel gives up and the
+ * next inkq_ctx_synchronize returns INKQ_ERR_TIMEOUT).  After the barrier every rank
+ * holds the full [M][N] matrix; no collective library call is involved.
+ *
+ * A peer set is world <= 8 device buffers of equal size, one per rank, 256-byte aligned.
+ * Their first INKQ_PEER_RESERVED_BYTES belong to the barrier and must be zero when the set
+ * is made.  With one process per GPU: inkq_peer_export writes an INKQ_PEER_HANDLE_BYTES
+ * blob for the local buffer (CUDA IPC; the buffer must come from cudaMalloc, directly or
+ * through a caching allocator that does not use virtual-memory segments), the host
+ * gathers all ranks' blobs in rank order and inkq_peerset_open maps them.  With one
+ * process for all GPUs (peer access enabled) or several buffers on one GPU:
+ * inkq_peerset_from_pointers.  Use two offsets alternately when steps follow each other
+ * without any other synchronisation: a rank may start step i+1 while a peer still reads
+ * the result of step i. */
+#define INKQ_PEER_RESERVED_BYTES 256
+#define INKQ_PEER_HANDLE_BYTES 80
+typedef struct inkq_peerset inkq_peerset;
+int inkq_peer_export(inkq_ctx *ctx, void *dev_ptr, size_t bytes, void *blob_out);
+int inkq_peerset_open(inkq_ctx *ctx, int world, int rank, void *local_ptr, const void *blobs, inkq_peerset **out);
+int inkq_peerset_from_pointers(inkq_ctx *ctx, int world, int rank, void *const *ptrs, size_t bytes, inkq_peerset **out);
+int inkq_peerset_destroy(inkq_peerset *ps);
+int inkq_linear_scatter(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, int M, inkq_peerset *ps, size_t byte_offset, int ldc);
+int inkq_peer_barrier(inkq_ctx *ctx, inkq_peerset *ps, int timeout_ms);
+
 /* ---- weight-only W41 (fp16 activations) and fp16 lm_head ---------------------
  * No C++ kernel exists in the reference for these two; they follow
  * notebooks/evaluate-qwen3_8b_W4.ipynb cell 13 and, for lm_head, the fp32 GEMV

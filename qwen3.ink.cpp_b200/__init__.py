@@ -34,13 +34,18 @@ SYMBOLS = [
     "inkq_weight_export", "inkq_act_create", "inkq_act_destroy", "inkq_quantize", "inkq_act_export", "inkq_act_import", "inkq_quantize_host", "inkq_gemm_host", "inkq_gemv_host", "inkq_gemm",
     "inkq_gemv", "inkq_gemm_simt", "inkq_debug_block_dots", "inkq_debug_block_dots_tc", "inkq_linear",
     "inkq_linear_host", "inkq_linear_m1_static", "inkq_gemm_w41_f16act", "inkq_f16w_create", "inkq_f16w_create_dev", "inkq_f16w_destroy",
-    "inkq_f16w_matmul",
+    "inkq_f16w_matmul", "inkq_peer_export", "inkq_peerset_open", "inkq_peerset_from_pointers", "inkq_peerset_destroy",
+    "inkq_linear_scatter", "inkq_peer_barrier",
 ]
 
 
 # every symbol include/inkq_glue.h declares
 GLUE_SYMBOLS = ["inkq_glue_embedding", "inkq_glue_rmsnorm", "inkq_glue_qknorm_rope_cache", "inkq_glue_attention", "inkq_glue_silu_mul",
                 "inkq_glue_add_inplace", "inkq_glue_argmax_advance"]
+
+
+PEER_RESERVED_BYTES = 256   # INKQ_PEER_RESERVED_BYTES
+PEER_HANDLE_BYTES = 80      # INKQ_PEER_HANDLE_BYTES
 
 
 class InkqError(RuntimeError):
@@ -82,6 +87,24 @@ def _dp(t):
 
 def _hp(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+class PeerSet:
+    """Handle of a peer set (keeps the local buffers alive)."""
+
+    def __init__(self, ctx, h, world, rank, keep):
+        self.ctx, self.h, self.world, self.rank, self.keep = ctx, h, world, rank, keep
+
+    def close(self):
+        if self.h:
+            self.ctx.L.inkq_peerset_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class Context:
@@ -192,6 +215,35 @@ class Context:
         xp = x_host.ctypes.data_as(C.c_void_p) if isinstance(x_host, np.ndarray) else C.c_void_p(x_host.data_ptr())
         cp = C_host.ctypes.data_as(C.c_void_p) if isinstance(C_host, np.ndarray) else C.c_void_p(C_host.data_ptr())
         self.check(self.L.inkq_linear_host(self.h, w.h, xp, M, cp, ldc))
+
+    # ---- column-sharded layer with in-kernel exchange (csrc/peer.cu)
+    def peer_export(self, buf) -> bytes:
+        """80-byte blob naming the device buffer `buf` (a torch uint8/float tensor) for other processes."""
+        blob = C.create_string_buffer(PEER_HANDLE_BYTES)
+        self.check(self.L.inkq_peer_export(self.h, _dp(buf), C.c_size_t(buf.numel() * buf.element_size()), blob))
+        return blob.raw
+
+    def peerset_open(self, world: int, rank: int, local_buf, blobs):
+        h = C.c_void_p()
+        raw = b"".join(blobs)
+        assert len(raw) == world * PEER_HANDLE_BYTES
+        self.check(self.L.inkq_peerset_open(self.h, world, rank, _dp(local_buf), raw, C.byref(h)))
+        return PeerSet(self, h, world, rank, [local_buf])
+
+    def peerset_from_tensors(self, rank: int, bufs):
+        """Peer set over buffers this process can address itself (same GPU, or peer access enabled)."""
+        h = C.c_void_p()
+        arr = (C.c_void_p * len(bufs))(*[b.data_ptr() for b in bufs])
+        nbytes = bufs[0].numel() * bufs[0].element_size()
+        self.check(self.L.inkq_peerset_from_pointers(self.h, len(bufs), rank, arr, C.c_size_t(nbytes), C.byref(h)))
+        return PeerSet(self, h, len(bufs), rank, list(bufs))
+
+    def linear_scatter(self, w, x, M: int, ps, byte_offset: int, ldc: int):
+        """inkq_linear whose epilogue stores the shard's columns into every rank's buffer of the peer set."""
+        self.check(self.L.inkq_linear_scatter(self.h, w.h, _dp(x), M, ps.h, C.c_size_t(byte_offset), ldc))
+
+    def peer_barrier(self, ps, timeout_ms: int = 2000):
+        self.check(self.L.inkq_peer_barrier(self.h, ps.h, timeout_ms))
 
     def linear_m1_static(self, w, x, Cdev):
         """M == 1 forward that never allocates: scratch in the library's fixed device array (K <= 16384)."""

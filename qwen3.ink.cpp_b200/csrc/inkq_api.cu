@@ -585,6 +585,13 @@ static int ensure_scratch_act(inkq_ctx *ctx, int M, int K)
 
 int inkq_linear(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, int M, float *C_dev, int ldc)
 {
+    return inkq::linear_impl(ctx, w, x_dev, M, C_dev, ldc, nullptr);
+}
+
+}  // extern "C"
+
+int inkq::linear_impl(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, int M, float *C_dev, int ldc, const ExtraDst *extra)
+{
     int rc = use(ctx);
     if (rc) return rc;
     INKQ_REQUIRE(ctx, w != nullptr && x_dev != nullptr && C_dev != nullptr, "null handle, input or output");
@@ -597,9 +604,11 @@ int inkq_linear(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, int M, 
     if (w->scheme == INKQ_A81W41) qmode = (M > 1) ? INKQ_Q8_1_F32 : INKQ_Q8_1_F16;  // QwenOperator.cc:96-120
     else qmode = INKQ_Q8_0_F16;
     if ((rc = inkq_quantize(ctx, qmode, x_dev, M, w->K, act))) return rc;
-    if (M > 1) return launch_gemm_tc(ctx, act, w, C_dev, ldc, nullptr);
-    return launch_gemv(ctx, act, w, C_dev);
+    if (M > 1) return launch_gemm_tc(ctx, act, w, C_dev, ldc, nullptr, extra);
+    return launch_gemv(ctx, act, w, C_dev, extra);
 }
+
+extern "C" {
 
 int inkq_linear_host(inkq_ctx *ctx, const inkq_weight *w, const float *x_host, int M, float *C_host, int ldc)
 {

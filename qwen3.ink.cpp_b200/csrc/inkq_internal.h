@@ -61,6 +61,22 @@ struct Act {
     int32_t *isum;
 };
 
+// Further destinations of an output matrix: the same element offset is stored through every pointer
+// (other GPUs' mapped buffers of a column-sharded layer, or other local buffers).
+constexpr int MAX_PEERS = 8;
+struct ExtraDst {
+    float *p[MAX_PEERS - 1];
+    int n;
+};
+
+struct PeerSet {
+    inkq_ctx *ctx;
+    int world, rank;
+    size_t bytes;
+    char *ptr[MAX_PEERS];    // every rank's buffer as mapped into this process (ptr[rank] = the local one)
+    void *opened[MAX_PEERS]; // base addresses returned by cudaIpcOpenMemHandle (null for local / caller-mapped)
+};
+
 struct F16W {
     inkq_ctx *ctx;
     int rows, K;
@@ -88,6 +104,7 @@ struct inkq_ctx {
 struct inkq_weight : inkq::Weight {};
 struct inkq_act : inkq::Act {};
 struct inkq_f16w : inkq::F16W {};
+struct inkq_peerset : inkq::PeerSet {};
 
 namespace inkq {
 
@@ -114,11 +131,13 @@ int launch_quantize(inkq_ctx *ctx, int qmode, const float *x, int M, int K, Act 
 int launch_block_isum(inkq_ctx *ctx, Act *a, int M, int M_ld);
 int launch_retile(inkq_ctx *ctx, Weight *w, const uint8_t *nib, const float *d, const float *m, const uint8_t *zp, int n_begin);
 int launch_export(inkq_ctx *ctx, const Weight *w, uint8_t *nib, float *d, float *m, uint8_t *zp);
-int launch_gemv(inkq_ctx *ctx, const Act *a, const Weight *w, float *C);
+int launch_gemv(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, const ExtraDst *extra = nullptr);
 int launch_gemm_simt(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc);
 int launch_block_dots(inkq_ctx *ctx, const Act *a, const Weight *w, int32_t *dots);
-int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc, int32_t *dots);
+int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc, int32_t *dots, const ExtraDst *extra = nullptr);
 int launch_gemm_w41_f16(inkq_ctx *ctx, const uint16_t *a16, int M, const Weight *w, float *C, int ldc);
+// inkq_linear with further destinations for every output element (defined in inkq_api.cu)
+int linear_impl(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, int M, float *C_dev, int ldc, const ExtraDst *extra);
 int launch_f16w_matmul(inkq_ctx *ctx, const F16W *w, const float *x, int M, float *C, int ldc);
 
 }  // namespace inkq

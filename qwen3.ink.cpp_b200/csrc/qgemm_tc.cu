@@ -81,6 +81,7 @@ struct TcParams {
     const uint2 *sc16;
     const uchar2 *zpT;
     float *C;
+    ExtraDst extra;  // further destinations of every C element (peers of a column-sharded layer)
     int32_t *dots;   // non-null: dump raw int32 block dots [M][rows][K/32] instead of computing C
     int *flag;
     int M, M_ld, rows, K, pairs, tiles_n, tiles_m, block_m, ldc;
@@ -584,6 +585,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     const int m = tm * BLOCK_M + col0 + j;
                     if (m < prm.M) prm.C[static_cast<size_t>(m) * prm.ldc + n] = accf[j];
                 }
+                for (int e = 0; e < prm.extra.n; e++) {
+                    float *__restrict__ Ce = prm.extra.p[e];
+#pragma unroll
+                    for (int j = 0; j < CW; j++) {
+                        const int m = tm * BLOCK_M + col0 + j;
+                        if (m < prm.M) Ce[static_cast<size_t>(m) * prm.ldc + n] = accf[j];
+                    }
+                }
             }
         }
 #ifdef INKQ_ROLE_TIMERS
@@ -658,7 +667,7 @@ static int encode2d(inkq_ctx *ctx, CUtensorMap *map, CUtensorMapDataType dt, int
     return INKQ_OK;
 }
 
-int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc, int32_t *dots)
+int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc, int32_t *dots, const ExtraDst *extra)
 {
     if (ctx->encode_tiled == nullptr) return fail(ctx, INKQ_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled entry point not available");
     const int M = a->M;
@@ -678,6 +687,8 @@ int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int l
     prm.sc16 = w->sc16;
     prm.zpT = w->zpT;
     prm.C = C;
+    prm.extra = ExtraDst{};
+    if (extra != nullptr) prm.extra = *extra;
     prm.dots = dots;
     prm.flag = ctx->dev_flag;
     prm.M = M;

@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_a8w4(c
                                                                const uchar2 *__restrict__ zpT, const int8_t *__restrict__ q,
                                                                const float *__restrict__ d, const float *__restrict__ s,
                                                                const int32_t *__restrict__ isum, int M_ld, float *__restrict__ C,
-                                                               int rows, int K, int pairs)
+                                                               int rows, int K, int pairs, const ExtraDst extra)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int nb = K / QK;
@@ -159,12 +159,15 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_a8w4(c
 #pragma unroll
         for (int w2 = 1; w2 < WARPS; w2++) tot = __fadd_rn(tot, part[w2 * 32 + lane]);
         const int n = t * TILE_N + r;
-        if (n < rows) C[n] = tot;
+        if (n < rows) {
+            C[n] = tot;
+            for (int e = 0; e < extra.n; e++) extra.p[e][n] = tot;   // column-sharded layer: the same element in every peer's buffer
+        }
     }
 }
 
 template <bool HAS_MIN, int WARPS>
-static void launch_gemv_variant(inkq_ctx *ctx, const Act *a, const Weight *w, float *C)
+static void launch_gemv_variant(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, const ExtraDst &extra)
 {
     const size_t smem = static_cast<size_t>(w->K) + 2 * sizeof(float) * (w->K / QK) + sizeof(float) * WARPS * 32;
     if (smem > 48 * 1024) cudaFuncSetAttribute(k_qgemv_a8w4<HAS_MIN, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -182,19 +185,21 @@ static void launch_gemv_variant(inkq_ctx *ctx, const Act *a, const Weight *w, fl
     cfg.numAttrs = 1;
     cudaLaunchKernelEx(&cfg, k_qgemv_a8w4<HAS_MIN, WARPS>, static_cast<const uint8_t *>(w->nibT), static_cast<const uint2 *>(w->sc16),
                        static_cast<const uchar2 *>(w->zpT), static_cast<const int8_t *>(a->q), static_cast<const float *>(a->d),
-                       static_cast<const float *>(a->s), static_cast<const int32_t *>(a->isum), a->M_ld, C, w->rows, w->K, w->pairs);
+                       static_cast<const float *>(a->s), static_cast<const int32_t *>(a->isum), a->M_ld, C, w->rows, w->K, w->pairs, extra);
 }
 
-int launch_gemv(inkq_ctx *ctx, const Act *a, const Weight *w, float *C)
+int launch_gemv(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, const ExtraDst *extra_in)
 {
+    ExtraDst extra = {};
+    if (extra_in != nullptr) extra = *extra_in;
     // narrow layers (few CTAs) or long rows: 16 K-slices per CTA
     const bool wide_cta = (w->tiles * 4 <= 2 * ctx->num_sms) || (w->pairs >= 128);
     if (w->scheme == INKQ_A81W41) {
-        if (wide_cta) launch_gemv_variant<true, 16>(ctx, a, w, C);
-        else launch_gemv_variant<true, 8>(ctx, a, w, C);
+        if (wide_cta) launch_gemv_variant<true, 16>(ctx, a, w, C, extra);
+        else launch_gemv_variant<true, 8>(ctx, a, w, C, extra);
     } else {
-        if (wide_cta) launch_gemv_variant<false, 16>(ctx, a, w, C);
-        else launch_gemv_variant<false, 8>(ctx, a, w, C);
+        if (wide_cta) launch_gemv_variant<false, 16>(ctx, a, w, C, extra);
+        else launch_gemv_variant<false, 8>(ctx, a, w, C, extra);
     }
     return after_launch(ctx, "k_qgemv_a8w4");
 }

@@ -6,6 +6,14 @@ weight rows [r*N/P, (r+1)*N/P), every rank quantizes the full activations itself
 all-gather of the fp32 [M][N/P] shards assembles the output on every rank.  Per-column
 arithmetic is identical at every rank count, so the gathered result equals the 1-GPU result
 bit for bit.  Works with any torch.distributed backend (NCCL on GPUs, gloo in the CPU tests).
+
+Two ways to do the exchange:
+  ColumnGather  kernel writes its shard locally, then one all-gather (the library collective) and a
+                re-layout copy;
+  PeerScatter   the matmul's epilogue stores each finished element into every rank's [M][N] buffer
+                through peer-mapped pointers (csrc/peer.cu), followed by a small barrier kernel; no
+                collective call and no re-layout.  torch.distributed only carries the 80-byte buffer
+                handles at set-up.
 """
 from __future__ import annotations
 
@@ -40,3 +48,68 @@ class ColumnGather:
         # [P][M][N/P] -> [M][P][N/P] = [M][N]
         self.full.view(self.M, self.world, self.n_loc).copy_(self.stacked.permute(1, 0, 2))
         return self.full
+
+
+def scatter_offset(slot: int, M: int, N: int, n_begin: int, reserved: int = 256) -> int:
+    """Byte offset, inside every rank's peer buffer, of element [0][n_begin] of output slot `slot`
+    ([slots][M][N] fp32 after the reserved head)."""
+    return reserved + 4 * (slot * M * N + n_begin)
+
+
+class PeerScatter:
+    """[slots][M][N] fp32 output buffers, one per rank, each mapped into every rank's process.
+
+    `linear(w_shard, x, slot)` runs quantize + QGEMM/QGEMV on the rank's weight rows and stores the
+    columns [n_begin, n_end) of slot `slot` on every rank; `barrier()` completes the exchange;
+    `result(slot)` is then the full [M][N] matrix.  Alternate two slots between consecutive steps."""
+
+    def __init__(self, pkg, ctx, dist, M: int, N: int, world: int, rank: int, slots: int = 2):
+        import torch
+        self.pkg, self.ctx, self.dist, self.M, self.N, self.world, self.rank, self.slots = pkg, ctx, dist, M, N, world, rank, slots
+        self.n_begin, self.n_end = shard_range(N, world, rank)
+        nbytes = pkg.PEER_RESERVED_BYTES + 4 * slots * M * N
+        self.buf = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")      # zero head: the barrier counters start at 0
+        torch.cuda.synchronize()
+        # Set-up is collective: every rank takes part in both exchanges whatever happened locally, and all
+        # ranks raise together, so that a caller can fall back to ColumnGather without a rank left behind.
+        err = None
+        try:
+            blob = ctx.peer_export(self.buf)
+        except Exception as e:           # e.g. an allocator whose memory CUDA IPC cannot export
+            err, blob = e, b""
+        blobs = self._all_gather(blob)
+        self.ps = None
+        if all(len(b) == pkg.PEER_HANDLE_BYTES for b in blobs):
+            try:
+                self.ps = ctx.peerset_open(world, rank, self.buf, blobs)
+            except Exception as e:
+                err = e
+        oks = self._all_gather(self.ps is not None)
+        if not all(oks):
+            if self.ps is not None:
+                self.ps.close()
+            raise RuntimeError(f"peer buffers could not be mapped on every rank (this rank: {err!r})")
+        self.out = self.buf[pkg.PEER_RESERVED_BYTES:].view(torch.float32).view(slots, M, N)
+
+    def _all_gather(self, obj):
+        if self.world == 1:
+            return [obj]
+        out = [None] * self.world
+        self.dist.all_gather_object(out, obj)
+        return out
+
+    def linear(self, w, x, slot: int):
+        self.ctx.linear_scatter(w, x, self.M, self.ps, scatter_offset(slot, self.M, self.N, self.n_begin, self.pkg.PEER_RESERVED_BYTES), self.N)
+
+    def barrier(self, timeout_ms: int = 2000):
+        if self.world > 1:
+            self.ctx.peer_barrier(self.ps, timeout_ms)
+
+    def result(self, slot: int):
+        return self.out[slot]
+
+    def close(self):
+        if self.world > 1:
+            self.ctx.synchronize()
+            self.dist.barrier()   # nobody unmaps while a peer may still store
+        self.ps.close()

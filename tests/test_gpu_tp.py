@@ -1,5 +1,6 @@
 """GPU, 2 ranks over NCCL (skipped on a single-GPU box): the column-sharded CUDA linear layer,
-gathered, equals the unsharded 1-GPU result bit for bit."""
+gathered by NCCL or scattered by the kernels' own peer stores, equals the unsharded 1-GPU result
+bit for bit."""
 import os
 import socket
 import sys
@@ -41,6 +42,26 @@ def _worker(rank, world, port, out_dir):
     ctx.linear(whole, x, M, ref, N)
     ctx.synchronize()
     ok = bool(torch.equal(full, ref))
+    # the same exchange done by the kernels' epilogues through peer-mapped buffers + barrier kernel
+    sc = pkg.tp.PeerScatter(pkg, ctx, dist, M, N, world, rank, slots=2)
+    for step in range(4):
+        sc.linear(wh, x, step % 2)
+        sc.barrier()
+        ctx.synchronize()
+        ok = ok and bool(torch.equal(sc.result(step % 2), ref))
+        sc.result(step % 2).zero_()
+        torch.cuda.synchronize()
+        dist.barrier()           # the zeroing above must not overtake a peer's check (test only)
+    # decode path (QGEMV epilogue) through the same buffers
+    sc1 = pkg.tp.PeerScatter(pkg, ctx, dist, 1, N, world, rank, slots=2)
+    ref1 = torch.empty((1, N), device="cuda")
+    ctx.linear(whole, x[:1], 1, ref1, N)
+    sc1.linear(wh, x[:1], 0)
+    sc1.barrier()
+    ctx.synchronize()
+    ok = ok and bool(torch.equal(sc1.result(0), ref1))
+    sc1.close()
+    sc.close()
     with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
         f.write("ok" if ok else "mismatch")
     dist.barrier()

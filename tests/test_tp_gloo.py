@@ -58,3 +58,18 @@ def test_shard_ranges(pkg):
     assert pkg.tp.shard_range(151936, 8, 7) == (132944, 151936)
     with pytest.raises(ValueError):
         pkg.tp.shard_range(12288 + 8, 8, 0)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_scatter_offsets_tile_every_slot_exactly_once(pkg, world):
+    """The byte ranges the ranks' epilogues store to (row m of slot s: scatter_offset + 4*m*N .. + 4*n_loc)
+    cover [slots][M][N] after the reserved head exactly once."""
+    M, N, slots = 5, 64 * world, 2
+    hit = np.zeros(pkg.PEER_RESERVED_BYTES + 4 * slots * M * N, np.int32)
+    for s in range(slots):
+        for r in range(world):
+            n0, n1 = pkg.tp.shard_range(N, world, r)
+            off = pkg.tp.scatter_offset(s, M, N, n0, pkg.PEER_RESERVED_BYTES)
+            for m in range(M):
+                hit[off + 4 * m * N: off + 4 * (m * N + n1 - n0)] += 1
+    assert (hit[:pkg.PEER_RESERVED_BYTES] == 0).all() and (hit[pkg.PEER_RESERVED_BYTES:] == 1).all()
