@@ -195,6 +195,8 @@ int inkq_peer_barrier(inkq_ctx *ctx, inkq_peerset *ps, int timeout_ms);
  * notebooks/evaluate-qwen3_8b_W4.ipynb cell 13 and, for lm_head, the fp32 GEMV
  * gemv_fp32_rcr_mt_impl_1 (qwen3/src/qwen/fp32_gemx_kernels_rcr.cc:494-507). */
 int inkq_gemm_w41_f16act(inkq_ctx *ctx, const uint16_t *a16_dev, int M, const inkq_weight *w, float *C_dev, int ldc);
+/* The same matmul on the CUDA cores, k ascending (cross-check of the tensor-core kernel above; slow). */
+int inkq_gemm_w41_f16act_simt(inkq_ctx *ctx, const uint16_t *a16_dev, int M, const inkq_weight *w, float *C_dev, int ldc);
 int inkq_f16w_create(inkq_ctx *ctx, int N, int K, const uint16_t *w16_host, int n_begin, int n_end, inkq_f16w **out);
 int inkq_f16w_create_dev(inkq_ctx *ctx, int N, int K, const uint16_t *w16_dev, int n_begin, int n_end, inkq_f16w **out);
 int inkq_f16w_destroy(inkq_f16w *w);

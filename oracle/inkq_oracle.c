@@ -360,9 +360,25 @@ void ink_gemm_a8w4_samples(int scheme, int N, int K,
 /*
  * Weight-only W41 (evaluate-qwen3_8b_W4.ipynb cell 13): the fp16 model's weight
  * is replaced by the dequantised value w = q*d + m held in fp16, then a stock
- * fp16 linear runs.  Restated as: w16 = fp16(fmaf(q, d, m)); C = sum_k a16*w16
- * accumulated in fp32, k ascending.  a is given as fp16 bit patterns.
+ * fp16 linear runs.  Restated as: w16 = fp16(q*d + m) with d, m the fp16-rounded
+ * block scale and minimum and ONE rounding of the exact value (what a half-precision
+ * fused multiply-add returns); C = sum_k a16*w16 accumulated in fp32, k ascending.
+ * a is given as fp16 bit patterns.
  */
+/* Nearest fp16 (ties to even) of a double that holds an exact value, returned as float. */
+static float round_f16_exact(double v)
+{
+    if (v == 0.0) return 0.0f;
+    int e;
+    (void)frexp(fabs(v), &e);                /* |v| = f * 2^e, f in [0.5, 1) */
+    int ulp_exp = (e - 1) - 10;              /* fp16 keeps 11 significant bits */
+    if (ulp_exp < -24) ulp_exp = -24;        /* subnormal grid */
+    const double r = nearbyint(ldexp(v, -ulp_exp));   /* exact scaling; default rounding mode = ties to even */
+    double out = ldexp(r, ulp_exp);
+    if (fabs(out) > 65504.0) out = copysign(INFINITY, v);
+    return (float)out;
+}
+
 void ink_gemm_w41_f16act(int M, int N, int K, const uint16_t *a16,
                          const uint8_t *nib, const float *d_w, const float *m_w,
                          float *C, int ldc)
@@ -375,8 +391,9 @@ void ink_gemm_w41_f16act(int M, int N, int K, const uint16_t *a16,
             for (int e = 0; e < 32; e++) {
                 const uint8_t byte = nib[(size_t)n * (K / 2) + g * 32 + e];
                 const size_t wb = (size_t)n * nbk + 2 * g;
-                w[g * 64 + e] = round_f16(fmaf((float)(byte & 0x0f), d_w[wb], m_w[wb]));
-                w[g * 64 + 32 + e] = round_f16(fmaf((float)(byte >> 4), d_w[wb + 1], m_w[wb + 1]));
+                /* q*d + m is exact in double (4 + 11 + 11 significant bits within fp16's exponent range) */
+                w[g * 64 + e] = round_f16_exact((double)(byte & 0x0f) * (double)round_f16(d_w[wb]) + (double)round_f16(m_w[wb]));
+                w[g * 64 + 32 + e] = round_f16_exact((double)(byte >> 4) * (double)round_f16(d_w[wb + 1]) + (double)round_f16(m_w[wb + 1]));
             }
         for (int i = 0; i < M; i++) {
             float acc = 0.0f;

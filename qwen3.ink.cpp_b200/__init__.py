@@ -33,7 +33,7 @@ SYMBOLS = [
     "inkq_launch_count", "inkq_weight_create", "inkq_weight_create_dev", "inkq_weight_destroy", "inkq_weight_info",
     "inkq_weight_export", "inkq_act_create", "inkq_act_destroy", "inkq_quantize", "inkq_act_export", "inkq_act_import", "inkq_quantize_host", "inkq_gemm_host", "inkq_gemv_host", "inkq_gemm",
     "inkq_gemv", "inkq_gemm_simt", "inkq_debug_block_dots", "inkq_debug_block_dots_tc", "inkq_linear",
-    "inkq_linear_host", "inkq_linear_m1_static", "inkq_gemm_w41_f16act", "inkq_f16w_create", "inkq_f16w_create_dev", "inkq_f16w_destroy",
+    "inkq_linear_host", "inkq_linear_m1_static", "inkq_gemm_w41_f16act", "inkq_gemm_w41_f16act_simt", "inkq_f16w_create", "inkq_f16w_create_dev", "inkq_f16w_destroy",
     "inkq_f16w_matmul", "inkq_peer_export", "inkq_peerset_open", "inkq_peerset_from_pointers", "inkq_peerset_destroy",
     "inkq_linear_scatter", "inkq_peer_barrier",
 ]
@@ -251,6 +251,10 @@ class Context:
 
     def gemm_w41_f16act(self, a16, M: int, w, Cdev, ldc: int):
         self.check(self.L.inkq_gemm_w41_f16act(self.h, _dp(a16), M, w.h, _dp(Cdev), ldc))
+
+    def gemm_w41_f16act_simt(self, a16, M: int, w, Cdev, ldc: int):
+        """CUDA-core cross-check of gemm_w41_f16act (slow)."""
+        self.check(self.L.inkq_gemm_w41_f16act_simt(self.h, _dp(a16), M, w.h, _dp(Cdev), ldc))
 
     def f16w_matmul(self, w, x, M: int, Cdev, ldc: int):
         self.check(self.L.inkq_f16w_matmul(self.h, w.h, _dp(x), M, _dp(Cdev), ldc))

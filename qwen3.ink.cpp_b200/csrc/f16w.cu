@@ -106,8 +106,9 @@ int launch_f16w_matmul(inkq_ctx *ctx, const F16W *w, const float *x, int M, floa
     return INKQ_OK;
 }
 
-// Weight-only W41 on the CUDA cores: one output per thread, k ascending, fp32
-// accumulate: acc = fma(a16[k], fp16(q*d + m), acc).
+// Weight-only W41 on the CUDA cores (cross-check of the tensor-core kernel): one output per thread,
+// k ascending, fp32 accumulate: acc = fma(a16[k], w16, acc) with w16 = the half-precision fma q*d + m
+// (one rounding), d and m the layer's fp16 scales.
 __global__ void __launch_bounds__(256) k_gemm_w41_f16act(Weight w, const __half *__restrict__ a, int M, float *__restrict__ C, int ldc)
 {
     const int n = blockIdx.x * 32 + (threadIdx.x & 31);
@@ -120,23 +121,16 @@ __global__ void __launch_bounds__(256) k_gemm_w41_f16act(Weight w, const __half 
         const uint4 c0 = *reinterpret_cast<const uint4 *>(w.nibT + nib_offset(w.pairs, t, p, r, 0));
         const uint4 c1 = *reinterpret_cast<const uint4 *>(w.nibT + nib_offset(w.pairs, t, p, r, 1));
         const size_t rec = (static_cast<size_t>(t) * w.pairs + p) * TILE_N + r;
-        float4 sc;
-        if (w.sc32 != nullptr) {
-            sc = w.sc32[rec];
-        } else {
-            const uint2 pk = w.sc16[rec];
-            const float2 x0 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.x));
-            const float2 x1 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.y));
-            sc = make_float4(x0.x, x0.y, x1.x, x1.y);
-        }
+        const uint2 pk = w.sc16[rec];
+        const __half2 d2 = *reinterpret_cast<const __half2 *>(&pk.x), m2 = *reinterpret_cast<const __half2 *>(&pk.y);
         const uint32_t wd[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
         for (int hi = 0; hi < 2; hi++) {
-            const float dd = hi ? sc.y : sc.x, mm = hi ? sc.w : sc.z;
+            const __half dd = hi ? __high2half(d2) : __low2half(d2), mm = hi ? __high2half(m2) : __low2half(m2);
 #pragma unroll
             for (int e = 0; e < 32; e++) {
                 const uint32_t nibble = (wd[e >> 2] >> (8 * (e & 3) + 4 * hi)) & 0xf;
-                const float wv = __half2float(__float2half_rn(fmaf(static_cast<float>(nibble), dd, mm)));
+                const float wv = __half2float(__hfma(__ushort2half_rn(static_cast<unsigned short>(nibble)), dd, mm));
                 acc = fmaf(__half2float(arow[p * 64 + hi * 32 + e]), wv, acc);
             }
         }

@@ -634,6 +634,16 @@ int inkq_gemm_w41_f16act(inkq_ctx *ctx, const uint16_t *a16_dev, int M, const in
     INKQ_REQUIRE(ctx, w != nullptr && a16_dev != nullptr && C_dev != nullptr, "null handle, input or output");
     INKQ_REQUIRE(ctx, w->scheme == INKQ_W41 || w->scheme == INKQ_A81W41, "weight-only matmul needs Q4_1 weights");
     INKQ_REQUIRE(ctx, M >= 1 && ldc >= w->rows, "bad M or ldc");
+    return launch_gemm_w41_tc(ctx, a16_dev, M, w, C_dev, ldc);
+}
+
+int inkq_gemm_w41_f16act_simt(inkq_ctx *ctx, const uint16_t *a16_dev, int M, const inkq_weight *w, float *C_dev, int ldc)
+{
+    int rc = use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, w != nullptr && a16_dev != nullptr && C_dev != nullptr, "null handle, input or output");
+    INKQ_REQUIRE(ctx, w->scheme == INKQ_W41 || w->scheme == INKQ_A81W41, "weight-only matmul needs Q4_1 weights");
+    INKQ_REQUIRE(ctx, M >= 1 && ldc >= w->rows, "bad M or ldc");
     return launch_gemm_w41_f16(ctx, a16_dev, M, w, C_dev, ldc);
 }
 

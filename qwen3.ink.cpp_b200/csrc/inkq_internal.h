@@ -135,7 +135,8 @@ int launch_gemv(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, const Ex
 int launch_gemm_simt(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc);
 int launch_block_dots(inkq_ctx *ctx, const Act *a, const Weight *w, int32_t *dots);
 int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc, int32_t *dots, const ExtraDst *extra = nullptr);
-int launch_gemm_w41_f16(inkq_ctx *ctx, const uint16_t *a16, int M, const Weight *w, float *C, int ldc);
+int launch_gemm_w41_f16(inkq_ctx *ctx, const uint16_t *a16, int M, const Weight *w, float *C, int ldc);   // CUDA cores
+int launch_gemm_w41_tc(inkq_ctx *ctx, const uint16_t *a16, int M, const Weight *w, float *C, int ldc);    // tcgen05 kind::f16
 // inkq_linear with further destinations for every output element (defined in inkq_api.cu)
 int linear_impl(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, int M, float *C_dev, int ldc, const ExtraDst *extra);
 int launch_f16w_matmul(inkq_ctx *ctx, const F16W *w, const float *x, int M, float *C, int ldc);

@@ -3,6 +3,7 @@
     python qwen3.ink.cpp_b200/profile_case.py qgemm [M]       # k_qgemm_tc, N=12288, K=4096 (default M=322)
     python qwen3.ink.cpp_b200/profile_case.py qgemv [N] [K]   # k_qgemv_a8w4 (default 12288 x 4096), 12 distinct weight sets
     python qwen3.ink.cpp_b200/profile_case.py quantize [M]    # k_quantize_q8, K=4096 (default M=8192)
+    python qwen3.ink.cpp_b200/profile_case.py w41 [M]         # k_gemm_w41_tc, N=12288, K=4096 (default M=2048); prints its time
 
 Typical capture (one kernel, one launch, after the same command has exited 0 without ncu):
     ncu --set full --clock-control none -k regex:k_qgemm_tc -s 1 -c 1 -o prof python qwen3.ink.cpp_b200/profile_case.py qgemm
@@ -54,6 +55,23 @@ def main():
             ctx.quantize(act, x, M, pkg.Q8_1_F32)
         ctx.synchronize()
         print("quantize ok", M, K)
+    elif what == "w41":
+        M, N, K = (args + [2048])[0], 12288, 4096
+        w = pkg.synth.weights(N, K)
+        wh = ctx.weight(pkg.W41, pkg.SCALES_F16, w["nib"], w["d"], w["m"])
+        a16 = torch.from_numpy(pkg.synth.activations(M, K)).cuda().half()
+        C = torch.empty((M, N), device="cuda")
+        for _ in range(3):
+            ctx.gemm_w41_f16act(a16, M, wh, C, N)
+        ctx.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(10):
+            ctx.gemm_w41_f16act(a16, M, wh, C, N)
+        b.record()
+        ctx.synchronize()
+        us = a.elapsed_time(b) * 100
+        print(f"w41 ok {M} {N} {K} mean|C| {float(C.abs().mean()):.4f}  {us:.1f} us per launch, {2.0 * M * N * K / us / 1e6:.1f} TFLOP/s")
     else:
         raise SystemExit("unknown case " + what)
 
