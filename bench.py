@@ -35,7 +35,7 @@ from __graft_entry__ import load_package  # noqa: E402
 
 M_PP, K_PP, N_PP = 322, 4096, 12288
 GEMV_SHAPES = [("q_proj/o_proj", 4096, 4096), ("k_proj/v_proj", 1024, 4096), ("gate/up_proj", 12288, 4096),
-               ("down_proj", 4096, 12288), ("qkv_fused", 6144, 4096)]
+               ("down_proj", 4096, 12288), ("qkv_fused", 6144, 4096), ("gate_up_fused", 24576, 4096)]
 L2_BYTES = 126e6
 
 
@@ -235,6 +235,80 @@ def gemv_sweep(pkg, torch, ctx, peak_gbs, iters=200):
     return out
 
 
+# --------------------------------------------------------------------------- scheme matrix and fp16 lm_head (extra figures)
+def graph_time_us(torch, ctx, calls, reps=5):
+    """Average device time of one call when the list of calls runs as one CUDA graph (launch gaps excluded)."""
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        ctx.set_stream(s.cuda_stream)
+        for c in calls:
+            c()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=s):
+            for c in calls:
+                c()
+    ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+    g.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        g.replay()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / (reps * len(calls))
+
+
+def scheme_matrix(pkg, torch, ctx, pk):
+    """The layer's forward (quantizer + matmul, one call of inkq_linear; weight-only W41: fp16 activations into the
+    tensor-core matmul) for every scheme at M in {1, 322, 2048}, K=4096, N=12288, rotating 6 weight sets (> L2)."""
+    K, N, sets = K_PP, N_PP, 6
+    wt = pkg.synth.weights(N, K)
+    zp = wt["zp"]
+    out = []
+    for name, scheme in (("A81W41", pkg.A81W41), ("A80W40", pkg.A80W40), ("A80W4Z", pkg.A80W4Z), ("W41", pkg.W41)):
+        m = wt["m"] if scheme in (pkg.A81W41, pkg.W41) else None
+        z = zp if scheme == pkg.A80W4Z else None
+        ws = [ctx.weight(scheme, pkg.SCALES_F16, wt["nib"], wt["d"], m, z) for _ in range(sets)]
+        for M in (1, 322, 2048):
+            x = torch.randn((M, K), device="cuda")
+            x16 = x.half()
+            C = torch.empty((M, N), device="cuda")
+            if scheme == pkg.W41:
+                calls = [(lambda w=w: ctx.gemm_w41_f16act(x16, M, w, C, N)) for w in ws]
+            else:
+                calls = [(lambda w=w: ctx.linear(w, x, M, C, N)) for w in ws]
+            us = graph_time_us(torch, ctx, calls)
+            row = {"scheme": name, "M": M, "us": round(us, 2), "TOPS": round(2.0 * M * N * K / us / 1e6, 2)}
+            if M == 1:
+                bpw = {"A81W41": 0.625, "A80W40": 0.5625 + 1 / 32, "A80W4Z": 0.5625 + 1 / 32, "W41": 0.625}[name]   # zero-point byte per block
+                row["GBs"] = round(N * K * bpw / us / 1e3, 1)
+                row["frac_of_hbm"] = round(row["GBs"] / pk["hbm_gbs"], 4)
+            else:
+                peak = pk["bf16_tflops"] * (1.0 if scheme == pkg.W41 else 2.0)
+                row["frac_of_tensor_peak"] = round(row["TOPS"] / peak, 4)
+            out.append(row)
+        for h in ws:
+            h.close()
+    return out
+
+
+def lm_head_gemv(pkg, torch, ctx, pk, vocab=151936, K=4096):
+    """fp16 lm_head for one token (1.245 GB of weights per launch: far larger than L2)."""
+    w16 = (torch.randn((vocab, K), device="cuda") * 0.02).half()
+    wh = ctx.f16w_dev(w16, vocab, K)
+    del w16
+    x = torch.randn((1, K), device="cuda")
+    C = torch.empty((1, vocab), device="cuda")
+    us = graph_time_us(torch, ctx, [lambda: ctx.f16w_matmul(wh, x, 1, C, vocab)] * 4)
+    wh.close()
+    nbytes = vocab * K * 2 + K * 4 + vocab * 4
+    return {"shape": "lm_head fp16", "N": vocab, "K": K, "us": round(us, 2), "GBs": round(nbytes / us / 1e3, 1),
+            "frac_of_hbm": round(nbytes / us / 1e3 / pk["hbm_gbs"], 4)}
+
+
 # --------------------------------------------------------------------------- synthetic Qwen3-8B forward (pp322 / tg128)
 def model_pp_tg(pkg, torch, ctx, prompt_len=322, new_tokens=128, reps=3):
     """Prompt prefill and greedy decode of the synthetic Qwen3-8B (random-init A81W41 weights with fp16 block
@@ -262,12 +336,31 @@ def model_pp_tg(pkg, torch, ctx, prompt_len=322, new_tokens=128, reps=3):
         pp_ms.append(a.elapsed_time(b))
         tg_ms.append(b.elapsed_time(c))
     n_gen = len(model.generated_tokens())
+    # the same decode step with every operator as its own launch (17 per layer), for comparison
+    unfused_ms = None
+    launches_per_token = 6 * cfg.layers + 4 if cfg.fused_decode else 17 * cfg.layers + 4
+    if cfg.fused_decode:
+        model.cfg.fused_decode = False
+        model.reset()
+        model.prefill(prompt)
+        model.decode_step()
+        model.capture_decode()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(new_tokens):
+            model.graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        unfused_ms = a.elapsed_time(b) / new_tokens
     pp, tg = prompt_len / (min(pp_ms) * 1e-3), new_tokens / (min(tg_ms) * 1e-3)
     w_bytes = cfg.layers * ((cfg.nq + 2 * cfg.nkv) * 128 * cfg.hidden + cfg.hidden * cfg.nq * 128 + 3 * cfg.hidden * cfg.ffn) * 0.625 \
         + cfg.vocab * cfg.hidden * 2
     out = {"pp322_tok_s": pp, "tg128_tok_s": tg, "prefill_ms": min(pp_ms), "decode_ms_per_token": min(tg_ms) / new_tokens,
            "tokens_generated_last_rep": int(n_gen), "decode_weight_bytes_per_token": w_bytes,
            "decode_GBs": w_bytes / (min(tg_ms) / new_tokens * 1e-3) / 1e9,
+           "decode_launches_per_token": launches_per_token,
+           "decode_ms_per_token_unfused_kernels": unfused_ms,
            "published_reference_cpu": {"pp322_tok_s": 134.35, "tg128_tok_s": 9.26, "hardware": "Intel i5-13600KF, 16 threads (reference README)"},
            "vs_published": {"pp322": pp / 134.35, "tg128": tg / 9.26},
            "config": "Qwen3-8B shape: 36 layers, hidden 4096, 32q/8kv heads x128, ffn 12288, vocab 151936; A81W41 fp16 scales, fp16 lm_head and KV cache; "
@@ -385,7 +478,10 @@ def run_ours(args, rank, world, local_rank):
         ach = 2.0 * M * n_loc * K / (ms_g * 1e-3) / 1e12
         int8_peak = 2.0 * pk["bf16_tflops"]
         line["roofline"] = {"bound": "tensor", "achieved": ach, "peak": int8_peak, "unit": "TOP/s", "frac": ach / int8_peak,
-                            "traffic": None, "kernel": "k_qgemm_tc", "us_per_launch": ms_g * 1e3,
+                            "traffic": 41.12e6 if (wl in ("qgemm_pp322", "qgemv_sweep") and world == 1) else None,
+                            "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one launch at this shape (ncu capture summarised under "
+                                            "profiles/): 41.01 MB read = the compulsory operand bytes, 0.11 MB written (the 15.8 MB result stays in L2)",
+                            "kernel": "k_qgemm_tc", "us_per_launch": ms_g * 1e3,
                             "peak_note": f"2 x the {pk['source']} dense bf16 figure ({pk['bf16_tflops']} TFLOP/s); int8 itself is not in MEASURED_PEAKS.json",
                             "cuda_core_note": "every K=32 MMA is followed by an fp32 scale+accumulate of its whole tile on the CUDA cores "
                                               "(M*N*K/32 block dots per launch); that, not the tensor pipe, bounds this kernel"}
@@ -415,6 +511,8 @@ def run_ours(args, rank, world, local_rank):
                 h.close()
             ws = []
             line["gemv"] = gemv_sweep(pkg, torch, ctx, pk["hbm_gbs"])
+            line["gemv"].append(lm_head_gemv(pkg, torch, ctx, pk))
+            line["scheme_matrix"] = scheme_matrix(pkg, torch, ctx, pk)
         if world == 1 and args.model:
             try:
                 line["model"] = model_pp_tg(pkg, torch, ctx)

@@ -35,6 +35,15 @@ int inkq_glue_attention(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cac
                         int nq, int nkv, int max_pos, float scale, float *out_dev);
 /* out = silu(gate) * up.  Qwen3SiLuMul, qwen3/src/qwen/QwenOperator.cc:697-722 */
 int inkq_glue_silu_mul(inkq_ctx *ctx, const float *gate_dev, const float *up_dev, long long n, float *out_dev);
+/* The same on the output of a fused gate_up projection: gu [T][2F] (gate columns first), out [T][F]. */
+int inkq_glue_silu_mul_rows(inkq_ctx *ctx, const float *gu_dev, int T, int F, float *out_dev);
+/* One decode-step layer in one launch (no counterpart in the reference, which runs these as separate
+ * operators: QwenDecoderLayer.cc:66-105): the M == 1 forward of inkq_linear on
+ *   pro 0: x                      pro 1: RMSNorm(x; g, eps)          pro 2: SiLU(x[0..K)) * x[K..2K)
+ * with the activation quantizer inside the QGEMV's prologue (same arithmetic as inkq_quantize), and
+ * accumulate != 0 adding the result onto C (the residual connection) instead of overwriting it. */
+int inkq_glue_linear_m1(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, int pro, const float *g_dev, float eps, float *C_dev,
+                        int accumulate);
 /* a += b (residual).  qwen3/src/qwen/QwenDecoderLayer.cc:73,105 */
 int inkq_glue_add_inplace(inkq_ctx *ctx, float *a_dev, const float *b_dev, long long n);
 /* Greedy sampling: *token_out = argmax(logits) (first index on ties), appended to generated

@@ -15,6 +15,7 @@
 //   greedy argmax              qwen3/src/qwen/Pipeline.cc:54-62
 // Activations are fp32 row-major [tokens][features].  The position of the first token of a call
 // is read from device memory so that one captured CUDA graph serves every decode step.
+#include <cooperative_groups.h>
 #include <cuda_fp16.h>
 #include <math.h>
 
@@ -36,24 +37,29 @@ __global__ void __launch_bounds__(256) k_embedding(const __half *__restrict__ ta
     reinterpret_cast<float2 *>(out + static_cast<size_t>(t) * dim)[c] = v;
 }
 
-// one warp per row
+// one CTA per row
 __global__ void __launch_bounds__(256) k_rmsnorm(const float *__restrict__ x, const float *__restrict__ w, int rows, int dim, float eps,
                                                  float *__restrict__ y)
 {
-    const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (row >= rows) return;
+    __shared__ float red[8];
+    const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float4 *xr = reinterpret_cast<const float4 *>(x + static_cast<size_t>(row) * dim);
     float ss = 0.0f;
-    for (int i = lane; i < dim / 4; i += 32) {
+    for (int i = threadIdx.x; i < dim / 4; i += 256) {
         const float4 v = xr[i];
         ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float inv = 1.0f / sqrtf(ss / static_cast<float>(dim) + eps);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += red[i];
+    const float inv = 1.0f / sqrtf(tot / static_cast<float>(dim) + eps);
     float4 *yr = reinterpret_cast<float4 *>(y + static_cast<size_t>(row) * dim);
     const float4 *wr = reinterpret_cast<const float4 *>(w);
-    for (int i = lane; i < dim / 4; i += 32) {
+    for (int i = threadIdx.x; i < dim / 4; i += 256) {
         const float4 v = xr[i], g = wr[i];
         yr[i] = make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
     }
@@ -115,25 +121,27 @@ __global__ void __launch_bounds__(256) k_qknorm_rope_cache(const float *__restri
 // head is h / (nq / nkv).  Pass 1: one thread per key computes the scaled dot product into shared
 // memory; block max and sum; pass 2: warp w accumulates the values of keys j = w mod 4, lanes over
 // the 128 dimensions; the four partials are added in warp order.
-__global__ void __launch_bounds__(128) k_attention(const float *__restrict__ q, const __half *__restrict__ k_cache,
+template <int NT>
+__global__ void __launch_bounds__(NT) k_attention(const float *__restrict__ q, const __half *__restrict__ k_cache,
                                                    const __half *__restrict__ v_cache, const int *__restrict__ pos0_dev, int T, int nq, int nkv,
                                                    int max_pos, float scale, float *__restrict__ out)
 {
     extern __shared__ float sm[];
     float *qs = sm;                  // 128
-    float *part = sm + HEAD_DIM;     // 4 * 128
-    float *red = part + 4 * HEAD_DIM;  // 8
-    float *sc = red + 8;             // scores, nkeys
+    constexpr int NW = NT / 32;
+    float *part = sm + HEAD_DIM;        // NW * 128
+    float *red = part + NW * HEAD_DIM;  // 2 * NW
+    float *sc = red + 2 * NW;           // scores, nkeys
     const int t = blockIdx.x / nq, h = blockIdx.x % nq;
     const int kvh = h / (nq / nkv);
     const int nkeys = min(*pos0_dev + t + 1, max_pos);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    qs[tid] = q[(static_cast<size_t>(t) * nq + h) * HEAD_DIM + tid];
+    if (tid < HEAD_DIM) qs[tid] = q[(static_cast<size_t>(t) * nq + h) * HEAD_DIM + tid];
     __syncthreads();
     const __half *kb = k_cache + static_cast<size_t>(kvh) * max_pos * HEAD_DIM;
     const __half *vb = v_cache + static_cast<size_t>(kvh) * max_pos * HEAD_DIM;
     float lmax = -INFINITY;
-    for (int j = tid; j < nkeys; j += 128) {
+    for (int j = tid; j < nkeys; j += NT) {
         const uint4 *kr = reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(j) * HEAD_DIM);
         float acc = 0.0f;
 #pragma unroll 4
@@ -155,20 +163,26 @@ __global__ void __launch_bounds__(128) k_attention(const float *__restrict__ q, 
     for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
     if (lane == 0) red[warp] = lmax;
     __syncthreads();
-    const float gmax = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    float gmax = red[0];
+#pragma unroll
+    for (int i = 1; i < NW; i++) gmax = fmaxf(gmax, red[i]);
     float lsum = 0.0f;
-    for (int j = tid; j < nkeys; j += 128) {
+    for (int j = tid; j < nkeys; j += NT) {
         const float e = __expf(sc[j] - gmax);
         sc[j] = e;
         lsum += e;
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
-    if (lane == 0) red[4 + warp] = lsum;
+    if (lane == 0) red[NW + warp] = lsum;
     __syncthreads();
-    const float inv = 1.0f / (red[4] + red[5] + red[6] + red[7]);
+    float den = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NW; i++) den += red[NW + i];
+    const float inv = 1.0f / den;
     float a[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int j = warp; j < nkeys; j += 4) {
+#pragma unroll 4
+    for (int j = warp; j < nkeys; j += NW) {
         const float p = sc[j];
         const uint2 pk = reinterpret_cast<const uint2 *>(vb + static_cast<size_t>(j) * HEAD_DIM)[lane];
         const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.x));
@@ -181,8 +195,12 @@ __global__ void __launch_bounds__(128) k_attention(const float *__restrict__ q, 
 #pragma unroll
     for (int i = 0; i < 4; i++) part[warp * HEAD_DIM + lane * 4 + i] = a[i];
     __syncthreads();
-    const float o = (part[tid] + part[HEAD_DIM + tid] + part[2 * HEAD_DIM + tid] + part[3 * HEAD_DIM + tid]) * inv;
-    out[(static_cast<size_t>(t) * nq + h) * HEAD_DIM + tid] = o;
+    if (tid < HEAD_DIM) {
+        float o = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NW; i++) o += part[i * HEAD_DIM + tid];
+        out[(static_cast<size_t>(t) * nq + h) * HEAD_DIM + tid] = o * inv;
+    }
 }
 
 __global__ void __launch_bounds__(256) k_silu_mul(const float4 *__restrict__ gate, const float4 *__restrict__ up, long long n4,
@@ -195,6 +213,17 @@ __global__ void __launch_bounds__(256) k_silu_mul(const float4 *__restrict__ gat
     out[i] = make_float4(f(g.x, u.x), f(g.y, u.y), f(g.z, u.z), f(g.w, u.w));
 }
 
+// gu [T][2F] -> out [T][F]
+__global__ void __launch_bounds__(256) k_silu_mul_rows(const float4 *__restrict__ gu, int T, int F4, float4 *__restrict__ out)
+{
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= static_cast<long long>(T) * F4) return;
+    const long long t = i / F4, c = i % F4;
+    const float4 g = gu[t * 2 * F4 + c], u = gu[t * 2 * F4 + F4 + c];
+    auto f = [](float a, float b) { return a / (1.0f + __expf(-a)) * b; };
+    out[i] = make_float4(f(g.x, u.x), f(g.y, u.y), f(g.z, u.z), f(g.w, u.w));
+}
+
 __global__ void __launch_bounds__(256) k_add_inplace(float4 *__restrict__ a, const float4 *__restrict__ b, long long n4)
 {
     const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -203,30 +232,45 @@ __global__ void __launch_bounds__(256) k_add_inplace(float4 *__restrict__ a, con
     a[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
 }
 
-// Single CTA: argmax of one logits row (first index on ties), written to *token_out and appended to
-// generated[*pos - prompt_len] when generated is given; then the position advances by `advance`.
-__global__ void __launch_bounds__(1024) k_argmax_advance(const float *__restrict__ logits, int n, int *__restrict__ token_out,
-                                                        int *__restrict__ pos_dev, int advance, int *__restrict__ generated, int gen_cap)
+// Greedy sampling over the logits by a cluster of 8 CTAs: every CTA scans an eighth of the vector with 128-bit
+// loads, the eight (value, index) candidates meet in CTA 0's shared memory (distributed shared memory), and CTA 0
+// publishes the token, appends it to the generated list and advances the position.  Ties go to the lowest index.
+constexpr int ARGMAX_CTAS = 8;
+__device__ __forceinline__ void argmax_take(float v, int i, float &best, int &idx)
 {
+    if (v > best || (v == best && i < idx)) {
+        best = v;
+        idx = i;
+    }
+}
+__global__ void __cluster_dims__(ARGMAX_CTAS, 1, 1) __launch_bounds__(1024)
+    k_argmax_advance(const float *__restrict__ logits, int n, int *__restrict__ token_out, int *__restrict__ pos_dev, int advance,
+                     int *__restrict__ generated, int gen_cap)
+{
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
     __shared__ float bv[32];
     __shared__ int bi[32];
+    __shared__ float cv[ARGMAX_CTAS];
+    __shared__ int ci[ARGMAX_CTAS];
+    const int rank = static_cast<int>(cluster.block_rank());
+    const int gtid = rank * 1024 + threadIdx.x, gthreads = ARGMAX_CTAS * 1024;
     float best = -INFINITY;
     int idx = n - 1;   // stays a valid index even when every logit is NaN
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = logits[i];
-        if (v > best || (v == best && i < idx)) {
-            best = v;
-            idx = i;
-        }
+    const int n4 = n / 4;
+    for (int i = gtid; i < n4; i += gthreads) {
+        const float4 v = reinterpret_cast<const float4 *>(logits)[i];
+        argmax_take(v.x, 4 * i, best, idx);
+        argmax_take(v.y, 4 * i + 1, best, idx);
+        argmax_take(v.z, 4 * i + 2, best, idx);
+        argmax_take(v.w, 4 * i + 3, best, idx);
     }
+    for (int i = 4 * n4 + gtid; i < n; i += gthreads) argmax_take(logits[i], i, best, idx);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
         const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (ov > best || (ov == best && oi < idx)) {
-            best = ov;
-            idx = oi;
-        }
+        argmax_take(ov, oi, best, idx);
     }
     if ((threadIdx.x & 31) == 0) {
         bv[threadIdx.x >> 5] = best;
@@ -234,11 +278,15 @@ __global__ void __launch_bounds__(1024) k_argmax_advance(const float *__restrict
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (int w = 1; w < 32; w++)
-            if (bv[w] > best || (bv[w] == best && bi[w] < idx)) {
-                best = bv[w];
-                idx = bi[w];
-            }
+        for (int w = 1; w < 32; w++) argmax_take(bv[w], bi[w], best, idx);
+        cluster.map_shared_rank(cv, 0)[rank] = best;   // into CTA 0's shared memory
+        cluster.map_shared_rank(ci, 0)[rank] = idx;
+    }
+    cluster.sync();
+    if (rank == 0 && threadIdx.x == 0) {
+        best = cv[0];
+        idx = ci[0];
+        for (int c = 1; c < ARGMAX_CTAS; c++) argmax_take(cv[c], ci[c], best, idx);
         *token_out = idx;
         if (generated != nullptr) {
             const int slot = generated[0];   // generated[0] counts the tokens stored so far, the tokens follow
@@ -279,7 +327,7 @@ int inkq_glue_rmsnorm(inkq_ctx *ctx, const float *x_dev, const float *w_dev, int
     int rc = glue_use(ctx);
     if (rc) return rc;
     INKQ_REQUIRE(ctx, x_dev && w_dev && y_dev && rows >= 1 && dim % 4 == 0, "bad rmsnorm arguments");
-    k_rmsnorm<<<(rows + 7) / 8, 256, 0, ctx->stream>>>(x_dev, w_dev, rows, dim, eps, y_dev);
+    k_rmsnorm<<<rows, 256, 0, ctx->stream>>>(x_dev, w_dev, rows, dim, eps, y_dev);
     return after_launch(ctx, "k_rmsnorm");
 }
 
@@ -305,11 +353,20 @@ int inkq_glue_attention(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cac
     if (rc) return rc;
     INKQ_REQUIRE(ctx, q_dev && k_cache_dev && v_cache_dev && pos0_dev && out_dev, "null argument");
     INKQ_REQUIRE(ctx, T >= 1 && nq % nkv == 0 && max_pos >= 1, "bad head configuration");
-    const size_t smem = sizeof(float) * (HEAD_DIM + 4 * HEAD_DIM + 8 + static_cast<size_t>(max_pos));
+    // few (token, head) items (a decode step): 16 warps per item so that the item's keys are spread over more
+    // loads in flight; many items (a prompt): 4 warps per item, the grid fills the machine
+    const bool wide = T * nq <= 4 * ctx->num_sms;
+    const int nw = wide ? 16 : 4;
+    const size_t smem = sizeof(float) * (HEAD_DIM + nw * HEAD_DIM + 2 * nw + static_cast<size_t>(max_pos));
     INKQ_REQUIRE(ctx, smem <= 200 * 1024, "context too long for the simple attention kernel");
-    if (smem > 48 * 1024) cudaFuncSetAttribute(k_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    k_attention<<<T * nq, 128, smem, ctx->stream>>>(q_dev, reinterpret_cast<const __half *>(k_cache_dev), reinterpret_cast<const __half *>(v_cache_dev),
-                                                    pos0_dev, T, nq, nkv, max_pos, scale, out_dev);
+    const __half *kc = reinterpret_cast<const __half *>(k_cache_dev), *vc = reinterpret_cast<const __half *>(v_cache_dev);
+    if (wide) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k_attention<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        k_attention<512><<<T * nq, 512, smem, ctx->stream>>>(q_dev, kc, vc, pos0_dev, T, nq, nkv, max_pos, scale, out_dev);
+    } else {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k_attention<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        k_attention<128><<<T * nq, 128, smem, ctx->stream>>>(q_dev, kc, vc, pos0_dev, T, nq, nkv, max_pos, scale, out_dev);
+    }
     return after_launch(ctx, "k_attention");
 }
 
@@ -322,6 +379,30 @@ int inkq_glue_silu_mul(inkq_ctx *ctx, const float *gate_dev, const float *up_dev
                                                                                   reinterpret_cast<const float4 *>(up_dev), n / 4,
                                                                                   reinterpret_cast<float4 *>(out_dev));
     return after_launch(ctx, "k_silu_mul");
+}
+
+int inkq_glue_silu_mul_rows(inkq_ctx *ctx, const float *gu_dev, int T, int F, float *out_dev)
+{
+    int rc = glue_use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, gu_dev && out_dev && T >= 1 && F >= 4 && F % 4 == 0, "bad silu_mul_rows arguments");
+    const long long n4 = static_cast<long long>(T) * (F / 4);
+    k_silu_mul_rows<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, ctx->stream>>>(reinterpret_cast<const float4 *>(gu_dev), T, F / 4,
+                                                                                    reinterpret_cast<float4 *>(out_dev));
+    return after_launch(ctx, "k_silu_mul_rows");
+}
+
+int inkq_glue_linear_m1(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, int pro, const float *g_dev, float eps, float *C_dev, int accumulate)
+{
+    int rc = glue_use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, w != nullptr && x_dev != nullptr && C_dev != nullptr, "null handle, input or output");
+    INKQ_REQUIRE(ctx, pro >= 0 && pro <= 2, "pro must be 0 (plain), 1 (RMSNorm) or 2 (SiLU * up)");
+    INKQ_REQUIRE(ctx, pro != 1 || g_dev != nullptr, "RMSNorm needs its weight vector");
+    INKQ_REQUIRE(ctx, w->scheme != INKQ_W41, "a weight-only layer takes fp16 activations");
+    INKQ_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(x_dev) & 15) == 0 && (g_dev == nullptr || (reinterpret_cast<uintptr_t>(g_dev) & 15) == 0),
+                 "x and g must be 16-byte aligned");
+    return launch_gemv_fused(ctx, w, x_dev, pro, g_dev, eps, C_dev, accumulate);
 }
 
 int inkq_glue_add_inplace(inkq_ctx *ctx, float *a_dev, const float *b_dev, long long n)
@@ -340,7 +421,8 @@ int inkq_glue_argmax_advance(inkq_ctx *ctx, const float *logits_dev, int n, int 
     int rc = glue_use(ctx);
     if (rc) return rc;
     INKQ_REQUIRE(ctx, logits_dev && token_out_dev && pos_dev && n >= 1, "bad argmax arguments");
-    k_argmax_advance<<<1, 1024, 0, ctx->stream>>>(logits_dev, n, token_out_dev, pos_dev, advance, generated_dev, gen_cap);
+    INKQ_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(logits_dev) & 15) == 0, "the logits must be 16-byte aligned");
+    k_argmax_advance<<<ARGMAX_CTAS, 1024, 0, ctx->stream>>>(logits_dev, n, token_out_dev, pos_dev, advance, generated_dev, gen_cap);
     return after_launch(ctx, "k_argmax_advance");
 }
 

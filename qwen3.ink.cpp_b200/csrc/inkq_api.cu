@@ -107,8 +107,9 @@ static int build_weight(inkq_ctx *ctx, int scheme, int scale_mode, int K, const 
     int rc = dev_alloc(ctx, &w->nibT, recs * 32);
     if (!rc) rc = dev_alloc(ctx, &w->sc16, recs);
     if (!rc) rc = dev_alloc(ctx, &w->zpT, recs);
-    if (!rc && scale_mode == INKQ_SCALES_F32) rc = dev_alloc(ctx, &w->sc32, recs);
-    w->bytes = recs * (32 + 8 + 2 + (scale_mode == INKQ_SCALES_F32 ? 16 : 0));
+    const bool want32 = scheme != INKQ_W41;   // fp32 scale records for the prefill QGEMM (the weight-only kernel reads fp16)
+    if (!rc && want32) rc = dev_alloc(ctx, &w->sc32, recs);
+    w->bytes = recs * (32 + 8 + 2 + (want32 ? 16 : 0));
     if (!rc) rc = launch_retile(ctx, w, nib_dev, d_dev, (scheme == INKQ_A81W41 || scheme == INKQ_W41) ? m_dev : nullptr,
                                 scheme == INKQ_A80W4Z ? zp_dev : nullptr, n_begin);
     if (rc) {

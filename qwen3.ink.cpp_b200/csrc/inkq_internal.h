@@ -132,6 +132,8 @@ int launch_block_isum(inkq_ctx *ctx, Act *a, int M, int M_ld);
 int launch_retile(inkq_ctx *ctx, Weight *w, const uint8_t *nib, const float *d, const float *m, const uint8_t *zp, int n_begin);
 int launch_export(inkq_ctx *ctx, const Weight *w, uint8_t *nib, float *d, float *m, uint8_t *zp);
 int launch_gemv(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, const ExtraDst *extra = nullptr);
+// decode QGEMV that builds its quantized activation row itself: pro 0 = x as is, 1 = RMSNorm(x; g, eps), 2 = SiLU(x[0..K)) * x[K..2K)
+int launch_gemv_fused(inkq_ctx *ctx, const Weight *w, const float *x, int pro, const float *g, float eps, float *C, int accumulate);
 int launch_gemm_simt(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc);
 int launch_block_dots(inkq_ctx *ctx, const Act *a, const Weight *w, int32_t *dots);
 int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc, int32_t *dots, const ExtraDst *extra = nullptr);

@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(256) k_retile_nibbles(const uint8_t *__restric
 // one thread per (tile, pair, row)
 __global__ void __launch_bounds__(256) k_retile_scales(const float *__restrict__ d, const float *__restrict__ m,
                                                        const uint8_t *__restrict__ zp, int scheme, int rows, int K, int tiles,
-                                                       int pairs, float4 *__restrict__ sc32, uint2 *__restrict__ sc16,
+                                                       int pairs, float4 *__restrict__ sc32, int round16, uint2 *__restrict__ sc16,
                                                        uchar2 *__restrict__ zpT)
 {
     const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -60,9 +60,17 @@ __global__ void __launch_bounds__(256) k_retile_scales(const float *__restrict__
         if (scheme == INKQ_A80W40) z = make_uchar2(8, 8);
         if (scheme == INKQ_A80W4Z) z = make_uchar2(zp[b], zp[b + 1]);
     }
-    if (sc32 != nullptr) sc32[idx] = sc;
     const __half2 h0 = __floats2half2_rn(sc.x, sc.y);
     const __half2 h1 = __floats2half2_rn(sc.z, sc.w);
+    if (sc32 != nullptr) {
+        // the prefill kernel reads fp32 records either way (widening fp16 in its inner loop costs more than the
+        // extra bytes): the values as given, or the fp16-rounded ones widened again
+        if (round16) {
+            const float2 a = __half22float2(h0), b = __half22float2(h1);
+            sc = make_float4(a.x, a.y, b.x, b.y);
+        }
+        sc32[idx] = sc;
+    }
     uint2 packed;
     packed.x = *reinterpret_cast<const uint32_t *>(&h0);
     packed.y = *reinterpret_cast<const uint32_t *>(&h1);
@@ -135,7 +143,7 @@ int launch_retile(inkq_ctx *ctx, Weight *w, const uint8_t *nib, const float *d, 
     {
         const long long total = static_cast<long long>(w->tiles) * w->pairs * TILE_N;
         k_retile_scales<<<static_cast<unsigned>((total + 255) / 256), 256, 0, ctx->stream>>>(d0, m0, zp0, w->scheme, w->rows, w->K, w->tiles,
-                                                                                           w->pairs, w->sc32, w->sc16, w->zpT);
+                                                                                           w->pairs, w->sc32, w->scale_mode == INKQ_SCALES_F16 ? 1 : 0, w->sc16, w->zpT);
         return after_launch(ctx, "k_retile_scales");
     }
 }

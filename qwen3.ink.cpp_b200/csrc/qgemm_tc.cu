@@ -585,12 +585,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     const int m = tm * BLOCK_M + col0 + j;
                     if (m < prm.M) prm.C[static_cast<size_t>(m) * prm.ldc + n] = accf[j];
                 }
-                for (int e = 0; e < prm.extra.n; e++) {
-                    float *__restrict__ Ce = prm.extra.p[e];
 #pragma unroll
-                    for (int j = 0; j < CW; j++) {
-                        const int m = tm * BLOCK_M + col0 + j;
-                        if (m < prm.M) Ce[static_cast<size_t>(m) * prm.ldc + n] = accf[j];
+                for (int e = 0; e < MAX_PEERS - 1; e++) {   // static indices: the parameter array stays out of local memory
+                    if (e < prm.extra.n) {
+                        float *__restrict__ Ce = prm.extra.p[e];
+#pragma unroll
+                        for (int j = 0; j < CW; j++) {
+                            const int m = tm * BLOCK_M + col0 + j;
+                            if (m < prm.M) Ce[static_cast<size_t>(m) * prm.ldc + n] = accf[j];
+                        }
                     }
                 }
             }

@@ -97,15 +97,103 @@ __device__ __forceinline__ float consume_batch(const PairBatch &b, float acc, bo
     return acc;
 }
 
+// What a fused launch does around the matrix-vector product (decode step of a model: one launch per layer
+// instead of norm + quantizer + QGEMV + residual add).  The quantization arithmetic is the quantizer's own,
+// operation for operation, so the result equals quantize + QGEMV on the same fp32 row.
+struct FusedM1 {
+    const float *x;      // fp32 input row: K values (PRO_SILU_MUL: 2K values, gate then up)
+    const float *g;      // PRO_RMSNORM: the norm's weight vector
+    float eps;
+    int pro;             // PRO_*
+    int qmode;           // INKQ_Q8_1_F16 or INKQ_Q8_0_F16
+    int accumulate;      // 1: C[n] += result (residual connection), 0: C[n] = result
+};
+enum { PRO_PLAIN = 0, PRO_RMSNORM = 1, PRO_SILU_MUL = 2 };
+
+__device__ __forceinline__ uint32_t pack_sat_s8x4_m1(int a, int b, int c, int d)
+{
+    uint32_t hi, out;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(d), "r"(c), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(b), "r"(a), "r"(hi));
+    return out;
+}
+
+// Builds the quantized activation row in shared memory from fp32 input (two lanes per 32-element block, as
+// k_quantize_q8): optional RMSNorm (x * 1/sqrt(mean(x^2) + eps) * g) or SiLU(gate) * up first.
+template <bool HAS_MIN>
+__device__ __forceinline__ void fused_prologue(const FusedM1 &f, int K, uint32_t *qa, float *da, float *sa, float *red)
+{
+    const int nb = K / QK;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    float inv = 1.0f;
+    if (f.pro == PRO_RMSNORM) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < K / 4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4 *>(f.x)[i];
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float tot = 0.0f;
+        for (int w2 = 0; w2 < nwarps; w2++) tot += red[w2];
+        inv = 1.0f / sqrtf(tot / static_cast<float>(K) + f.eps);
+        __syncthreads();   // red is reused for the slice partials
+    }
+    const int half = threadIdx.x & 1;
+    const unsigned gmask = 0x3u << (threadIdx.x & 30);                     // the two lanes of a block
+    for (int blk = threadIdx.x >> 1; blk < nb; blk += blockDim.x >> 1) {   // both lanes of a pair run the same trip count
+        float4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int i4 = blk * 8 + 2 * j + half;
+            float4 t = reinterpret_cast<const float4 *>(f.x)[i4];
+            if (f.pro == PRO_RMSNORM) {
+                const float4 gg = reinterpret_cast<const float4 *>(f.g)[i4];
+                t = make_float4(t.x * inv * gg.x, t.y * inv * gg.y, t.z * inv * gg.z, t.w * inv * gg.w);
+            } else if (f.pro == PRO_SILU_MUL) {
+                const float4 u = reinterpret_cast<const float4 *>(f.x + K)[i4];
+                auto act = [](float a, float b) { return a / (1.0f + __expf(-a)) * b; };
+                t = make_float4(act(t.x, u.x), act(t.y, u.y), act(t.z, u.z), act(t.w, u.w));
+            }
+            v[j] = t;
+        }
+        float mx = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; j++) mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
+        mx = fmaxf(mx, __shfl_xor_sync(gmask, mx, 1));
+        const float dd = __fdiv_rn(mx, 127.0f);
+        const float id = (mx != 0.0f) ? __fdiv_rn(127.0f, mx) : 0.0f;
+        int sum = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int i0 = __float2int_rn(__fmul_rn(v[j].x, id));
+            const int i1 = __float2int_rn(__fmul_rn(v[j].y, id));
+            const int i2 = __float2int_rn(__fmul_rn(v[j].z, id));
+            const int i3 = __float2int_rn(__fmul_rn(v[j].w, id));
+            sum += (i0 + i1) + (i2 + i3);
+            qa[blk * 8 + 2 * j + half] = pack_sat_s8x4_m1(i0, i1, i2, i3);
+        }
+        sum += __shfl_xor_sync(gmask, sum, 1);
+        if (half == 0) {
+            da[blk] = __half2float(__float2half_rn(dd));
+            if (HAS_MIN) sa[blk] = (f.qmode == INKQ_Q8_1_F16) ? __half2float(__float2half_rn(__fmul_rn(dd, static_cast<float>(sum)))) : 0.0f;
+            else reinterpret_cast<int32_t *>(sa)[blk] = sum;
+        }
+    }
+}
+
 // WARPS = K-slices per CTA: 8 for wide layers, 16 for narrow ones (more bytes in flight per SM when
 // the grid alone cannot fill the machine).  The register budget keeps 3 (resp. 2) CTAs per SM resident so
-// that every Qwen3-8B shape runs as a single wave.
-template <bool HAS_MIN, int WARPS>
+// that every Qwen3-8B shape runs as a single wave.  FUSED: the activation row is built from fp32 input in
+// the prologue (FusedM1) instead of being read from a quantizer's output.
+template <bool HAS_MIN, int WARPS, bool FUSED>
 __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_a8w4(const uint8_t *__restrict__ nibT, const uint2 *__restrict__ sc16,
                                                                const uchar2 *__restrict__ zpT, const int8_t *__restrict__ q,
                                                                const float *__restrict__ d, const float *__restrict__ s,
                                                                const int32_t *__restrict__ isum, int M_ld, float *__restrict__ C,
-                                                               int rows, int K, int pairs, const ExtraDst extra)
+                                                               int rows, int K, int pairs, const ExtraDst extra, const FusedM1 fused)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int nb = K / QK;
@@ -133,12 +221,16 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_a8w4(c
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    for (int i = threadIdx.x; i < K / 16; i += blockDim.x)
-        reinterpret_cast<uint4 *>(qa)[i] = reinterpret_cast<const uint4 *>(q)[i];
-    for (int b = threadIdx.x; b < nb; b += blockDim.x) {
-        da[b] = d[static_cast<size_t>(b) * M_ld];
-        if (HAS_MIN) sa[b] = s[static_cast<size_t>(b) * M_ld];
-        else reinterpret_cast<int32_t *>(sa)[b] = isum[static_cast<size_t>(b) * M_ld];
+    if (FUSED) {
+        fused_prologue<HAS_MIN>(fused, K, qa, da, sa, part);
+    } else {
+        for (int i = threadIdx.x; i < K / 16; i += blockDim.x)
+            reinterpret_cast<uint4 *>(qa)[i] = reinterpret_cast<const uint4 *>(q)[i];
+        for (int b = threadIdx.x; b < nb; b += blockDim.x) {
+            da[b] = d[static_cast<size_t>(b) * M_ld];
+            if (HAS_MIN) sa[b] = s[static_cast<size_t>(b) * M_ld];
+            else reinterpret_cast<int32_t *>(sa)[b] = isum[static_cast<size_t>(b) * M_ld];
+        }
     }
     __syncthreads();
 
@@ -160,17 +252,21 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_a8w4(c
         for (int w2 = 1; w2 < WARPS; w2++) tot = __fadd_rn(tot, part[w2 * 32 + lane]);
         const int n = t * TILE_N + r;
         if (n < rows) {
+            if (FUSED && fused.accumulate) tot = __fadd_rn(C[n], tot);
             C[n] = tot;
-            for (int e = 0; e < extra.n; e++) extra.p[e][n] = tot;   // column-sharded layer: the same element in every peer's buffer
+#pragma unroll
+            for (int e = 0; e < MAX_PEERS - 1; e++)                  // column-sharded layer: the same element in every peer's buffer
+                if (e < extra.n) extra.p[e][n] = tot;                // (static indices: the parameter array stays out of local memory)
         }
     }
 }
 
-template <bool HAS_MIN, int WARPS>
-static void launch_gemv_variant(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, const ExtraDst &extra)
+template <bool HAS_MIN, int WARPS, bool FUSED>
+static void launch_gemv_variant(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, const ExtraDst &extra, const FusedM1 &fused)
 {
     const size_t smem = static_cast<size_t>(w->K) + 2 * sizeof(float) * (w->K / QK) + sizeof(float) * WARPS * 32;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(k_qgemv_a8w4<HAS_MIN, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(k_qgemv_a8w4<HAS_MIN, WARPS, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     // launched with programmatic stream serialization: the grid may begin (and prefetch weights) before the
     // previous kernel in the stream has finished; it waits for that kernel inside (griddepcontrol.wait)
     cudaLaunchConfig_t cfg = {};
@@ -183,25 +279,45 @@ static void launch_gemv_variant(inkq_ctx *ctx, const Act *a, const Weight *w, fl
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaLaunchKernelEx(&cfg, k_qgemv_a8w4<HAS_MIN, WARPS>, static_cast<const uint8_t *>(w->nibT), static_cast<const uint2 *>(w->sc16),
-                       static_cast<const uchar2 *>(w->zpT), static_cast<const int8_t *>(a->q), static_cast<const float *>(a->d),
-                       static_cast<const float *>(a->s), static_cast<const int32_t *>(a->isum), a->M_ld, C, w->rows, w->K, w->pairs, extra);
+    cudaLaunchKernelEx(&cfg, k_qgemv_a8w4<HAS_MIN, WARPS, FUSED>, static_cast<const uint8_t *>(w->nibT), static_cast<const uint2 *>(w->sc16),
+                       static_cast<const uchar2 *>(w->zpT), static_cast<const int8_t *>(a ? a->q : nullptr),
+                       static_cast<const float *>(a ? a->d : nullptr), static_cast<const float *>(a ? a->s : nullptr),
+                       static_cast<const int32_t *>(a ? a->isum : nullptr), a ? a->M_ld : 0, C, w->rows, w->K, w->pairs, extra, fused);
+}
+
+template <bool FUSED>
+static void launch_gemv_any(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, const ExtraDst &extra, const FusedM1 &fused)
+{
+    // narrow layers (few CTAs) or long rows: 16 K-slices per CTA
+    const bool wide_cta = (w->tiles * 4 <= 2 * ctx->num_sms) || (w->pairs >= 128);
+    if (w->scheme == INKQ_A81W41) {
+        if (wide_cta) launch_gemv_variant<true, 16, FUSED>(ctx, a, w, C, extra, fused);
+        else launch_gemv_variant<true, 8, FUSED>(ctx, a, w, C, extra, fused);
+    } else {
+        if (wide_cta) launch_gemv_variant<false, 16, FUSED>(ctx, a, w, C, extra, fused);
+        else launch_gemv_variant<false, 8, FUSED>(ctx, a, w, C, extra, fused);
+    }
 }
 
 int launch_gemv(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, const ExtraDst *extra_in)
 {
     ExtraDst extra = {};
     if (extra_in != nullptr) extra = *extra_in;
-    // narrow layers (few CTAs) or long rows: 16 K-slices per CTA
-    const bool wide_cta = (w->tiles * 4 <= 2 * ctx->num_sms) || (w->pairs >= 128);
-    if (w->scheme == INKQ_A81W41) {
-        if (wide_cta) launch_gemv_variant<true, 16>(ctx, a, w, C, extra);
-        else launch_gemv_variant<true, 8>(ctx, a, w, C, extra);
-    } else {
-        if (wide_cta) launch_gemv_variant<false, 16>(ctx, a, w, C, extra);
-        else launch_gemv_variant<false, 8>(ctx, a, w, C, extra);
-    }
+    launch_gemv_any<false>(ctx, a, w, C, extra, FusedM1{});
     return after_launch(ctx, "k_qgemv_a8w4");
+}
+
+int launch_gemv_fused(inkq_ctx *ctx, const Weight *w, const float *x, int pro, const float *g, float eps, float *C, int accumulate)
+{
+    FusedM1 f;
+    f.x = x;
+    f.g = g;
+    f.eps = eps;
+    f.pro = pro;
+    f.qmode = (w->scheme == INKQ_A81W41) ? INKQ_Q8_1_F16 : INKQ_Q8_0_F16;   // as inkq_linear chooses for M == 1
+    f.accumulate = accumulate;
+    launch_gemv_any<true>(ctx, nullptr, w, C, ExtraDst{}, f);
+    return after_launch(ctx, "k_qgemv_a8w4 (fused prologue)");
 }
 
 }  // namespace inkq

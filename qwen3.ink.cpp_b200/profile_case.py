@@ -3,6 +3,8 @@
     python qwen3.ink.cpp_b200/profile_case.py qgemm [M]       # k_qgemm_tc, N=12288, K=4096 (default M=322)
     python qwen3.ink.cpp_b200/profile_case.py qgemv [N] [K]   # k_qgemv_a8w4 (default 12288 x 4096), 12 distinct weight sets
     python qwen3.ink.cpp_b200/profile_case.py quantize [M]    # k_quantize_q8, K=4096 (default M=8192)
+    python qwen3.ink.cpp_b200/profile_case.py model [layers]  # synthetic Qwen3-8B-shaped forward with few layers (default 2): prefill of 322
+                                                              # tokens, then 3 decode steps (launch list of the glue around the linears)
     python qwen3.ink.cpp_b200/profile_case.py w41 [M]         # k_gemm_w41_tc, N=12288, K=4096 (default M=2048); prints its time
 
 Typical capture (one kernel, one launch, after the same command has exited 0 without ncu):
@@ -55,6 +57,17 @@ def main():
             ctx.quantize(act, x, M, pkg.Q8_1_F32)
         ctx.synchronize()
         print("quantize ok", M, K)
+    elif what == "model":
+        layers = (args + [2])[0]
+        cfg = pkg.qwen3_forward.Qwen3Config(layers=layers, max_pos=512)
+        model = pkg.qwen3_forward.Qwen3Synthetic(pkg, ctx, cfg, seed=7)
+        prompt = torch.from_numpy(pkg.synth.tokens(322, cfg.vocab)).cuda()
+        model.reset()
+        model.prefill(prompt)
+        for _ in range(3):
+            model.decode_step()
+        ctx.synchronize()
+        print("model ok", layers, model.generated_tokens())
     elif what == "w41":
         M, N, K = (args + [2048])[0], 12288, 4096
         w = pkg.synth.weights(N, K)

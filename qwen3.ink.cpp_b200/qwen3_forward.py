@@ -5,10 +5,13 @@ it was written for (Qwen3-8B: 36 layers, hidden 4096, 32 query / 8 KV heads of 1
 12288, vocabulary 151936, RoPE theta 1e6, per-head q/k RMSNorm), with random-init weights
 generated directly on the device.  Structure follows the reference's model code
 (qwen3/src/qwen/QwenForCausalLM.cc:11-122, QwenDecoder.cc:53-142, QwenDecoderLayer.cc:39-119,
-QwenAttention.cc:52-207): fused qkv projection, last-token lm_head, greedy argmax.  Every
+QwenAttention.cc:52-207): fused qkv projection, fused gate_up projection (the reference's export writes
+one, notebooks/save_A81W41_quantized_weight-qwen3_8b.ipynb cell 26), last-token lm_head, greedy argmax.  Every
 linear goes through Context.linear (Qwen_Linear_with_bias_Int4::forward: quantize + QGEMM for
 a prompt, + QGEMV for a single token); everything between them is the thin glue of
-csrc/glue_ops.cu.  One decode step is captured once as a CUDA graph and replayed.
+csrc/glue_ops.cu.  In a decode step (one token) the norms, SiLU*up, the activation quantizer and the residual
+additions run inside the QGEMV launches (inkq_glue_linear_m1): 6 launches per layer instead of 17.  One decode
+step is captured once as a CUDA graph and replayed.
 """
 from __future__ import annotations
 
@@ -31,6 +34,7 @@ class Qwen3Config:
     eps: float = 1e-6
     max_pos: int = 512
     lm_head_fp16: bool = True     # fp16 lm_head (benchmark config); False: A81W41 like the reference
+    fused_decode: bool = True     # decode step: norm / SiLU*up + quantizer in the QGEMV prologue, residual in its epilogue
 
 
 def _p(t):
@@ -66,7 +70,7 @@ class Qwen3Synthetic:
             self.layers.append(dict(
                 ln1=torch.ones(H, device="cuda"), ln2=torch.ones(H, device="cuda"),
                 qn=torch.ones(cfg.head_dim, device="cuda"), kn=torch.ones(cfg.head_dim, device="cuda"),
-                qkv=qlinear(qkv_n, H), o=qlinear(H, cfg.nq * cfg.head_dim), gate=qlinear(F, H), up=qlinear(F, H), down=qlinear(H, F),
+                qkv=qlinear(qkv_n, H), o=qlinear(H, cfg.nq * cfg.head_dim), gate_up=qlinear(2 * F, H), down=qlinear(H, F),
                 k_cache=torch.zeros((cfg.nkv, cfg.max_pos, cfg.head_dim), dtype=torch.float16, device="cuda"),
                 v_cache=torch.zeros((cfg.nkv, cfg.max_pos, cfg.head_dim), dtype=torch.float16, device="cuda")))
         self.final_norm = torch.ones(H, device="cuda")
@@ -95,7 +99,7 @@ class Qwen3Synthetic:
             qkv_n = (cfg.nq + 2 * cfg.nkv) * cfg.head_dim
             z = lambda *s: torch.empty(s, device="cuda", dtype=torch.float32)
             self.bufs[T] = dict(x=z(T, cfg.hidden), xn=z(T, cfg.hidden), qkv=z(T, qkv_n), q=z(T, cfg.nq * cfg.head_dim),
-                                attn=z(T, cfg.nq * cfg.head_dim), proj=z(T, cfg.hidden), gate=z(T, cfg.ffn), up=z(T, cfg.ffn),
+                                attn=z(T, cfg.nq * cfg.head_dim), proj=z(T, cfg.hidden), gu=z(T, 2 * cfg.ffn),
                                 act=z(T, cfg.ffn), logits=z(1, cfg.vocab))
         return self.bufs[T]
 
@@ -110,7 +114,20 @@ class Qwen3Synthetic:
         H, F = cfg.hidden, cfg.ffn
         scale = 1.0 / float(np.sqrt(cfg.head_dim))
         self._chk(L.inkq_glue_embedding(h, _p(self.embed), _p(tokens_dev), T, H, cfg.vocab, _p(b["x"])))
-        for ly in self.layers:
+        fused = (T == 1 and cfg.fused_decode)
+        eps = C.c_float(cfg.eps)
+        for ly in (self.layers if fused else []):
+            # one launch per linear: norm / SiLU*up and the activation quantizer run in the QGEMV's prologue,
+            # the residual connection in its epilogue (x += ...)
+            self._chk(L.inkq_glue_linear_m1(h, ly["qkv"].h, _p(b["x"]), 1, _p(ly["ln1"]), eps, _p(b["qkv"]), 0))
+            self._chk(L.inkq_glue_qknorm_rope_cache(h, _p(b["qkv"]), _p(ly["qn"]), _p(ly["kn"]), _p(self.cos), _p(self.sin), _p(self.pos), T,
+                                                    cfg.nq, cfg.nkv, cfg.max_pos, eps, _p(b["q"]), _p(ly["k_cache"]), _p(ly["v_cache"])))
+            self._chk(L.inkq_glue_attention(h, _p(b["q"]), _p(ly["k_cache"]), _p(ly["v_cache"]), _p(self.pos), T, cfg.nq, cfg.nkv, cfg.max_pos,
+                                            C.c_float(scale), _p(b["attn"])))
+            self._chk(L.inkq_glue_linear_m1(h, ly["o"].h, _p(b["attn"]), 0, None, eps, _p(b["x"]), 1))
+            self._chk(L.inkq_glue_linear_m1(h, ly["gate_up"].h, _p(b["x"]), 1, _p(ly["ln2"]), eps, _p(b["gu"]), 0))
+            self._chk(L.inkq_glue_linear_m1(h, ly["down"].h, _p(b["gu"]), 2, None, eps, _p(b["x"]), 1))
+        for ly in ([] if fused else self.layers):
             self._chk(L.inkq_glue_rmsnorm(h, _p(b["x"]), _p(ly["ln1"]), T, H, C.c_float(cfg.eps), _p(b["xn"])))
             self.ctx.linear(ly["qkv"], b["xn"], T, b["qkv"], b["qkv"].shape[1])
             self._chk(L.inkq_glue_qknorm_rope_cache(h, _p(b["qkv"]), _p(ly["qn"]), _p(ly["kn"]), _p(self.cos), _p(self.sin), _p(self.pos), T,
@@ -121,9 +138,8 @@ class Qwen3Synthetic:
             self.ctx.linear(ly["o"], b["attn"], T, b["proj"], H)
             self._chk(L.inkq_glue_add_inplace(h, _p(b["x"]), _p(b["proj"]), C.c_longlong(T * H)))
             self._chk(L.inkq_glue_rmsnorm(h, _p(b["x"]), _p(ly["ln2"]), T, H, C.c_float(cfg.eps), _p(b["xn"])))
-            self.ctx.linear(ly["gate"], b["xn"], T, b["gate"], F)
-            self.ctx.linear(ly["up"], b["xn"], T, b["up"], F)
-            self._chk(L.inkq_glue_silu_mul(h, _p(b["gate"]), _p(b["up"]), C.c_longlong(T * F), _p(b["act"])))
+            self.ctx.linear(ly["gate_up"], b["xn"], T, b["gu"], 2 * F)       # fused gate_up projection, gate columns first
+            self._chk(L.inkq_glue_silu_mul_rows(h, _p(b["gu"]), T, F, _p(b["act"])))
             self.ctx.linear(ly["down"], b["act"], T, b["proj"], H)
             self._chk(L.inkq_glue_add_inplace(h, _p(b["x"]), _p(b["proj"]), C.c_longlong(T * H)))
         last = b["x"][T - 1:T]

@@ -10,8 +10,8 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def small_cfg(pkg):
-    return pkg.qwen3_forward.Qwen3Config(layers=2, hidden=256, nq=4, nkv=2, head_dim=128, ffn=512, vocab=1024, max_pos=64, lm_head_fp16=True)
+def small_cfg(pkg, **kw):
+    return pkg.qwen3_forward.Qwen3Config(layers=2, hidden=256, nq=4, nkv=2, head_dim=128, ffn=512, vocab=1024, max_pos=64, lm_head_fp16=True, **kw)
 
 
 def torch_forward(torch, model, tokens):
@@ -46,7 +46,8 @@ def torch_forward(torch, model, tokens):
         a = torch.einsum("hts,shd->thd", torch.softmax(s, dim=-1), v).reshape(T, cfg.nq * 128)
         x = x + lin(ly["o"], a, cfg.hidden)
         h = rms(x, ly["ln2"])
-        act = torch.nn.functional.silu(lin(ly["gate"], h, cfg.ffn)) * lin(ly["up"], h, cfg.ffn)
+        gu = lin(ly["gate_up"], h, 2 * cfg.ffn)
+        act = torch.nn.functional.silu(gu[:, :cfg.ffn]) * gu[:, cfg.ffn:]
         x = x + lin(ly["down"], act, cfg.hidden)
     last = rms(x[T - 1:T], model.final_norm)
     return last
@@ -108,3 +109,62 @@ def test_decode_path_and_graph_agree_with_prefill(pkg, gpu):
         model.graph.replay()
     torch.cuda.synchronize()
     assert np.array_equal(model.generated_tokens(), eager) and len(eager) == 6
+
+
+def test_fused_decode_layer_equals_separate_kernels(pkg, gpu):
+    """inkq_glue_linear_m1 (norm / SiLU*up + quantizer in the QGEMV prologue, residual in the epilogue) against the
+    separate kernels.  Plain and SiLU*up prologues quantize the very same fp32 values, so the results are
+    bit-identical; the RMSNorm prologue sums the squares in another order, so its input to the quantizer may
+    differ in the last bit and the outputs agree to the tolerance of a flipped rounding."""
+    import ctypes as C
+    import torch
+    L = gpu.L
+    K, N = 512, 384
+    w = pkg.synth.weights(N, K, 31)
+    for scheme, m in ((pkg.A81W41, w["m"]), (pkg.A80W40, None)):
+        wh = gpu.weight(scheme, pkg.SCALES_F16, w["nib"], w["d"], m)
+        x = torch.randn((1, K), device="cuda")
+        g = torch.rand(K, device="cuda") + 0.5
+        ref = torch.empty((1, N), device="cuda")
+        out = torch.empty((1, N), device="cuda")
+        # plain
+        gpu.linear(wh, x, 1, ref, N)
+        gpu.check(L.inkq_glue_linear_m1(gpu.h, wh.h, C.c_void_p(x.data_ptr()), 0, None, C.c_float(0.0), C.c_void_p(out.data_ptr()), 0))
+        gpu.synchronize()
+        assert torch.equal(out, ref)
+        # residual accumulate
+        base = torch.randn((1, N), device="cuda")
+        acc = base.clone()
+        gpu.check(L.inkq_glue_linear_m1(gpu.h, wh.h, C.c_void_p(x.data_ptr()), 0, None, C.c_float(0.0), C.c_void_p(acc.data_ptr()), 1))
+        gpu.synchronize()
+        assert torch.equal(acc, base + ref)
+        # RMSNorm prologue
+        xn = torch.empty_like(x)
+        gpu.check(L.inkq_glue_rmsnorm(gpu.h, C.c_void_p(x.data_ptr()), C.c_void_p(g.data_ptr()), 1, K, C.c_float(1e-6), C.c_void_p(xn.data_ptr())))
+        gpu.linear(wh, xn, 1, ref, N)
+        gpu.check(L.inkq_glue_linear_m1(gpu.h, wh.h, C.c_void_p(x.data_ptr()), 1, C.c_void_p(g.data_ptr()), C.c_float(1e-6), C.c_void_p(out.data_ptr()), 0))
+        gpu.synchronize()
+        assert (out - ref).abs().max().item() <= 5e-3 * ref.abs().max().item()
+        # SiLU(gate) * up prologue: input [2K]
+        gu = torch.randn((1, 2 * K), device="cuda")
+        act = torch.empty((1, K), device="cuda")
+        gpu.check(L.inkq_glue_silu_mul_rows(gpu.h, C.c_void_p(gu.data_ptr()), 1, K, C.c_void_p(act.data_ptr())))
+        gpu.linear(wh, act, 1, ref, N)
+        gpu.check(L.inkq_glue_linear_m1(gpu.h, wh.h, C.c_void_p(gu.data_ptr()), 2, None, C.c_float(0.0), C.c_void_p(out.data_ptr()), 0))
+        gpu.synchronize()
+        assert torch.equal(out, ref)
+
+
+def test_fused_and_unfused_decode_agree(pkg, gpu):
+    import torch
+    toks = torch.from_numpy(pkg.synth.tokens(9, 1024, 6)).cuda()
+    logits = []
+    for fused in (False, True):
+        model = pkg.qwen3_forward.Qwen3Synthetic(pkg, gpu, small_cfg(pkg, fused_decode=fused), seed=2)
+        model.reset()
+        model.prefill(toks[:8])
+        model.token.copy_(toks[8:9])
+        logits.append(model.decode_step().clone())
+        gpu.synchronize()
+    rel = (logits[0] - logits[1]).abs().max().item() / logits[0].abs().max().item()
+    assert rel < 2e-2, rel
