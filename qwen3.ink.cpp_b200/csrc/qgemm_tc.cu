@@ -674,8 +674,27 @@ int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int l
 {
     if (ctx->encode_tiled == nullptr) return fail(ctx, INKQ_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled entry point not available");
     const int M = a->M;
-    const int tiles_m = (M + 127) / 128;
-    const int block_m = (((M + tiles_m - 1) / tiles_m) + 15) & ~15;  // even split, multiple of 16, <= 128
+    // Split of the M activation rows into tiles of block_m columns (a multiple of 16, at most 128).  A tile's time
+    // has a floor set by the serial K=32 MMAs and grows with block_m only above ~48 columns (measured on a B200,
+    // one tile per SM, K=4096, in us; only the ratios matter).  With few weight tiles (a shard of a column-sharded
+    // layer) narrower tiles fill more SMs; the choice minimises waves x tile time.  It depends on the shapes and
+    // the SM count only, and every choice gives the same bits (the per-output operation order never changes).
+    static const float tile_us[9] = {0.f, 43.5f, 45.5f, 48.3f, 55.6f, 64.0f, 72.4f, 75.0f, 86.3f};   // block_m = 16 * index
+    int tiles_m = (M + 127) / 128, block_m = 128;
+    {
+        float best = 0.f;
+        for (int tm = (M + 127) / 128; tm <= (M + 15) / 16; tm++) {
+            const int bm = (((M + tm - 1) / tm) + 15) & ~15;
+            const long long total = static_cast<long long>(w->tiles) * tm;
+            const float cost = static_cast<float>((total + ctx->num_sms - 1) / ctx->num_sms) * tile_us[bm / 16];
+            if (best == 0.f || cost < best * 0.999f) {
+                best = cost;
+                tiles_m = tm;
+                block_m = bm;
+            }
+            if (total > 64LL * ctx->num_sms) break;   // many waves already: finer splits only add padding
+        }
+    }
     const int nb = a->K / QK;
 
     CUtensorMap maps[3];
