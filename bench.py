@@ -338,9 +338,9 @@ def model_pp_tg(pkg, torch, ctx, prompt_len=322, new_tokens=128, reps=3):
     n_gen = len(model.generated_tokens())
     # the same decode step with every operator as its own launch (17 per layer), for comparison
     unfused_ms = None
-    launches_per_token = 6 * cfg.layers + 4 if cfg.fused_decode else 17 * cfg.layers + 4
-    if cfg.fused_decode:
-        model.cfg.fused_decode = False
+    launches_per_token = {"epilogue": 5 * cfg.layers + 4, "prologue": 6 * cfg.layers + 4, "separate": 17 * cfg.layers + 4}[cfg.decode_mode]
+    if cfg.decode_mode != "separate":
+        model.cfg.decode_mode = "separate"
         model.reset()
         model.prefill(prompt)
         model.decode_step()

@@ -35,15 +35,36 @@ int inkq_glue_attention(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cac
                         int nq, int nkv, int max_pos, float scale, float *out_dev);
 /* out = silu(gate) * up.  Qwen3SiLuMul, qwen3/src/qwen/QwenOperator.cc:697-722 */
 int inkq_glue_silu_mul(inkq_ctx *ctx, const float *gate_dev, const float *up_dev, long long n, float *out_dev);
-/* The same on the output of a fused gate_up projection: gu [T][2F] (gate columns first), out [T][F]. */
+/* The same on the output of a fused gate_up projection whose columns come in (32 gate, 32 up) groups:
+ * gu [T][2F], out[t][k] = SiLU(gu[t][64*(k/32) + k%32]) * gu[t][64*(k/32) + 32 + k%32]. */
 int inkq_glue_silu_mul_rows(inkq_ctx *ctx, const float *gu_dev, int T, int F, float *out_dev);
 /* One decode-step layer in one launch (no counterpart in the reference, which runs these as separate
  * operators: QwenDecoderLayer.cc:66-105): the M == 1 forward of inkq_linear on
- *   pro 0: x                      pro 1: RMSNorm(x; g, eps)          pro 2: SiLU(x[0..K)) * x[K..2K)
+ *   pro 0: x                      pro 1: RMSNorm(x; g, eps)          pro 2: SiLU(gate) * up of a 2K-row in (32 gate, 32 up) groups
  * with the activation quantizer inside the QGEMV's prologue (same arithmetic as inkq_quantize), and
  * accumulate != 0 adding the result onto C (the residual connection) instead of overwriting it. */
 int inkq_glue_linear_m1(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, int pro, const float *g_dev, float eps, float *C_dev,
                         int accumulate);
+/* ---- decode step with the activation work in the producers' epilogues -----------------------
+ * No counterpart in the reference (separate operators, QwenDecoderLayer.cc:66-105).  Every matrix-vector
+ * product reads a ready quantized row (an activation handle holding M == 1) and the kernel that produces
+ * a layer's input also quantizes it:
+ *   inkq_glue_decode_gemv, epilogue 0: C = y      1: C += y      2: C += y, then RMSNorm(C; norm_w, eps) of the
+ *       whole row quantized into `out` by the CTA that finishes last (xn_out_dev, if not NULL, also receives
+ *       the normalized fp32 row)      3: the weight's rows are (32 gate, 32 up) groups - row 64b+e is gate
+ *       row 32b+e, row 64b+32+e is up row 32b+e of a fused gate_up projection - and SiLU(gate)*up is quantized
+ *       into `out` (C_dev unused)
+ *   inkq_glue_rmsnorm_quant: the same RMSNorm + quantizer for a row that no product made (after the embedding)
+ *   inkq_glue_attention_quant: inkq_glue_attention for one token with its output quantized into `out`
+ * `out` must have been created with inkq_act_create(ctx, 1, K_of_the_produced_row); out_qmode is the mode
+ * the consuming layer's M == 1 path uses (INKQ_Q8_1_F16 for A81W41, INKQ_Q8_0_F16 for the A80 schemes).
+ * Results equal the separate operators' except for the summation order inside RMSNorm. */
+int inkq_glue_decode_gemv(inkq_ctx *ctx, const inkq_weight *w, const inkq_act *in, float *C_dev, int epilogue, const float *norm_w_dev, float eps,
+                          inkq_act *out, int out_qmode, float *xn_out_dev);
+int inkq_glue_rmsnorm_quant(inkq_ctx *ctx, const float *x_dev, const float *norm_w_dev, float eps, int K, inkq_act *out, int out_qmode,
+                            float *xn_out_dev);
+int inkq_glue_attention_quant(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev,
+                              int nq, int nkv, int max_pos, float scale, inkq_act *out, int out_qmode);
 /* a += b (residual).  qwen3/src/qwen/QwenDecoderLayer.cc:73,105 */
 int inkq_glue_add_inplace(inkq_ctx *ctx, float *a_dev, const float *b_dev, long long n);
 /* Greedy sampling: *token_out = argmax(logits) (first index on ties), appended to generated

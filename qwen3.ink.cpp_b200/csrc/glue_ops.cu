@@ -21,6 +21,7 @@
 
 #include "inkq_glue.h"
 #include "inkq_internal.h"
+#include "qgemv_common.cuh"
 
 namespace inkq {
 
@@ -76,6 +77,10 @@ __global__ void __launch_bounds__(256) k_qknorm_rope_cache(const float *__restri
                                                            int nkv, int max_pos, float eps, float *__restrict__ q_out,
                                                            __half *__restrict__ k_cache, __half *__restrict__ v_cache)
 {
+    // launched with programmatic stream serialization in the decode step: wait for the producer of the inputs,
+    // then let the next kernel (a QGEMV) start its weight prefetch while this grid runs
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int heads = nq + 2 * nkv;
     const int item = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (item >= T * heads) return;
@@ -124,8 +129,12 @@ __global__ void __launch_bounds__(256) k_qknorm_rope_cache(const float *__restri
 template <int NT>
 __global__ void __launch_bounds__(NT) k_attention(const float *__restrict__ q, const __half *__restrict__ k_cache,
                                                    const __half *__restrict__ v_cache, const int *__restrict__ pos0_dev, int T, int nq, int nkv,
-                                                   int max_pos, float scale, float *__restrict__ out)
+                                                   int max_pos, float scale, float *__restrict__ out, const QuantOut qo)
 {
+    // launched with programmatic stream serialization in the decode step: wait for the producer of the inputs,
+    // then let the next kernel (a QGEMV) start its weight prefetch while this grid runs
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ float sm[];
     float *qs = sm;                  // 128
     constexpr int NW = NT / 32;
@@ -199,7 +208,10 @@ __global__ void __launch_bounds__(NT) k_attention(const float *__restrict__ q, c
         float o = 0.0f;
 #pragma unroll
         for (int i = 0; i < NW; i++) o += part[i * HEAD_DIM + tid];
-        out[(static_cast<size_t>(t) * nq + h) * HEAD_DIM + tid] = o * inv;
+        o *= inv;
+        if (out != nullptr) out[(static_cast<size_t>(t) * nq + h) * HEAD_DIM + tid] = o;
+        // decode step: the head's 128 outputs are four quantization blocks of the o_proj input row, one per warp
+        if (qo.q != nullptr) quantize_block_lanes(o, (t * nq + h) * (HEAD_DIM / QK) + warp, lane, qo);
     }
 }
 
@@ -213,13 +225,148 @@ __global__ void __launch_bounds__(256) k_silu_mul(const float4 *__restrict__ gat
     out[i] = make_float4(f(g.x, u.x), f(g.y, u.y), f(g.z, u.z), f(g.w, u.w));
 }
 
-// gu [T][2F] -> out [T][F]
+// Prompt attention: one CTA per (block of 8 query tokens, kv head).  Warp w owns query token t0 + w and the
+// G = nq / nkv (<= 4) query heads that share the kv head, so a key/value tile (32 keys, staged once in shared
+// memory as fp16) serves 8 * G queries instead of being re-read from L2 by every (token, head).  Scores: lane =
+// key of the tile, 128-dim dot products against the warp's pre-scaled queries (broadcast reads); online softmax
+// per (token, head) with warp reductions; values: lane = 4 output dims, keys of the tile in turn.
+constexpr int ATT_QT = 8, ATT_GMAX = 4, ATT_KT = 32, ATT_KROW = HEAD_DIM + 8;   // padded key rows: conflict-free 16-byte reads
+__global__ void __launch_bounds__(256) k_attention_prefill(const float *__restrict__ q, const __half *__restrict__ k_cache,
+                                                           const __half *__restrict__ v_cache, const int *__restrict__ pos0_dev, int T, int nq,
+                                                           int nkv, int max_pos, float scale, float *__restrict__ out)
+{
+    __shared__ __align__(16) float qs[ATT_QT][ATT_GMAX][HEAD_DIM];
+    __shared__ __align__(16) __half ks[ATT_KT][ATT_KROW];
+    __shared__ __align__(16) __half vs[ATT_KT][HEAD_DIM];
+    __shared__ __align__(16) float ps[ATT_QT][ATT_GMAX][ATT_KT];
+    const int G = nq / nkv;
+    const int t0 = blockIdx.x * ATT_QT, g = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = t0 + warp;
+    const int pos0 = *pos0_dev;
+    const int my_keys = (t < T) ? min(pos0 + t + 1, max_pos) : 0;               // causal: keys 0 .. pos0 + t
+    const int cta_keys = min(pos0 + min(t0 + ATT_QT, T), max_pos);
+    for (int i = threadIdx.x; i < ATT_QT * G * (HEAD_DIM / 4); i += 256) {
+        const int d4 = i % (HEAD_DIM / 4), hh = (i / (HEAD_DIM / 4)) % G, w = i / (HEAD_DIM / 4) / G;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t0 + w < T) v = reinterpret_cast<const float4 *>(q + (static_cast<size_t>(t0 + w) * nq + g * G + hh) * HEAD_DIM)[d4];
+        reinterpret_cast<float4 *>(qs[w][hh])[d4] = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
+    }
+    const __half *kb = k_cache + static_cast<size_t>(g) * max_pos * HEAD_DIM;
+    const __half *vb = v_cache + static_cast<size_t>(g) * max_pos * HEAD_DIM;
+    float mrun[ATT_GMAX], lrun[ATT_GMAX], acc[ATT_GMAX][4];
+#pragma unroll
+    for (int hh = 0; hh < ATT_GMAX; hh++) {
+        mrun[hh] = -INFINITY;
+        lrun[hh] = 0.0f;
+        acc[hh][0] = acc[hh][1] = acc[hh][2] = acc[hh][3] = 0.0f;
+    }
+    for (int k0 = 0; k0 < cta_keys; k0 += ATT_KT) {
+        __syncthreads();   // the previous tile is consumed (and, first time, qs is written)
+        for (int i = threadIdx.x; i < ATT_KT * (HEAD_DIM / 8); i += 256) {
+            const int r = i / (HEAD_DIM / 8), c = i % (HEAD_DIM / 8);
+            uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+            if (k0 + r < cta_keys) {
+                kv = reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(k0 + r) * HEAD_DIM)[c];
+                vv = reinterpret_cast<const uint4 *>(vb + static_cast<size_t>(k0 + r) * HEAD_DIM)[c];
+            }
+            *reinterpret_cast<uint4 *>(&ks[r][c * 8]) = kv;
+            *reinterpret_cast<uint4 *>(&vs[r][c * 8]) = vv;
+        }
+        __syncthreads();
+        if (k0 >= my_keys) continue;   // warp-uniform: this token sees none of the tile's keys
+        // ---- scores of key k0 + lane for the warp's G heads
+        float sdot[ATT_GMAX] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int c = 0; c < HEAD_DIM / 8; c++) {
+            const uint4 pk = *reinterpret_cast<const uint4 *>(&ks[lane][c * 8]);
+            const uint32_t wd[4] = {pk.x, pk.y, pk.z, pk.w};
+            float kf[8];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&wd[i]));
+                kf[2 * i] = f.x;
+                kf[2 * i + 1] = f.y;
+            }
+#pragma unroll
+            for (int hh = 0; hh < ATT_GMAX; hh++) {
+                if (hh < G) {
+                    const float4 qa = *reinterpret_cast<const float4 *>(&qs[warp][hh][c * 8]);
+                    const float4 qb = *reinterpret_cast<const float4 *>(&qs[warp][hh][c * 8 + 4]);
+                    sdot[hh] = fmaf(qa.x, kf[0], sdot[hh]);
+                    sdot[hh] = fmaf(qa.y, kf[1], sdot[hh]);
+                    sdot[hh] = fmaf(qa.z, kf[2], sdot[hh]);
+                    sdot[hh] = fmaf(qa.w, kf[3], sdot[hh]);
+                    sdot[hh] = fmaf(qb.x, kf[4], sdot[hh]);
+                    sdot[hh] = fmaf(qb.y, kf[5], sdot[hh]);
+                    sdot[hh] = fmaf(qb.z, kf[6], sdot[hh]);
+                    sdot[hh] = fmaf(qb.w, kf[7], sdot[hh]);
+                }
+            }
+        }
+        const bool visible = (k0 + lane) < my_keys;
+#pragma unroll
+        for (int hh = 0; hh < ATT_GMAX; hh++) {
+            if (hh < G) {
+                const float sc = visible ? sdot[hh] : -INFINITY;
+                float tmax = sc;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+                const float mnew = fmaxf(mrun[hh], tmax);        // finite: key k0 is visible to this token
+                const float pe = visible ? __expf(sc - mnew) : 0.0f;
+                float tsum = pe;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) tsum += __shfl_xor_sync(0xffffffffu, tsum, o);
+                const float corr = __expf(mrun[hh] - mnew);      // exp(-inf) = 0 on the first tile
+                lrun[hh] = lrun[hh] * corr + tsum;
+                mrun[hh] = mnew;
+                acc[hh][0] *= corr;
+                acc[hh][1] *= corr;
+                acc[hh][2] *= corr;
+                acc[hh][3] *= corr;
+                ps[warp][hh][lane] = pe;
+            }
+        }
+        __syncwarp();
+        // ---- values: lane owns output dims 4*lane .. 4*lane+3
+        const int nk = min(ATT_KT, my_keys - k0);
+        for (int j = 0; j < nk; j++) {
+            const uint2 pk = *reinterpret_cast<const uint2 *>(&vs[j][lane * 4]);
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.x));
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.y));
+#pragma unroll
+            for (int hh = 0; hh < ATT_GMAX; hh++) {
+                if (hh < G) {
+                    const float pj = ps[warp][hh][j];
+                    acc[hh][0] = fmaf(pj, f0.x, acc[hh][0]);
+                    acc[hh][1] = fmaf(pj, f0.y, acc[hh][1]);
+                    acc[hh][2] = fmaf(pj, f1.x, acc[hh][2]);
+                    acc[hh][3] = fmaf(pj, f1.y, acc[hh][3]);
+                }
+            }
+        }
+        __syncwarp();   // ps is rewritten by the next tile
+    }
+    if (t < T) {
+#pragma unroll
+        for (int hh = 0; hh < ATT_GMAX; hh++) {
+            if (hh < G) {
+                const float inv = 1.0f / lrun[hh];
+                reinterpret_cast<float4 *>(out + (static_cast<size_t>(t) * nq + g * G + hh) * HEAD_DIM)[lane] =
+                    make_float4(acc[hh][0] * inv, acc[hh][1] * inv, acc[hh][2] * inv, acc[hh][3] * inv);
+            }
+        }
+    }
+}
+
+// gu [T][2F] in (32 gate, 32 up) column groups -> out [T][F]: out[k] = SiLU(gu[64*(k/32) + k%32]) * gu[64*(k/32) + 32 + k%32]
 __global__ void __launch_bounds__(256) k_silu_mul_rows(const float4 *__restrict__ gu, int T, int F4, float4 *__restrict__ out)
 {
     const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= static_cast<long long>(T) * F4) return;
-    const long long t = i / F4, c = i % F4;
-    const float4 g = gu[t * 2 * F4 + c], u = gu[t * 2 * F4 + F4 + c];
+    const long long t = i / F4, c = i % F4;            // c: float4 index inside the row; 8 float4 per 32-element block
+    const long long src = t * 2 * F4 + (c / 8) * 16 + (c % 8);
+    const float4 g = gu[src], u = gu[src + 8];
     auto f = [](float a, float b) { return a / (1.0f + __expf(-a)) * b; };
     out[i] = make_float4(f(g.x, u.x), f(g.y, u.y), f(g.z, u.z), f(g.w, u.w));
 }
@@ -340,19 +487,45 @@ int inkq_glue_qknorm_rope_cache(inkq_ctx *ctx, const float *qkv_dev, const float
     INKQ_REQUIRE(ctx, qkv_dev && q_norm_w && k_norm_w && cos_dev && sin_dev && pos0_dev && q_out_dev && k_cache_dev && v_cache_dev, "null argument");
     INKQ_REQUIRE(ctx, T >= 1 && nq >= 1 && nkv >= 1 && nq % nkv == 0 && max_pos >= 1, "bad head configuration");
     const int items = T * (nq + 2 * nkv);
-    k_qknorm_rope_cache<<<(items + 7) / 8, 256, 0, ctx->stream>>>(qkv_dev, q_norm_w, k_norm_w, cos_dev, sin_dev, pos0_dev, T, nq, nkv, max_pos, eps,
-                                                               q_out_dev, reinterpret_cast<__half *>(k_cache_dev),
-                                                               reinterpret_cast<__half *>(v_cache_dev));
+    launch_pdl(k_qknorm_rope_cache, dim3((items + 7) / 8), dim3(256), 0, ctx->stream, qkv_dev, q_norm_w, k_norm_w, cos_dev, sin_dev, pos0_dev, T, nq,
+               nkv, max_pos, eps, q_out_dev, reinterpret_cast<__half *>(k_cache_dev), reinterpret_cast<__half *>(v_cache_dev));
     return after_launch(ctx, "k_qknorm_rope_cache");
 }
+
+static int attention_impl(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev, int T,
+                          int nq, int nkv, int max_pos, float scale, float *out_dev, const QuantOut &qo);
 
 int inkq_glue_attention(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev, int T,
                         int nq, int nkv, int max_pos, float scale, float *out_dev)
 {
     int rc = glue_use(ctx);
     if (rc) return rc;
-    INKQ_REQUIRE(ctx, q_dev && k_cache_dev && v_cache_dev && pos0_dev && out_dev, "null argument");
+    INKQ_REQUIRE(ctx, out_dev != nullptr, "null argument");
+    return attention_impl(ctx, q_dev, k_cache_dev, v_cache_dev, pos0_dev, T, nq, nkv, max_pos, scale, out_dev, QuantOut{});
+}
+
+int inkq_glue_attention_quant(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev,
+                              int nq, int nkv, int max_pos, float scale, inkq_act *out, int out_qmode)
+{
+    int rc = glue_use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, out != nullptr && out->K == nq * HEAD_DIM, "the output activation handle must have been created for K = nq * 128");
+    INKQ_REQUIRE(ctx, out_qmode == INKQ_Q8_1_F16 || out_qmode == INKQ_Q8_0_F16 || out_qmode == INKQ_Q8_1_F32, "bad output quantization mode");
+    return attention_impl(ctx, q_dev, k_cache_dev, v_cache_dev, pos0_dev, 1, nq, nkv, max_pos, scale, nullptr, quant_out_of(out, nq * HEAD_DIM, out_qmode));
+}
+
+static int attention_impl(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev, int T,
+                          int nq, int nkv, int max_pos, float scale, float *out_dev, const QuantOut &qo)
+{
+    int rc = INKQ_OK;
+    INKQ_REQUIRE(ctx, q_dev && k_cache_dev && v_cache_dev && pos0_dev, "null argument");
     INKQ_REQUIRE(ctx, T >= 1 && nq % nkv == 0 && max_pos >= 1, "bad head configuration");
+    if (T >= 16 && nq / nkv <= ATT_GMAX) {   // a prompt: key/value tiles shared by 8 tokens x the heads of a kv group
+        k_attention_prefill<<<dim3((T + ATT_QT - 1) / ATT_QT, nkv), 256, 0, ctx->stream>>>(
+            q_dev, reinterpret_cast<const __half *>(k_cache_dev), reinterpret_cast<const __half *>(v_cache_dev), pos0_dev, T, nq, nkv, max_pos,
+            scale, out_dev);
+        return after_launch(ctx, "k_attention_prefill");
+    }
     // few (token, head) items (a decode step): 16 warps per item so that the item's keys are spread over more
     // loads in flight; many items (a prompt): 4 warps per item, the grid fills the machine
     const bool wide = T * nq <= 4 * ctx->num_sms;
@@ -362,10 +535,10 @@ int inkq_glue_attention(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cac
     const __half *kc = reinterpret_cast<const __half *>(k_cache_dev), *vc = reinterpret_cast<const __half *>(v_cache_dev);
     if (wide) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(k_attention<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        k_attention<512><<<T * nq, 512, smem, ctx->stream>>>(q_dev, kc, vc, pos0_dev, T, nq, nkv, max_pos, scale, out_dev);
+        launch_pdl(k_attention<512>, dim3(T * nq), dim3(512), smem, ctx->stream, q_dev, kc, vc, pos0_dev, T, nq, nkv, max_pos, scale, out_dev, qo);
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(k_attention<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        k_attention<128><<<T * nq, 128, smem, ctx->stream>>>(q_dev, kc, vc, pos0_dev, T, nq, nkv, max_pos, scale, out_dev);
+        k_attention<128><<<T * nq, 128, smem, ctx->stream>>>(q_dev, kc, vc, pos0_dev, T, nq, nkv, max_pos, scale, out_dev, qo);
     }
     return after_launch(ctx, "k_attention");
 }
@@ -385,7 +558,7 @@ int inkq_glue_silu_mul_rows(inkq_ctx *ctx, const float *gu_dev, int T, int F, fl
 {
     int rc = glue_use(ctx);
     if (rc) return rc;
-    INKQ_REQUIRE(ctx, gu_dev && out_dev && T >= 1 && F >= 4 && F % 4 == 0, "bad silu_mul_rows arguments");
+    INKQ_REQUIRE(ctx, gu_dev && out_dev && T >= 1 && F >= 32 && F % 32 == 0, "bad silu_mul_rows arguments (F must be a multiple of 32)");
     const long long n4 = static_cast<long long>(T) * (F / 4);
     k_silu_mul_rows<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, ctx->stream>>>(reinterpret_cast<const float4 *>(gu_dev), T, F / 4,
                                                                                     reinterpret_cast<float4 *>(out_dev));

@@ -162,8 +162,9 @@ int inkq_ctx_create(int device, void *stream, inkq_ctx **out)
                                                         std::to_string(prop.major) + "." + std::to_string(prop.minor));
     }
     ctx->num_sms = prop.multiProcessorCount;
-    if ((e = cudaMalloc(reinterpret_cast<void **>(&ctx->dev_flag), sizeof(int))) != cudaSuccess ||
-        (e = cudaMemset(ctx->dev_flag, 0, sizeof(int))) != cudaSuccess) {
+    // word 0: set by a kernel whose bounded wait ran out; word 1: ticket counter of the decode GEMV's last-CTA epilogue
+    if ((e = cudaMalloc(reinterpret_cast<void **>(&ctx->dev_flag), 4 * sizeof(int))) != cudaSuccess ||
+        (e = cudaMemset(ctx->dev_flag, 0, 4 * sizeof(int))) != cudaSuccess) {
         delete ctx;
         return fail(nullptr, INKQ_ERR_ALLOC, std::string("context allocation: ") + cudaGetErrorString(e));
     }

@@ -123,6 +123,25 @@ int fail(inkq_ctx *ctx, int code, const std::string &msg);
         if (!(cond)) return ::inkq::fail((ctx), INKQ_ERR_INVALID, (msg));       \
     } while (0)
 
+// Launch with programmatic stream serialization: the grid may be scheduled while its predecessor in the stream is
+// still running; the kernel must execute griddepcontrol.wait before it touches anything the predecessor writes
+// (everything before that instruction overlaps the predecessor's tail).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Checks the launch, counts it.
 int after_launch(inkq_ctx *ctx, const char *what);
 

@@ -26,82 +26,15 @@
 
 #include "inkq_internal.h"
 #include "ptx.cuh"
+#include "qgemv_common.cuh"
 
 namespace inkq {
-
-constexpr int GEMV_UNROLL = 2;   // pairs per batch; two batches are in flight per lane
-
-__device__ __forceinline__ void dots_of_pair(const uint4 c0, const uint4 c1, const uint32_t *__restrict__ a_lo,
-                                             const uint32_t *__restrict__ a_hi, int &ilo, int &ihi)
-{
-    const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-    ilo = 0;
-    ihi = 0;
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        ilo = __dp4a(static_cast<int>(w[i] & 0x0F0F0F0Fu), static_cast<int>(a_lo[i]), ilo);
-        ihi = __dp4a(static_cast<int>((w[i] >> 4) & 0x0F0F0F0Fu), static_cast<int>(a_hi[i]), ihi);
-    }
-}
-
-// One batch of GEMV_UNROLL pairs of this lane's row, as loaded.
-struct PairBatch {
-    uint4 ca[GEMV_UNROLL], cb[GEMV_UNROLL];
-    uint2 sc[GEMV_UNROLL];
-    uchar2 z[GEMV_UNROLL];
-};
-
-template <bool HAS_MIN>
-__device__ __forceinline__ void load_batch(PairBatch &b, const uint8_t *__restrict__ nibT, const uint2 *__restrict__ sc16,
-                                           const uchar2 *__restrict__ zpT, size_t slab, int r, int p0, int p_end)
-{
-#pragma unroll
-    for (int u = 0; u < GEMV_UNROLL; u++) {
-        const int p = min(p0 + u, p_end - 1);  // clamped duplicates are loaded but never used
-        const size_t rec = (slab + p) * TILE_N + r;
-        const uint8_t *src = nibT + rec * 32;
-        b.ca[u] = ldg_stream_v4(src);
-        b.cb[u] = ldg_stream_v4(src + 16);
-        b.sc[u] = ldg_stream_v2(sc16 + rec);
-        if (!HAS_MIN) b.z[u] = zpT[rec];
-    }
-}
-
-template <bool HAS_MIN>
-__device__ __forceinline__ float consume_batch(const PairBatch &b, float acc, bool swz, const uint32_t *__restrict__ qa, const float *__restrict__ da,
-                                               const float *__restrict__ sa, int p0, int p_end)
-{
-#pragma unroll
-    for (int u = 0; u < GEMV_UNROLL; u++) {
-        const int p = p0 + u;
-        if (p < p_end) {
-            int ilo, ihi;
-            dots_of_pair(swz ? b.cb[u] : b.ca[u], swz ? b.ca[u] : b.cb[u], qa + p * 16, qa + p * 16 + 8, ilo, ihi);
-            const float2 dw = __half22float2(*reinterpret_cast<const __half2 *>(&b.sc[u].x));
-            const float da_lo = da[2 * p], da_hi = da[2 * p + 1];
-            if (HAS_MIN) {
-                const float2 mw = __half22float2(*reinterpret_cast<const __half2 *>(&b.sc[u].y));
-                acc = fmaf(static_cast<float>(ilo), __fmul_rn(da_lo, dw.x), acc);
-                acc = fmaf(static_cast<float>(ihi), __fmul_rn(da_hi, dw.y), acc);
-                acc = fmaf(mw.x, sa[2 * p], acc);
-                acc = fmaf(mw.y, sa[2 * p + 1], acc);
-            } else {
-                const int32_t *is = reinterpret_cast<const int32_t *>(sa);
-                ilo -= static_cast<int>(b.z[u].x) * is[2 * p];
-                ihi -= static_cast<int>(b.z[u].y) * is[2 * p + 1];
-                acc = fmaf(static_cast<float>(ilo), __fmul_rn(da_lo, dw.x), acc);
-                acc = fmaf(static_cast<float>(ihi), __fmul_rn(da_hi, dw.y), acc);
-            }
-        }
-    }
-    return acc;
-}
 
 // What a fused launch does around the matrix-vector product (decode step of a model: one launch per layer
 // instead of norm + quantizer + QGEMV + residual add).  The quantization arithmetic is the quantizer's own,
 // operation for operation, so the result equals quantize + QGEMV on the same fp32 row.
 struct FusedM1 {
-    const float *x;      // fp32 input row: K values (PRO_SILU_MUL: 2K values, gate then up)
+    const float *x;      // fp32 input row: K values (PRO_SILU_MUL: 2K values in (32 gate, 32 up) groups)
     const float *g;      // PRO_RMSNORM: the norm's weight vector
     float eps;
     int pro;             // PRO_*
@@ -110,14 +43,6 @@ struct FusedM1 {
 };
 enum { PRO_PLAIN = 0, PRO_RMSNORM = 1, PRO_SILU_MUL = 2 };
 
-__device__ __forceinline__ uint32_t pack_sat_s8x4_m1(int a, int b, int c, int d)
-{
-    uint32_t hi, out;
-    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(d), "r"(c), "r"(0));
-    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(b), "r"(a), "r"(hi));
-    return out;
-}
-
 // Builds the quantized activation row in shared memory from fp32 input (two lanes per 32-element block, as
 // k_quantize_q8): optional RMSNorm (x * 1/sqrt(mean(x^2) + eps) * g) or SiLU(gate) * up first.
 template <bool HAS_MIN>
@@ -125,12 +50,30 @@ __device__ __forceinline__ void fused_prologue(const FusedM1 &f, int K, uint32_t
 {
     const int nb = K / QK;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int half = threadIdx.x & 1;
+    const unsigned gmask = 0x3u << (threadIdx.x & 30);                     // the two lanes of a block
+    // When the row fits one trip of the block loop (K <= 16 * blockDim.x) the values read for the sum of squares
+    // stay in registers for the quantization: every CTA of the grid reads the row, so a second read doubles the
+    // L2 traffic of the prologue.
+    const bool single_trip = nb <= static_cast<int>(blockDim.x >> 1);
+    float4 keep[4];
     float inv = 1.0f;
     if (f.pro == PRO_RMSNORM) {
         float ss = 0.0f;
-        for (int i = threadIdx.x; i < K / 4; i += blockDim.x) {
-            const float4 v = reinterpret_cast<const float4 *>(f.x)[i];
-            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        if (single_trip) {
+            const int blk = threadIdx.x >> 1;
+            if (blk < nb) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    keep[j] = reinterpret_cast<const float4 *>(f.x)[blk * 8 + 2 * j + half];
+                    ss += keep[j].x * keep[j].x + keep[j].y * keep[j].y + keep[j].z * keep[j].z + keep[j].w * keep[j].w;
+                }
+            }
+        } else {
+            for (int i = threadIdx.x; i < K / 4; i += blockDim.x) {
+                const float4 v = reinterpret_cast<const float4 *>(f.x)[i];
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -141,19 +84,20 @@ __device__ __forceinline__ void fused_prologue(const FusedM1 &f, int K, uint32_t
         inv = 1.0f / sqrtf(tot / static_cast<float>(K) + f.eps);
         __syncthreads();   // red is reused for the slice partials
     }
-    const int half = threadIdx.x & 1;
-    const unsigned gmask = 0x3u << (threadIdx.x & 30);                     // the two lanes of a block
     for (int blk = threadIdx.x >> 1; blk < nb; blk += blockDim.x >> 1) {   // both lanes of a pair run the same trip count
         float4 v[4];
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int i4 = blk * 8 + 2 * j + half;
-            float4 t = reinterpret_cast<const float4 *>(f.x)[i4];
+            float4 t;
+            if (f.pro == PRO_RMSNORM && single_trip) t = keep[j];
+            else if (f.pro == PRO_SILU_MUL) t = reinterpret_cast<const float4 *>(f.x)[blk * 16 + 2 * j + half];   // gate half of the group
+            else t = reinterpret_cast<const float4 *>(f.x)[i4];
             if (f.pro == PRO_RMSNORM) {
                 const float4 gg = reinterpret_cast<const float4 *>(f.g)[i4];
                 t = make_float4(t.x * inv * gg.x, t.y * inv * gg.y, t.z * inv * gg.z, t.w * inv * gg.w);
             } else if (f.pro == PRO_SILU_MUL) {
-                const float4 u = reinterpret_cast<const float4 *>(f.x + K)[i4];
+                const float4 u = reinterpret_cast<const float4 *>(f.x)[blk * 16 + 8 + 2 * j + half];                   // up half
                 auto act = [](float a, float b) { return a / (1.0f + __expf(-a)) * b; };
                 t = make_float4(act(t.x, u.x), act(t.y, u.y), act(t.z, u.z), act(t.w, u.w));
             }

@@ -47,16 +47,18 @@ def torch_forward(torch, model, tokens):
         x = x + lin(ly["o"], a, cfg.hidden)
         h = rms(x, ly["ln2"])
         gu = lin(ly["gate_up"], h, 2 * cfg.ffn)
-        act = torch.nn.functional.silu(gu[:, :cfg.ffn]) * gu[:, cfg.ffn:]
+        gu = gu.view(T, cfg.ffn // 32, 2, 32)                     # (32 gate, 32 up) column groups
+        act = (torch.nn.functional.silu(gu[:, :, 0, :]) * gu[:, :, 1, :]).reshape(T, cfg.ffn)
         x = x + lin(ly["down"], act, cfg.hidden)
     last = rms(x[T - 1:T], model.final_norm)
     return last
 
 
-def test_forward_matches_pytorch_graph(pkg, gpu):
+@pytest.mark.parametrize("T", [13, 45])     # per-(token, head) attention kernel / tiled prompt kernel (two key tiles)
+def test_forward_matches_pytorch_graph(pkg, gpu, T):
     import torch
     model = pkg.qwen3_forward.Qwen3Synthetic(pkg, gpu, small_cfg(pkg), seed=1)
-    tokens = torch.from_numpy(pkg.synth.tokens(13, 1024, 5)).cuda()
+    tokens = torch.from_numpy(pkg.synth.tokens(T, 1024, 5)).cuda()
     model.reset()
     logits = model.prefill(tokens).clone()
     gpu.synchronize()
@@ -75,7 +77,7 @@ def test_forward_matches_pytorch_graph(pkg, gpu):
         assert int(model.token.item()) == int(ref.argmax().item())
     else:
         assert int(model.token.item()) in torch.topk(ref.flatten(), 8).indices.tolist()
-    assert int(model.pos.item()) == 13
+    assert int(model.pos.item()) == T
 
 
 def test_decode_path_and_graph_agree_with_prefill(pkg, gpu):
@@ -159,12 +161,92 @@ def test_fused_and_unfused_decode_agree(pkg, gpu):
     import torch
     toks = torch.from_numpy(pkg.synth.tokens(9, 1024, 6)).cuda()
     logits = []
-    for fused in (False, True):
-        model = pkg.qwen3_forward.Qwen3Synthetic(pkg, gpu, small_cfg(pkg, fused_decode=fused), seed=2)
+    for mode in ("separate", "prologue", "epilogue"):
+        model = pkg.qwen3_forward.Qwen3Synthetic(pkg, gpu, small_cfg(pkg, decode_mode=mode), seed=2)
         model.reset()
         model.prefill(toks[:8])
         model.token.copy_(toks[8:9])
         logits.append(model.decode_step().clone())
         gpu.synchronize()
-    rel = (logits[0] - logits[1]).abs().max().item() / logits[0].abs().max().item()
-    assert rel < 2e-2, rel
+    for other in logits[1:]:
+        rel = (logits[0] - other).abs().max().item() / logits[0].abs().max().item()
+        assert rel < 2e-2, rel
+
+
+def test_decode_gemv_epilogues_equal_separate_kernels(pkg, gpu):
+    """inkq_glue_decode_gemv / _rmsnorm_quant / _attention_quant against the separate operators: accumulate and the
+    gate/up pair epilogue reproduce them bit for bit (same quantizer arithmetic on the same fp32 values); the
+    RMSNorm epilogue sums the squares in another order, so its quantized row may differ by a flipped rounding."""
+    import ctypes as C
+    import torch
+    L, h = gpu.L, gpu.h
+    P = lambda t: C.c_void_p(t.data_ptr())
+    K, N = 512, 384
+    w = pkg.synth.weights(N, K, 33)
+    wh = gpu.weight(pkg.A81W41, pkg.SCALES_F16, w["nib"], w["d"], w["m"])
+    x = torch.randn((1, K), device="cuda")
+    a_in = gpu.act(1, K)
+    gpu.quantize(a_in, x, 1, pkg.Q8_1_F16)
+    ref = torch.empty((1, N), device="cuda")
+    gpu.linear(wh, x, 1, ref, N)
+    # 0: store, 1: accumulate
+    out = torch.zeros((1, N), device="cuda")
+    gpu.check(L.inkq_glue_decode_gemv(h, wh.h, a_in.h, P(out), 0, None, C.c_float(0), None, pkg.Q8_1_F16, None))
+    gpu.synchronize()
+    assert torch.equal(out, ref)
+    base = torch.randn((1, N), device="cuda")
+    acc = base.clone()
+    gpu.check(L.inkq_glue_decode_gemv(h, wh.h, a_in.h, P(acc), 1, None, C.c_float(0), None, pkg.Q8_1_F16, None))
+    gpu.synchronize()
+    assert torch.equal(acc, base + ref)
+    # 2: accumulate, then RMSNorm + quantizer by the last CTA (twice in a row: the ticket counter must come back to zero)
+    g = torch.rand(N, device="cuda") + 0.5
+    a_out = gpu.act(1, N)
+    xn = torch.empty((1, N), device="cuda")
+    for _ in range(2):
+        acc = base.clone()
+        gpu.check(L.inkq_glue_decode_gemv(h, wh.h, a_in.h, P(acc), 2, P(g), C.c_float(1e-6), a_out.h, pkg.Q8_1_F16, P(xn)))
+        gpu.synchronize()
+        want = base + ref
+        assert torch.equal(acc, want)
+        xn_ref = torch.empty_like(want)
+        gpu.check(L.inkq_glue_rmsnorm(h, P(want), P(g), 1, N, C.c_float(1e-6), P(xn_ref)))
+        a_ref = gpu.act(1, N)
+        gpu.quantize(a_ref, xn_ref, 1, pkg.Q8_1_F16)
+        gpu.synchronize()
+        assert (xn - xn_ref).abs().max().item() <= 1e-5 * xn_ref.abs().max().item()
+        q1, d1, s1, _ = a_out.export(1)
+        q2, d2, s2, _ = a_ref.export(1)
+        assert np.abs(q1.astype(np.int32) - q2.astype(np.int32)).max() <= 1 and (q1 != q2).mean() < 0.01
+        assert np.allclose(d1, d2, rtol=2e-3) and np.allclose(s1, s2, rtol=0, atol=2e-3 * np.abs(s2).max())
+        # stand-alone rmsnorm_quant: same routine
+        a_sa = gpu.act(1, N)
+        gpu.check(L.inkq_glue_rmsnorm_quant(h, P(want), P(g), C.c_float(1e-6), N, a_sa.h, pkg.Q8_1_F16, None))
+        gpu.synchronize()
+        q3, d3, s3, _ = a_sa.export(1)
+        assert np.array_equal(q1, q3) and np.array_equal(d1, d3) and np.array_equal(s1, s3)
+    # 3: gate/up pairs -> SiLU * up -> quantized row of N/2
+    a_pair = gpu.act(1, N // 2)
+    gpu.check(L.inkq_glue_decode_gemv(h, wh.h, a_in.h, None, 3, None, C.c_float(0), a_pair.h, pkg.Q8_1_F16, None))
+    act = torch.empty((1, N // 2), device="cuda")
+    gpu.check(L.inkq_glue_silu_mul_rows(h, P(ref), 1, N // 2, P(act)))
+    a_ref = gpu.act(1, N // 2)
+    gpu.quantize(a_ref, act, 1, pkg.Q8_1_F16)
+    gpu.synchronize()
+    for got, want_ in zip(a_pair.export(1), a_ref.export(1)):
+        assert np.array_equal(got, want_)
+    # attention with quantized output against attention + quantizer
+    nq, nkv, max_pos, pos = 4, 2, 64, 37
+    qv = torch.randn((1, nq * 128), device="cuda")
+    kc = torch.randn((nkv, max_pos, 128), device="cuda").half()
+    vc = torch.randn((nkv, max_pos, 128), device="cuda").half()
+    posd = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    o = torch.empty((1, nq * 128), device="cuda")
+    gpu.check(L.inkq_glue_attention(h, P(qv), P(kc), P(vc), P(posd), 1, nq, nkv, max_pos, C.c_float(0.088), P(o)))
+    a_ref = gpu.act(1, nq * 128)
+    gpu.quantize(a_ref, o, 1, pkg.Q8_1_F16)
+    a_att = gpu.act(1, nq * 128)
+    gpu.check(L.inkq_glue_attention_quant(h, P(qv), P(kc), P(vc), P(posd), nq, nkv, max_pos, C.c_float(0.088), a_att.h, pkg.Q8_1_F16))
+    gpu.synchronize()
+    for got, want_ in zip(a_att.export(1), a_ref.export(1)):
+        assert np.array_equal(got, want_)
