@@ -33,6 +33,7 @@
 // from L2 once per weight tile) + M*N*4 output.
 #include <cuda.h>
 #include <cuda_fp16.h>
+#include <stdlib.h>
 
 #include "inkq_internal.h"
 #include "ptx.cuh"
@@ -90,6 +91,7 @@ __device__ __forceinline__ void dequant4(uint32_t v, __half2 d2, __half2 m2, uin
     out23 = *reinterpret_cast<const uint32_t *>(&w23);
 }
 
+template <bool A_SW128>
 __global__ void __launch_bounds__(THREADS, 1) k_gemm_w41_tc(const __grid_constant__ CUtensorMap map_a, const Params prm)
 {
     extern __shared__ __align__(1024) unsigned char smem_dyn[];
@@ -181,12 +183,13 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_w41_tc(const __grid_constan
                     //    offset); the j-th K=16 slice starts 4096 B further.
                     // B: activations, 128-byte swizzled rows of 64 halves; slice j is the j-th 32-byte part of the
                     //    row; 8-row groups are 1024 B apart.  The start-address field counts 16-byte units.
-                    const uint64_t a_desc0 = umma_smem_desc(smem_u32(u16_base + u16.idx * U16_STAGE_BYTES), 2048, 128, 0);
+                    const uint64_t a_desc0 = A_SW128 ? umma_smem_desc(smem_u32(u16_base + u16.idx * U16_STAGE_BYTES), 16, 1024, 2)
+                                                     : umma_smem_desc(smem_u32(u16_base + u16.idx * U16_STAGE_BYTES), 2048, 128, 0);
                     const uint64_t b_desc0 = umma_smem_desc(smem_u32(raw_base + raw.idx * RAW_STAGE_BYTES), 16, 1024, 2);
 #pragma unroll
                     for (int j = 0; j < 4; j++)
-                        umma_f16(d_tmem, a_desc0 + static_cast<uint64_t>(j * (4096 >> 4)), b_desc0 + static_cast<uint64_t>(j * (32 >> 4)), idesc,
-                                 (p > 0 || j > 0) ? 1u : 0u);
+                        umma_f16(d_tmem, a_desc0 + static_cast<uint64_t>(j * ((A_SW128 ? 32 : 4096) >> 4)),
+                                 b_desc0 + static_cast<uint64_t>(j * (32 >> 4)), idesc, (p > 0 || j > 0) ? 1u : 0u);
                     umma_commit(&raw_empty[raw.idx]);
                     umma_commit(&u16_empty[u16.idx]);
                     raw.advance();
@@ -212,7 +215,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_w41_tc(const __grid_constan
                 if (!mbar_wait_abortable(abort_flag, &u16_empty[u16.idx], u16.phase ^ 1, 200u)) INKQ_GIVE_UP();
                 const unsigned char *wsrc = raw_base + raw.idx * RAW_STAGE_BYTES + RAW_A_BYTES;
                 const unsigned char *ssrc = wsrc + RAW_W_BYTES;
-                unsigned char *dst = u16_base + u16.idx * U16_STAGE_BYTES + (4 * hi) * 2048 + r * 16;
+                unsigned char *stage = u16_base + u16.idx * U16_STAGE_BYTES;
+                unsigned char *dst = stage + (4 * hi) * 2048 + r * 16;
                 const uint2 sc = *reinterpret_cast<const uint2 *>(ssrc + r * 8);   // {d_lo, d_hi | m_lo, m_hi}
                 const uint32_t dbits = hi ? (sc.x >> 16) : (sc.x & 0xFFFFu), mbits = hi ? (sc.y >> 16) : (sc.y & 0xFFFFu);
                 const __half2 d2 = __half2half2(__ushort_as_half(static_cast<unsigned short>(dbits)));
@@ -228,8 +232,15 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_w41_tc(const __grid_constan
                         dequant4(nib, d2, m2, o[2 * i], o[2 * i + 1]);
                     }
                     // elements 16c..16c+7 -> core matrix 2c, 16c+8..16c+15 -> core matrix 2c+1 of this block's four
-                    *reinterpret_cast<uint4 *>(dst + (2 * c) * 2048) = make_uint4(o[0], o[1], o[2], o[3]);
-                    *reinterpret_cast<uint4 *>(dst + (2 * c + 1) * 2048) = make_uint4(o[4], o[5], o[6], o[7]);
+                    if (A_SW128) {
+                        // rows of 128 B (the pair's 64 halves), 16-byte chunk cc stored at position cc ^ (r % 8)
+                        const int cc = 4 * hi + 2 * c;
+                        *reinterpret_cast<uint4 *>(stage + r * 128 + ((cc ^ (r & 7)) * 16)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        *reinterpret_cast<uint4 *>(stage + r * 128 + (((cc + 1) ^ (r & 7)) * 16)) = make_uint4(o[4], o[5], o[6], o[7]);
+                    } else {
+                        *reinterpret_cast<uint4 *>(dst + (2 * c) * 2048) = make_uint4(o[0], o[1], o[2], o[3]);
+                        *reinterpret_cast<uint4 *>(dst + (2 * c + 1) * 2048) = make_uint4(o[4], o[5], o[6], o[7]);
+                    }
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(&u16_full[u16.idx]);
@@ -313,15 +324,18 @@ int launch_gemm_w41_tc(inkq_ctx *ctx, const uint16_t *a16, int M, const Weight *
     prm.tiles_m = tiles_m;
     prm.block_m = block_m;
     prm.ldc = ldc;
+    static const bool sw128 = [] { const char *e = getenv("INKQ_W41_A_NOSWIZZLE"); return !(e != nullptr && e[0] == '1'); }();
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(k_gemm_w41_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(k_gemm_w41_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(k_gemm_w41_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return fail(ctx, INKQ_ERR_CUDA, std::string("cudaFuncSetAttribute(k_gemm_w41_tc): ") + cudaGetErrorString(e));
         configured = true;
     }
     const int total = prm.tiles_n * prm.tiles_m;
     const int grid = total < ctx->num_sms ? total : ctx->num_sms;
-    k_gemm_w41_tc<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(map, prm);
+    if (sw128) k_gemm_w41_tc<true><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(map, prm);
+    else k_gemm_w41_tc<false><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(map, prm);
     return after_launch(ctx, "k_gemm_w41_tc");
 }
 
