@@ -547,21 +547,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 #pragma unroll
                         for (int j4 = 0; j4 < CH; j4 += 4) {
                             if (j4 < ncols) {
-                                const float4 da = *reinterpret_cast<const float4 *>(sd + c * CH + j4);
+                                // 128-bit shared loads straight into 64-bit register pairs: (d_a[m], d_a[m+1]) is already the
+                                // packed operand of the f32x2 instructions, no pack moves
+                                const ulonglong2 da = *reinterpret_cast<const ulonglong2 *>(sd + c * CH + j4);
                                 const unsigned long long dw2 = pack2(dw, dw);
                                 const int a0 = (c * CH + j4) / 2;
-                                accp[a0] = fma2(cvt2_exact(raw[j4], raw[j4 + 1]), mul2(pack2(da.x, da.y), dw2),
-                                                accp[a0]);
-                                accp[a0 + 1] = fma2(cvt2_exact(raw[j4 + 2], raw[j4 + 3]), mul2(pack2(da.z, da.w), dw2),
-                                                    accp[a0 + 1]);
+                                accp[a0] = fma2(cvt2_exact(raw[j4], raw[j4 + 1]), mul2(da.x, dw2), accp[a0]);
+                                accp[a0 + 1] = fma2(cvt2_exact(raw[j4 + 2], raw[j4 + 3]), mul2(da.y, dw2), accp[a0 + 1]);
                                 if (HAS_MIN && hi) {
-                                    const float4 s0 = *reinterpret_cast<const float4 *>(ss_lo + c * CH + j4);
-                                    const float4 s1 = *reinterpret_cast<const float4 *>(ss_lo + BLOCK_M + c * CH + j4);
+                                    const ulonglong2 s0 = *reinterpret_cast<const ulonglong2 *>(ss_lo + c * CH + j4);
+                                    const ulonglong2 s1 = *reinterpret_cast<const ulonglong2 *>(ss_lo + BLOCK_M + c * CH + j4);
                                     const unsigned long long mlo = pack2(wsc.z, wsc.z), mhi = pack2(wsc.w, wsc.w);
-                                    accp[a0] = fma2(mlo, pack2(s0.x, s0.y), accp[a0]);
-                                    accp[a0] = fma2(mhi, pack2(s1.x, s1.y), accp[a0]);
-                                    accp[a0 + 1] = fma2(mlo, pack2(s0.z, s0.w), accp[a0 + 1]);
-                                    accp[a0 + 1] = fma2(mhi, pack2(s1.z, s1.w), accp[a0 + 1]);
+                                    accp[a0] = fma2(mlo, s0.x, accp[a0]);
+                                    accp[a0] = fma2(mhi, s1.x, accp[a0]);
+                                    accp[a0 + 1] = fma2(mlo, s0.y, accp[a0 + 1]);
+                                    accp[a0 + 1] = fma2(mhi, s1.y, accp[a0 + 1]);
                                 }
                             }
                         }

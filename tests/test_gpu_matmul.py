@@ -216,6 +216,27 @@ def test_weight_only_w41(pkg, gpu, oracle, M, N, K):
     assert bool((C[M] == 7.0).all())                          # nothing stored past row M
 
 
+def test_weight_only_w41_dequantisation_bits(pkg, gpu, oracle):
+    """One-hot fp16 activations read the dequantised weights back out of both GPU kernels: they must be the oracle's
+    single rounding of q*d + m bit for bit, also for scales of very different exponents."""
+    import torch
+    rng = np.random.default_rng(78)
+    N, K = 256, 128
+    q = rng.integers(0, 16, size=(N, K), dtype=np.uint8)
+    d = (rng.uniform(0.5, 2.0, size=(N, K // 32)) * 2.0 ** rng.integers(-12, 4, size=(N, K // 32))).astype(np.float16).astype(np.float32)
+    m = (rng.uniform(-2.0, 2.0, size=(N, K // 32)) * 2.0 ** rng.integers(-12, 4, size=(N, K // 32))).astype(np.float16).astype(np.float32)
+    nib = pkg.synth.pack_nibbles(q)
+    a16 = np.eye(K, dtype=np.float16)
+    wh = gpu.weight(3, 1, nib, d, m)
+    a_dev = torch.from_numpy(a16).cuda()
+    C, Cs = torch.empty((K, N), device="cuda"), torch.empty((K, N), device="cuda")
+    gpu.gemm_w41_f16act(a_dev, K, wh, C, N)
+    gpu.gemm_w41_f16act_simt(a_dev, K, wh, Cs, N)
+    gpu.synchronize()
+    ref = oracle.gemm_w41_f16act(a16, nib, d, m)
+    assert np.array_equal(C.cpu().numpy(), ref) and np.array_equal(Cs.cpu().numpy(), ref)
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 1000, 4096), (1, 16, 64), (5, 264, 512)])
 def test_lm_head_f16(pkg, gpu, oracle, M, N, K):
     import torch

@@ -107,6 +107,23 @@ def test_fp16_conversion_is_ieee_rne(oracle):
     assert np.array_equal(back, np.arange(0, 0x7C00, 7, dtype=np.uint16).view(np.float16).astype(np.float32))
 
 
+def test_w41_dequantised_weight_is_one_rounding_of_the_exact_value(oracle, pkg):
+    """Weight-only W41: w16 = fp16(q*d + m) rounded once from the exact value (what a half-precision fused
+    multiply-add returns).  One-hot fp16 activations read the dequantised weights back out of the matmul; NumPy's
+    float64 -> float16 conversion is the independent single rounding.  Scales cover a wide exponent range so that
+    double rounding through fp32 would show."""
+    rng = np.random.default_rng(77)
+    N, K = 64, 128
+    q = rng.integers(0, 16, size=(N, K), dtype=np.uint8)
+    d = (rng.uniform(0.5, 2.0, size=(N, K // 32)) * 2.0 ** rng.integers(-12, 4, size=(N, K // 32))).astype(np.float16)
+    m = (rng.uniform(-2.0, 2.0, size=(N, K // 32)) * 2.0 ** rng.integers(-12, 4, size=(N, K // 32))).astype(np.float16)
+    a16 = np.eye(K, dtype=np.float16)
+    got = oracle.gemm_w41_f16act(a16, pkg.synth.pack_nibbles(q), d.astype(np.float32), m.astype(np.float32))      # [K][N] = w16[n][k]
+    exact = q.astype(np.float64) * np.repeat(d.astype(np.float64), 32, axis=1) + np.repeat(m.astype(np.float64), 32, axis=1)
+    want = exact.astype(np.float16).astype(np.float32)
+    assert np.array_equal(got.T, want)
+
+
 def test_weight_quantizers_round_trip(oracle, pkg):
     """Q4_1 / Q4_0 format definitions (notebooks/quantize_methods.py:13-125)."""
     rng = np.random.default_rng(3)
