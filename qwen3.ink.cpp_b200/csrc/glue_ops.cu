@@ -240,7 +240,8 @@ __global__ void __launch_bounds__(256) k_attention_prefill(const float *__restri
     __shared__ __align__(16) __half vs[ATT_KT][HEAD_DIM];
     __shared__ __align__(16) float ps[ATT_QT][ATT_GMAX][ATT_KT];
     const int G = nq / nkv;
-    const int t0 = blockIdx.x * ATT_QT, g = blockIdx.y;
+    // the last token blocks see the most keys: they get the lowest CTA indices, so that they start first
+    const int t0 = (gridDim.x - 1 - blockIdx.x) * ATT_QT, g = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = t0 + warp;
     const int pos0 = *pos0_dev;
@@ -261,19 +262,35 @@ __global__ void __launch_bounds__(256) k_attention_prefill(const float *__restri
         lrun[hh] = 0.0f;
         acc[hh][0] = acc[hh][1] = acc[hh][2] = acc[hh][3] = 0.0f;
     }
+    // Key/value tiles go global -> registers -> shared memory; the registers of tile i+1 are loaded before tile i is
+    // consumed, so the L2 latency of a tile hides behind the arithmetic of its predecessor.
+    constexpr int LD_PER_THREAD = ATT_KT * (HEAD_DIM / 8) / 256;   // 2 x (key, value) 16-byte chunks per thread
+    uint4 kreg[LD_PER_THREAD], vreg[LD_PER_THREAD];
+    auto fetch_tile = [&](int k0) {
+#pragma unroll
+        for (int u = 0; u < LD_PER_THREAD; u++) {
+            const int i = threadIdx.x + u * 256;
+            const int r = i / (HEAD_DIM / 8), c = i % (HEAD_DIM / 8);
+            kreg[u] = make_uint4(0, 0, 0, 0);
+            vreg[u] = make_uint4(0, 0, 0, 0);
+            if (k0 + r < cta_keys) {
+                kreg[u] = reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(k0 + r) * HEAD_DIM)[c];
+                vreg[u] = reinterpret_cast<const uint4 *>(vb + static_cast<size_t>(k0 + r) * HEAD_DIM)[c];
+            }
+        }
+    };
+    fetch_tile(0);
     for (int k0 = 0; k0 < cta_keys; k0 += ATT_KT) {
         __syncthreads();   // the previous tile is consumed (and, first time, qs is written)
-        for (int i = threadIdx.x; i < ATT_KT * (HEAD_DIM / 8); i += 256) {
+#pragma unroll
+        for (int u = 0; u < LD_PER_THREAD; u++) {
+            const int i = threadIdx.x + u * 256;
             const int r = i / (HEAD_DIM / 8), c = i % (HEAD_DIM / 8);
-            uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-            if (k0 + r < cta_keys) {
-                kv = reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(k0 + r) * HEAD_DIM)[c];
-                vv = reinterpret_cast<const uint4 *>(vb + static_cast<size_t>(k0 + r) * HEAD_DIM)[c];
-            }
-            *reinterpret_cast<uint4 *>(&ks[r][c * 8]) = kv;
-            *reinterpret_cast<uint4 *>(&vs[r][c * 8]) = vv;
+            *reinterpret_cast<uint4 *>(&ks[r][c * 8]) = kreg[u];
+            *reinterpret_cast<uint4 *>(&vs[r][c * 8]) = vreg[u];
         }
         __syncthreads();
+        if (k0 + ATT_KT < cta_keys) fetch_tile(k0 + ATT_KT);
         if (k0 >= my_keys) continue;   // warp-uniform: this token sees none of the tile's keys
         // ---- scores of key k0 + lane for the warp's G heads
         float sdot[ATT_GMAX] = {0.f, 0.f, 0.f, 0.f};
