@@ -151,6 +151,8 @@ int inkq_ctx_create(int device, void *stream, inkq_ctx **out)
     ctx->pin_x_cap = ctx->pin_c_cap = 0;
     ctx->dev_flag = nullptr;
     ctx->encode_tiled = nullptr;
+    ctx->copy_stream = nullptr;
+    for (int i = 0; i < 4; i++) ctx->chunk_ev[i] = nullptr;
     cudaDeviceProp prop;
     if ((e = cudaSetDevice(device)) != cudaSuccess || (e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) {
         delete ctx;
@@ -190,6 +192,9 @@ int inkq_ctx_destroy(inkq_ctx *ctx)
     cudaFree(ctx->lin_x);
     cudaFree(ctx->lin_c);
     cudaFree(ctx->dev_flag);
+    if (ctx->copy_stream != nullptr) cudaStreamDestroy(ctx->copy_stream);
+    for (int i = 0; i < 4; i++)
+        if (ctx->chunk_ev[i] != nullptr) cudaEventDestroy(ctx->chunk_ev[i]);
     delete ctx;
     return INKQ_OK;
 }
@@ -622,6 +627,33 @@ int inkq_linear_host(inkq_ctx *ctx, const inkq_weight *w, const float *x_host, i
     const size_t xn = static_cast<size_t>(M) * w->K, cn = static_cast<size_t>(M) * w->rows;
     if ((rc = ensure_staging(ctx, xn, cn))) return rc;
     INKQ_CUDA(ctx, cudaMemcpyAsync(ctx->lin_x, x_host, xn * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    constexpr int CHUNKS = 4;
+    if (M > 1 && w->scheme != INKQ_W41 && w->tiles >= 2 * CHUNKS) {
+        // The result (M*N*4 bytes over PCIe) takes longer to copy back than to compute: the QGEMM runs in four
+        // launches over quarters of the weight tiles, and the columns of a finished quarter travel to the host on a
+        // second stream while the next quarter is computed.
+        if (ctx->copy_stream == nullptr) {
+            INKQ_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+            for (int i = 0; i < CHUNKS; i++) INKQ_CUDA(ctx, cudaEventCreateWithFlags(&ctx->chunk_ev[i], cudaEventDisableTiming));
+        }
+        if ((rc = ensure_scratch_act(ctx, M, w->K))) return rc;
+        inkq_act *act = static_cast<inkq_act *>(ctx->scratch_act);
+        const int qmode = (w->scheme == INKQ_A81W41) ? INKQ_Q8_1_F32 : INKQ_Q8_0_F16;
+        if ((rc = inkq_quantize(ctx, qmode, ctx->lin_x, M, w->K, act))) return rc;
+        for (int c = 0; c < CHUNKS; c++) {
+            const int t0 = static_cast<int>(static_cast<long long>(w->tiles) * c / CHUNKS);
+            const int t1 = static_cast<int>(static_cast<long long>(w->tiles) * (c + 1) / CHUNKS);
+            if ((rc = launch_gemm_tc(ctx, act, w, ctx->lin_c, w->rows, nullptr, nullptr, t0, t1 - t0))) return rc;
+            INKQ_CUDA(ctx, cudaEventRecord(ctx->chunk_ev[c], ctx->stream));
+            INKQ_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->chunk_ev[c], 0));
+            const int n0 = t0 * TILE_N, n1 = (t1 * TILE_N < w->rows) ? t1 * TILE_N : w->rows;
+            INKQ_CUDA(ctx, cudaMemcpy2DAsync(C_host + n0, static_cast<size_t>(ldc) * sizeof(float), ctx->lin_c + n0,
+                                             static_cast<size_t>(w->rows) * sizeof(float), static_cast<size_t>(n1 - n0) * sizeof(float), M,
+                                             cudaMemcpyDeviceToHost, ctx->copy_stream));
+        }
+        INKQ_CUDA(ctx, cudaStreamSynchronize(ctx->copy_stream));
+        return inkq_ctx_synchronize(ctx);
+    }
     if ((rc = inkq_linear(ctx, w, ctx->lin_x, M, ctx->lin_c, w->rows))) return rc;
     INKQ_CUDA(ctx, cudaMemcpy2DAsync(C_host, static_cast<size_t>(ldc) * sizeof(float), ctx->lin_c, static_cast<size_t>(w->rows) * sizeof(float),
                                      static_cast<size_t>(w->rows) * sizeof(float), M, cudaMemcpyDeviceToHost, ctx->stream));

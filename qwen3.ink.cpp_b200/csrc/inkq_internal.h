@@ -100,6 +100,8 @@ struct inkq_ctx {
     float *pin_x, *pin_c;    // pinned host staging of inkq_linear_host
     size_t pin_x_cap, pin_c_cap;
     void *encode_tiled;      // cuTensorMapEncodeTiled entry point
+    cudaStream_t copy_stream;   // inkq_linear_host: device-to-host copies of finished column chunks (created on first use)
+    cudaEvent_t chunk_ev[4];
 };
 struct inkq_weight : inkq::Weight {};
 struct inkq_act : inkq::Act {};
@@ -155,7 +157,9 @@ int launch_gemv(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, const Ex
 int launch_gemv_fused(inkq_ctx *ctx, const Weight *w, const float *x, int pro, const float *g, float eps, float *C, int accumulate);
 int launch_gemm_simt(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc);
 int launch_block_dots(inkq_ctx *ctx, const Act *a, const Weight *w, int32_t *dots);
-int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc, int32_t *dots, const ExtraDst *extra = nullptr);
+// tn_begin / tn_count: the launch covers the weight tiles (of 128 rows) tn_begin .. tn_begin + tn_count - 1 (default: all)
+int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc, int32_t *dots, const ExtraDst *extra = nullptr,
+                   int tn_begin = 0, int tn_count = -1);
 int launch_gemm_w41_f16(inkq_ctx *ctx, const uint16_t *a16, int M, const Weight *w, float *C, int ldc);   // CUDA cores
 int launch_gemm_w41_tc(inkq_ctx *ctx, const uint16_t *a16, int M, const Weight *w, float *C, int ldc);    // tcgen05 kind::f16
 // inkq_linear with further destinations for every output element (defined in inkq_api.cu)

@@ -84,7 +84,7 @@ struct TcParams {
     ExtraDst extra;  // further destinations of every C element (peers of a column-sharded layer)
     int32_t *dots;   // non-null: dump raw int32 block dots [M][rows][K/32] instead of computing C
     int *flag;
-    int M, M_ld, rows, K, pairs, tiles_n, tiles_m, block_m, ldc;
+    int M, M_ld, rows, K, pairs, tn0, tiles_n, tiles_m, block_m, ldc;   // this launch covers weight tiles tn0 .. tn0 + tiles_n - 1
 #ifdef INKQ_ROLE_TIMERS
     long long *timers;   // [gridDim.x][16] cycle counters, development only
 #endif
@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             Ring raw(RAW_STAGES);
             bool dead = false;
             for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
-                const int tn = tile / prm.tiles_m, tm = tile % prm.tiles_m;
+                const int tn = prm.tn0 + tile / prm.tiles_m, tm = tile % prm.tiles_m;
                 for (int ks = 0; ks < k_stages; ks++) {
                     if (!mbar_wait_abortable(abort_flag, &raw_empty[raw.idx], raw.phase ^ 1, 1000u)) INKQ_GIVE_UP();
                     const int np = min(STAGE_PAIRS, prm.pairs - ks * STAGE_PAIRS);
@@ -456,7 +456,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         const long long t_role0 = clock64();
 #endif
         for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
-            const int tn = tile / prm.tiles_m, tm = tile % prm.tiles_m;
+            const int tn = prm.tn0 + tile / prm.tiles_m, tm = tile % prm.tiles_m;
             const int n = tn * TILE_N + row;
             unsigned long long accp[CW / 2];
 #pragma unroll
@@ -670,8 +670,9 @@ static int encode2d(inkq_ctx *ctx, CUtensorMap *map, CUtensorMapDataType dt, int
     return INKQ_OK;
 }
 
-int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc, int32_t *dots, const ExtraDst *extra)
+int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc, int32_t *dots, const ExtraDst *extra, int tn_begin, int tn_count)
 {
+    if (tn_count < 0) tn_count = w->tiles - tn_begin;   // default: every tile from tn_begin on
     if (ctx->encode_tiled == nullptr) return fail(ctx, INKQ_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled entry point not available");
     const int M = a->M;
     // Split of the M activation rows into tiles of block_m columns (a multiple of 16, at most 128).  A tile's time
@@ -685,7 +686,7 @@ int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int l
         float best = 0.f;
         for (int tm = (M + 127) / 128; tm <= (M + 15) / 16; tm++) {
             const int bm = (((M + tm - 1) / tm) + 15) & ~15;
-            const long long total = static_cast<long long>(w->tiles) * tm;
+            const long long total = static_cast<long long>(tn_count) * tm;
             const float cost = static_cast<float>((total + ctx->num_sms - 1) / ctx->num_sms) * tile_us[bm / 16];
             if (best == 0.f || cost < best * 0.999f) {
                 best = cost;
@@ -718,7 +719,8 @@ int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int l
     prm.rows = w->rows;
     prm.K = w->K;
     prm.pairs = w->pairs;
-    prm.tiles_n = w->tiles;
+    prm.tn0 = tn_begin;
+    prm.tiles_n = tn_count;
     prm.tiles_m = tiles_m;
     prm.block_m = block_m;
     prm.ldc = ldc;

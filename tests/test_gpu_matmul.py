@@ -177,6 +177,24 @@ def test_full_prefill_shape(pkg, gpu, oracle):
     assert torch.equal(C3, C * 2.0)
 
 
+@pytest.mark.parametrize("scheme", [0, 1])
+def test_linear_host_chunked_copy_back(pkg, gpu, scheme):
+    """inkq_linear_host computes in four launches over quarters of the weight tiles and copies finished columns back
+    meanwhile: ragged last tile, padded host rows (ldc > N), equals the device path bit for bit and leaves the padding
+    untouched."""
+    import torch
+    M, N, K, ldc = 37, 1064, 128, 1072           # 9 weight tiles, the last one 40 rows
+    w = pkg.synth.weights(N, K, 41)
+    wh = gpu.weight(scheme, pkg.SCALES_F16, w["nib"], w["d"], w["m"] if scheme == 0 else None)
+    x = pkg.synth.activations(M, K, 41)
+    C = torch.empty((M, N), device="cuda")
+    gpu.linear(wh, torch.from_numpy(x).cuda(), M, C, N)
+    gpu.synchronize()
+    Ch = np.full((M, ldc), -7.0, np.float32)
+    gpu.linear_host(wh, x, M, Ch, ldc)
+    assert np.array_equal(Ch[:, :N], C.cpu().numpy()) and (Ch[:, N:] == -7.0).all()
+
+
 def test_mismatched_quantizer_mode_is_rejected(pkg, gpu, oracle):
     import torch
     x, w, wh, act, _ = setup(pkg, gpu, oracle, 0, 4, 16, 64, 0, qmode=0)   # Q8_0 activations, A81W41 weights
