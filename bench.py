@@ -10,11 +10,16 @@ shape: M=322 activations x K=4096, N=12288 A81W41 weights (fp32 block scales).
   e2e     the same metric through the host-buffer entry point (inkq_linear_host):
           pinned host activations in, host result out, copies inside the timed region
   N > 1   the weight rows (output columns) are sharded across the ranks, every rank
-          quantizes the full activations, runs its shard and an NCCL all-gather
-          assembles the fp32 output on every rank (strong scaling)
+          quantizes the full activations and runs its shard; the QGEMM's epilogue stores
+          each finished element into every rank's [M][N] buffer over peer-mapped memory
+          and a barrier kernel completes the step (strong scaling; the same step with an
+          NCCL all-gather is timed beside it, and is the fallback when peer mapping fails)
   --impl reference   the reference project's own AVX kernels (oracle/_ref, compiled
           unmodified) on this box's host cores, same shape, all host threads
-Other workloads (--workload): qgemv_sweep, qgemm_m2048, qgemm_m8192.
+The line also carries the roofline of the dominant kernel, the reference's CPU kernels timed on
+this box, the decode QGEMV sweep, the scheme matrix and pp322 / tg128 of a synthetic Qwen3-8B
+(--no-gemv / --no-model skip the last three).  Other workloads (--workload): qgemv_sweep,
+qgemm_m2048, qgemm_m8192.
 """
 from __future__ import annotations
 
