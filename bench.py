@@ -425,6 +425,10 @@ def run_ours(args, rank, world, local_rank):
 
     step = step_scatter if scatter is not None else step_gather
 
+    # clocks are sampled from the warm-up on: the timed region itself lasts only a few milliseconds, less than the
+    # sampling period of nvidia-smi, and the warm-up steps put the same load on the GPU
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for i in range(args.warmup):
         step(i)
     torch.cuda.synchronize()
@@ -447,8 +451,6 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     l0 = ctx.launches
     torch.cuda.synchronize()
     if graph is not None:
