@@ -98,6 +98,15 @@ int inkq_weight_info(const inkq_weight *w, int *rows, int *K, int *scheme, size_
  * the values the kernels see (fp16-rounded when scale_mode is F16). */
 int inkq_weight_export(inkq_ctx *ctx, const inkq_weight *w, uint8_t *nib, float *d, float *m, uint8_t *zp);
 
+/* ---- offline weight quantizers -----------------------------------------------
+ * fp32 weights [N][K] on the device -> the on-disk format inkq_weight_create takes
+ * (nibbles u8 [N][K/2] AWQ-interleaved, scales and minima f32 [N][K/32], zero points
+ * i8 [N][K/32], may be NULL), all on the device.  format 0: Q4_0, 1: Q4_1.
+ * Replaces quantize_row_q40_tinyml / quantize_row_q41_tinyml
+ * (notebooks/quantize_methods.py:13-66, :68-125), bit for bit. */
+int inkq_weight_quantize_dev(inkq_ctx *ctx, int format, int N, int K, const float *w_dev, uint8_t *nib_dev, float *d_dev, float *m_dev,
+                             int8_t *zp_dev);
+
 /* ---- activation quantizer -------------------------------------------------
  * Replaces quantize_row_q8_0_repack / quantize_row_q8_1_repack_fp16 / _fp32
  * (QwenOperator.h:276-278).  x_dev: fp32 [M][K] on the device. */

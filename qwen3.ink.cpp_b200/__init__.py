@@ -17,6 +17,7 @@ from . import build as _build
 from . import synth  # noqa: F401  (re-exported)
 from . import tp  # noqa: F401
 from . import qwen3_forward  # noqa: F401
+from . import disk_format  # noqa: F401
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libinkq.so")
@@ -35,7 +36,7 @@ SYMBOLS = [
     "inkq_gemv", "inkq_gemm_simt", "inkq_debug_block_dots", "inkq_debug_block_dots_tc", "inkq_linear",
     "inkq_linear_host", "inkq_linear_m1_static", "inkq_gemm_w41_f16act", "inkq_gemm_w41_f16act_simt", "inkq_f16w_create", "inkq_f16w_create_dev", "inkq_f16w_destroy",
     "inkq_f16w_matmul", "inkq_peer_export", "inkq_peerset_open", "inkq_peerset_from_pointers", "inkq_peerset_destroy",
-    "inkq_linear_scatter", "inkq_peer_barrier",
+    "inkq_linear_scatter", "inkq_peer_barrier", "inkq_weight_quantize_dev",
 ]
 
 
@@ -166,6 +167,18 @@ class Context:
         self.check(self.L.inkq_weight_create_dev(self.h, scheme, scale_mode, N, K, _dp(nib), _dp(d), _dp(m), _dp(zp),
                                                  n_begin, N if n_end is None else n_end, C.byref(h)))
         return Weight(self, h, scheme)
+
+    def quantize_weights(self, fmt: int, w):
+        """fp32 weights [N][K] (torch, on the device) -> (nib, d, m, zp) device tensors in the on-disk format.
+        fmt 0: Q4_0 (quantize_row_q40_tinyml), 1: Q4_1 (quantize_row_q41_tinyml)."""
+        import torch
+        N, K = w.shape
+        nib = torch.empty((N, K // 2), dtype=torch.uint8, device=w.device)
+        d = torch.empty((N, K // 32), dtype=torch.float32, device=w.device)
+        m = torch.empty_like(d)
+        zp = torch.empty((N, K // 32), dtype=torch.int8, device=w.device)
+        self.check(self.L.inkq_weight_quantize_dev(self.h, fmt, N, K, _dp(w.contiguous()), _dp(nib), _dp(d), _dp(m), _dp(zp)))
+        return nib, d, m, zp
 
     def act(self, max_rows: int, K: int):
         h = C.c_void_p()

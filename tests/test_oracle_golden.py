@@ -124,6 +124,19 @@ def test_w41_dequantised_weight_is_one_rounding_of_the_exact_value(oracle, pkg):
     assert np.array_equal(got.T, want)
 
 
+@pytest.mark.parametrize("which,name", [(0, "q40"), (1, "q41")])
+def test_weight_quantizers_match_the_python_reference(oracle, golden, which, name):
+    """Fixture made by importing notebooks/quantize_methods.py of the reference (tests/golden/make_golden_weightquant.py):
+    packed nibbles, scales and minima of the restatement equal the reference's bit for bit, including zero, constant,
+    tie and extreme-magnitude blocks."""
+    g = golden("ref_weightquant.npz")
+    nib, d, m = oracle.quantize_weight(which, g["w"])
+    assert np.array_equal(nib, g[name + "_nib"])
+    assert np.array_equal(d.view(np.uint32), g[name + "_d"].view(np.uint32))
+    assert np.array_equal(m.view(np.uint32), g[name + "_m"].view(np.uint32))
+    assert (g[name + "_zp"] == (8 if which == 0 else 0)).all()
+
+
 def test_weight_quantizers_round_trip(oracle, pkg):
     """Q4_1 / Q4_0 format definitions (notebooks/quantize_methods.py:13-125)."""
     rng = np.random.default_rng(3)
