@@ -668,6 +668,7 @@ int inkq_gemm_w41_f16act(inkq_ctx *ctx, const uint16_t *a16_dev, int M, const in
     INKQ_REQUIRE(ctx, w != nullptr && a16_dev != nullptr && C_dev != nullptr, "null handle, input or output");
     INKQ_REQUIRE(ctx, w->scheme == INKQ_W41 || w->scheme == INKQ_A81W41, "weight-only matmul needs Q4_1 weights");
     INKQ_REQUIRE(ctx, M >= 1 && ldc >= w->rows, "bad M or ldc");
+    if (M == 1 && (reinterpret_cast<uintptr_t>(a16_dev) & 3) == 0) return launch_gemv_w41(ctx, a16_dev, w, C_dev);   // decode: stream the weights
     return launch_gemm_w41_tc(ctx, a16_dev, M, w, C_dev, ldc);
 }
 

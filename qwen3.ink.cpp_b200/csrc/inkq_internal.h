@@ -162,6 +162,7 @@ int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int l
                    int tn_begin = 0, int tn_count = -1);
 int launch_gemm_w41_f16(inkq_ctx *ctx, const uint16_t *a16, int M, const Weight *w, float *C, int ldc);   // CUDA cores
 int launch_gemm_w41_tc(inkq_ctx *ctx, const uint16_t *a16, int M, const Weight *w, float *C, int ldc);    // tcgen05 kind::f16
+int launch_gemv_w41(inkq_ctx *ctx, const uint16_t *a16, const Weight *w, float *C);                        // M == 1, bandwidth-bound
 // inkq_linear with further destinations for every output element (defined in inkq_api.cu)
 int linear_impl(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, int M, float *C_dev, int ldc, const ExtraDst *extra);
 int launch_f16w_matmul(inkq_ctx *ctx, const F16W *w, const float *x, int M, float *C, int ldc);

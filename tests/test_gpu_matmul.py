@@ -207,7 +207,8 @@ def test_mismatched_quantizer_mode_is_rejected(pkg, gpu, oracle):
 
 
 # ------------------------------------------------------------------ weight-only W41 and fp16 lm_head
-@pytest.mark.parametrize("M,N,K", [(9, 72, 256), (1, 256, 128), (16, 128, 64), (322, 384, 512), (200, 136, 1024), (400, 264, 192),
+@pytest.mark.parametrize("M,N,K", [(9, 72, 256), (1, 256, 128), (1, 1064, 512), (1, 4096, 4096), (1, 512, 12288),   # M == 1: the streaming kernel
+                                   (16, 128, 64), (322, 384, 512), (200, 136, 1024), (400, 264, 192),
                                    # enough work items for the two-weight-tiles-per-CTA variant: an odd tile count (the last
                                    # group holds one tile), and two activation tiles of 160 rows
                                    (16, 297 * 128, 64), (300, 74 * 256, 128)])
