@@ -50,7 +50,7 @@ __device__ __forceinline__ void cta_rmsnorm_quant(const float *x, const float *g
     const unsigned gmask = 0x3u << (threadIdx.x & 30);
     // rows of up to 16 * blockDim.x elements are read once and kept in registers between the two passes
     const bool single_trip = nb <= static_cast<int>(blockDim.x >> 1);
-    float4 keep[4];
+    float4 keep[4], gkeep[4];   // the norm weights are fetched together with the row: their latency hides under the reduction
     float ss = 0.0f;
     if (single_trip) {
         const int blk = threadIdx.x >> 1;
@@ -58,8 +58,10 @@ __device__ __forceinline__ void cta_rmsnorm_quant(const float *x, const float *g
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 keep[j] = __ldcg(reinterpret_cast<const float4 *>(x) + blk * 8 + 2 * j + half);
-                ss += keep[j].x * keep[j].x + keep[j].y * keep[j].y + keep[j].z * keep[j].z + keep[j].w * keep[j].w;
+                gkeep[j] = reinterpret_cast<const float4 *>(g)[blk * 8 + 2 * j + half];
             }
+#pragma unroll
+            for (int j = 0; j < 4; j++) ss += keep[j].x * keep[j].x + keep[j].y * keep[j].y + keep[j].z * keep[j].z + keep[j].w * keep[j].w;
         }
     } else {
         for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
@@ -80,7 +82,7 @@ __device__ __forceinline__ void cta_rmsnorm_quant(const float *x, const float *g
         for (int j = 0; j < 4; j++) {
             const int i4 = blk * 8 + 2 * j + half;
             const float4 t = single_trip ? keep[j] : __ldcg(reinterpret_cast<const float4 *>(x) + i4);
-            const float4 gg = reinterpret_cast<const float4 *>(g)[i4];
+            const float4 gg = single_trip ? gkeep[j] : reinterpret_cast<const float4 *>(g)[i4];
             v[j] = make_float4(t.x * inv * gg.x, t.y * inv * gg.y, t.z * inv * gg.z, t.w * inv * gg.w);
             if (xn != nullptr) reinterpret_cast<float4 *>(xn)[i4] = v[j];
         }
