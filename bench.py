@@ -513,6 +513,17 @@ def run_ours(args, rank, world, local_rank):
                             "peak_note": f"2 x the {pk['source']} dense bf16 figure ({pk['bf16_tflops']} TFLOP/s); int8 itself is not in MEASURED_PEAKS.json",
                             "cuda_core_note": "every K=32 MMA is followed by an fp32 scale+accumulate of its whole tile on the CUDA cores "
                                               "(M*N*K/32 block dots per launch); that, not the tensor pipe, bounds this kernel"}
+        # the second roof of this kernel: the per-block fp32 epilogue on the CUDA cores.  Per block dot and lane the exact
+        # arithmetic needs one int->float conversion, half a packed multiply (d_a*d_w), one packed fma pair (main and min
+        # terms) and half a shared load: 3 issue slots per warp-level block dot.
+        tiles_m = -(-M // 128)
+        bm = -(-(-(-M // tiles_m)) // 16) * 16
+        dots = float(tiles_m * bm) * n_loc * (K // 32)
+        sm_clock = (clocks.get("sm_mhz") or 1965.0) * 1e6
+        n_sms = torch.cuda.get_device_properties(local_rank).multi_processor_count
+        t_min = dots * 3.0 / 32.0 / (n_sms * 4) / sm_clock
+        line["roofline"]["cuda_core_roof"] = {"block_dots_per_launch": dots, "issue_slots_per_warp_block_dot": 3.0,
+                                              "min_us": t_min * 1e6, "frac": t_min / (ms_g * 1e-3)}
         line["quantizer"] = {"us_per_launch": ms_q * 1e3, "GBs": M * K * 5.375 / (ms_q * 1e-3) / 1e9, "frac_of_hbm": M * K * 5.375 / (ms_q * 1e-3) / 1e9 / pk["hbm_gbs"]}
         act.close()
 
