@@ -605,6 +605,11 @@ int inkq::linear_impl(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, i
     INKQ_REQUIRE(ctx, M >= 1, "M must be at least 1");
     INKQ_REQUIRE(ctx, ldc >= w->rows, "ldc is smaller than the number of weight rows");
     INKQ_REQUIRE(ctx, w->scheme != INKQ_W41, "a weight-only layer takes fp16 activations: use inkq_gemm_w41_f16act");
+    if (M == 1 && extra == nullptr && (reinterpret_cast<uintptr_t>(x_dev) & 15) == 0) {
+        // one token: the QGEMV quantizes the row in its own prologue (same arithmetic, same result bits as the
+        // stand-alone quantizer followed by the QGEMV, one launch less)
+        return launch_gemv_fused(ctx, w, x_dev, 0, nullptr, 0.0f, C_dev, 0);
+    }
     if ((rc = ensure_scratch_act(ctx, M, w->K))) return rc;
     inkq_act *act = static_cast<inkq_act *>(ctx->scratch_act);
     int qmode;
