@@ -160,7 +160,7 @@ int inkq_linear_host(inkq_ctx *ctx, const inkq_weight *w, const float *x_host, i
  * No counterpart in the reference.  For hosts that may not call cudaMalloc while
  * serving (a latency-bound decode loop, a process whose device heap belongs to
  * another allocator): the M == 1 forward of inkq_linear with its scratch - one
- * quantized activation row - in a fixed 20 KiB device array inside the library
+ * quantized activation row - in a fixed 40 KiB device array inside the library
  * instead of the context's growable buffer.  K <= 16384, else INKQ_ERR_UNSUPPORTED.
  * The first call on a device resolves the array's address; make it before any
  * stream capture.  All calls on a device share the array: calls that overlap on

@@ -3,7 +3,7 @@
     python qwen3.ink.cpp_b200/build.py            # or  __graft_entry__.build()
 
 nvcc cross-compiles without a GPU.  The ptxas resource report (registers, spills,
-shared memory per kernel) is written next to the library as libinkq.ptxas.txt.
+shared memory per kernel) is written to build/libinkq.ptxas.txt (not tracked).
 """
 from __future__ import annotations
 
@@ -47,7 +47,8 @@ def build_cuda(force: bool = False, verbose: bool = False) -> str:
     env.pop("CC", None)
     env.pop("CXX", None)
     res = subprocess.run(cmd, capture_output=True, text=True, env=env)
-    with open(os.path.join(HERE, "libinkq.ptxas.txt"), "w") as f:
+    os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
+    with open(os.path.join(HERE, "build", "libinkq.ptxas.txt"), "w") as f:
         f.write(res.stderr)
     if res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)

@@ -9,7 +9,8 @@
 // a larger shape shows up; this entry point never does.  Its scratch - one
 // quantized activation row: the int8 values plus the per-block scale, scaled sum
 // and integer sum planes - lives in the fixed array below, which every device that
-// loads this library carries until the process exits (20 KiB).
+// loads this library carries until the process exits (40 KiB: 16 KiB of int8 values and
+// three padded planes of 8 KiB).
 //
 // Limits and rules
 //   * K <= INKQ_STATIC_MAX_K (16384); larger K is rejected with INKQ_ERR_UNSUPPORTED.
@@ -22,7 +23,8 @@
 //     Two calls whose kernels overlap on the GPU (different streams, no ordering)
 //     race on it: order them.
 //   * It calls no cudaMalloc, cudaFree or any allocating library routine.
-// Same kernels, same arithmetic and same result as inkq_linear with M == 1.
+// Same arithmetic and the same result bits as inkq_linear with M == 1 (which fuses the
+// quantizer into the QGEMV's prologue; here they are two launches).
 #include <cuda_runtime.h>
 
 #include <mutex>
@@ -34,6 +36,7 @@ namespace inkq {
 constexpr int STATIC_MAX_K = 16384;
 constexpr int STATIC_PLANE = 4 * (STATIC_MAX_K / QK);  // [K/32][M_ld = 4] entries of one plane
 constexpr size_t STATIC_BYTES = STATIC_MAX_K + 3 * sizeof(float) * STATIC_PLANE;
+static_assert(STATIC_BYTES == 40 * 1024, "the documented size of the static scratch is 40 KiB");
 
 // In host code this name is only a handle for cudaGetSymbolAddress, never a pointer to pass on.
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_BYTES];

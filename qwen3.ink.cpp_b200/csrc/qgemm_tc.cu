@@ -23,19 +23,22 @@
 //   warp 1      MMA issuer: one elected thread issues the K=32 MMAs and commits
 //   warp 2      tensor-memory allocation / release
 //   warp 3      scale TMA producer: per stage the activation block scales d_a and sums s_a of
-//               the tile's rows, [4 blocks][BLOCK_M] fp32 each (tiled 2-D copies, zero-filled
-//               past the end), into their own ring because the epilogue consumes them later
-//               than the MMA consumes the operands
+//               the tile's rows ([4 blocks][BLOCK_M] fp32 each, tiled 2-D copies, zero-filled
+//               past the end) and the weight rows' {d_lo, d_hi, m_lo, m_hi} records (one bulk
+//               copy), into their own ring because the epilogue consumes them later than the
+//               MMA consumes the operands
 //   warps 4-7   unpack: packed nibbles (smem) -> signed int8 (q - z) in the canonical
 //               no-swizzle K-major core-matrix layout the MMA reads
 //   warps 8-23  epilogue (the binding resource: it owns all four schedulers): tcgen05.ld of a
 //               block's int32 tile, s32->f32, scale, accumulate in registers in exactly the
 //               reference's order; at the end of a tile the fp32 accumulators are stored to C.
 //               Warp w reads TMEM lanes 32*(w%4).. and a quarter of the columns.
-// Rings: 5 raw stages, 3 unpacked stages, 4 scale stages, 2 TMEM accumulator slots of 256 columns (one pair
-// of blocks each: two MMAs, one commit, one hand-shake per pair).
-// Every mbarrier wait is bounded; on expiry the kernel sets a device flag and all
-// roles drain and leave (the context stays usable, the host reports INKQ_ERR_TIMEOUT).
+// Rings: 5 raw stages, 3 unpacked stages (both freed by one "stage done" commit), 4 scale stages, and as many tensor-memory accumulator
+// slots as fit into the 512 columns (a slot = one pair of blocks = 2*BLOCK_M columns: two MMAs,
+// one commit, one hand-shake), so that narrow tiles keep many pairs in flight.
+// Every mbarrier wait is bounded; when one runs out the kernel sets a device flag, every later
+// wait of every role returns at once, all roles run to the end of their loops (on garbage,
+// inside their buffers) and leave; the host reports INKQ_ERR_TIMEOUT and the context stays usable.
 //
 // Operation order per output (bit-identical to the reference): for each pair of
 // blocks ascending: acc = fma((float)I_lo, d_a_lo*d_w_lo, acc); fma((float)I_hi, ...);
@@ -43,6 +46,8 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <stdlib.h>
+
+#include <mutex>
 
 #include "inkq_internal.h"
 #include "ptx.cuh"
@@ -52,20 +57,34 @@ namespace inkq {
 constexpr int TC_THREADS = 768;
 constexpr int EPI_WARPS = 16;
 // Register re-balancing after the roles split (setmaxnreg).  The kernel is launched with LAUNCH_REGS per
-// thread (checked on the host before the first launch); the two non-epilogue warpgroups release
-// 128*(80-40) + 128*(80-48) = 9216 registers, the four epilogue warpgroups take 512*(96-80) = 8192 of them.
-// A request larger than what was released would block forever, hence the static check.
-constexpr int LAUNCH_REGS = 80, CTRL_REGS = 40, UNPACK_REGS = 48, EPI_REGS = 96;
+// thread (checked on the host before the first launch); the two non-epilogue warpgroups release registers,
+// the four epilogue warpgroups take them.  A request larger than what was released would block forever,
+// hence the static check.
+#ifndef INKQ_TC_CTRL_REGS
+#define INKQ_TC_CTRL_REGS 40
+#endif
+#ifndef INKQ_TC_UNPACK_REGS
+#define INKQ_TC_UNPACK_REGS 48
+#endif
+#ifndef INKQ_TC_EPI_REGS
+#define INKQ_TC_EPI_REGS 96
+#endif
+// columns per tcgen05.ld chunk of the epilogue's software pipeline (8 or 16)
+#ifndef INKQ_TC_CHUNK
+#define INKQ_TC_CHUNK 16
+#endif
+constexpr int LAUNCH_REGS = 80, CTRL_REGS = INKQ_TC_CTRL_REGS, UNPACK_REGS = INKQ_TC_UNPACK_REGS, EPI_REGS = INKQ_TC_EPI_REGS;
 static_assert(128 * (LAUNCH_REGS - CTRL_REGS) + 128 * (LAUNCH_REGS - UNPACK_REGS) >= 512 * (EPI_REGS - LAUNCH_REGS), "setmaxnreg budget");
 constexpr int STAGE_PAIRS = 2;                         // pairs per stage
 constexpr int STAGE_BLOCKS = 2 * STAGE_PAIRS;          // 4 MMAs per stage
 constexpr int RAW_STAGES = 5;
 constexpr int U8_STAGES = 3;
-constexpr int ACC_STAGES = 2;
+constexpr int MAX_ACC_SLOTS = 8;
+constexpr int DONE_RING = 8;   // "the MMAs of K-stage g have completed" barriers, indexed by g % DONE_RING (deeper than both smem rings)
 constexpr int SC_STAGES = 4;
 constexpr int SC_PLANE_BYTES = STAGE_BLOCKS * 128 * 4;    // one plane of a scale stage: [4 blocks][128 rows] fp32
-constexpr int SC_STAGE_BYTES = 2 * SC_PLANE_BYTES;       // d_a and s_a
-constexpr int ACC_COLS = 256;                          // TMEM columns per accumulator slot: one pair, low block at +0, high block at +128
+constexpr int SC_W_BYTES = STAGE_PAIRS * TILE_N * 16;    // the weight rows' float4 records of the stage's pairs
+constexpr int SC_STAGE_BYTES = 2 * SC_PLANE_BYTES + SC_W_BYTES;   // d_a, s_a, weight scales
 constexpr int RAW_A_BYTES = 128 * 128;                 // activations: up to 128 rows x 128 B
 constexpr int RAW_W_BYTES = STAGE_PAIRS * TILE_N * 32; // packed weights: 8192
 constexpr int RAW_Z_BYTES = STAGE_PAIRS * TILE_N * 2;  // zero points: 512
@@ -74,35 +93,29 @@ constexpr int U8_BLOCK_BYTES = TILE_N * 32;            // one unpacked block: 40
 constexpr int U8_STAGE_BYTES = STAGE_BLOCKS * U8_BLOCK_BYTES;
 constexpr int TC_SMEM_BYTES =
     1024 /*align slack*/ + RAW_STAGES * RAW_STAGE_BYTES + U8_STAGES * U8_STAGE_BYTES + SC_STAGES * SC_STAGE_BYTES + 512 /*barriers*/;
+static_assert(TC_SMEM_BYTES <= 227 * 1024, "shared memory budget");
+
+__host__ __device__ constexpr int acc_slots_for(int block_m)
+{
+    return (512 / (2 * block_m)) < MAX_ACC_SLOTS ? (512 / (2 * block_m)) : MAX_ACC_SLOTS;
+}
 
 struct TcParams {
     const uint8_t *nibT;
     const float4 *sc32;
-    const uint2 *sc16;
     const uchar2 *zpT;
     float *C;
     ExtraDst extra;  // further destinations of every C element (peers of a column-sharded layer)
     int32_t *dots;   // non-null: dump raw int32 block dots [M][rows][K/32] instead of computing C
     int *flag;
-    int M, M_ld, rows, K, pairs, tn0, tiles_n, tiles_m, block_m, ldc;   // this launch covers weight tiles tn0 .. tn0 + tiles_n - 1
-#ifdef INKQ_ROLE_TIMERS
-    long long *timers;   // [gridDim.x][16] cycle counters, development only
-#endif
+    int M, rows, pairs, tn0, tiles_n, tiles_m, ldc;   // this launch covers weight tiles tn0 .. tn0 + tiles_n - 1
 };
-
-#ifdef INKQ_ROLE_TIMERS
-#define T_BEGIN() const long long t_begin__ = clock64()
-#define T_ADD(slot) tacc[slot] += clock64() - t_begin__
-#else
-#define T_BEGIN()
-#define T_ADD(slot)
-#endif
 
 struct Ring {
     uint32_t idx = 0, phase = 0;
     int n;
     __device__ explicit Ring(int n_) : n(n_) {}
-    __device__ void advance()
+    __device__ __forceinline__ void advance()
     {
         if (++idx == static_cast<uint32_t>(n)) {
             idx = 0;
@@ -111,17 +124,37 @@ struct Ring {
     }
 };
 
-// Exact s32 -> f32 (a block dot is at most 32 * 128 * 15 = 61440 in magnitude).  The
-// alternative under INKQ_CVT_MAGIC avoids the conversion instruction: adding 0x4B400000 as
-// an integer yields the bit pattern of the float 12582912 + v (ulp = 1 in [2^23, 2^24)), and
-// the float subtraction of 12582912 is exact for |v| < 2^22.
-__device__ __forceinline__ float s32_to_f32_exact(uint32_t v)
+// Bounded wait of this kernel.  The common case (phase already complete) is one probe and one
+// untaken branch.  Otherwise the thread probes until the phase completes, the CTA's abort word is
+// set by another role, or the cycle limit runs out; in the last case it sets the abort word and the
+// device flag.  It always returns: after an abort the roles finish their loops without waiting.
+__device__ __forceinline__ void tc_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *dev_flag, uint32_t sleep_ns)
 {
-#ifdef INKQ_CVT_MAGIC
-    return __int_as_float(static_cast<int>(v + 0x4B400000u)) - 12582912.0f;
-#else
-    return static_cast<float>(static_cast<int32_t>(v));
-#endif
+    if (mbar_try_wait(bar, parity)) return;
+    const long long t0 = clock64();
+#pragma unroll 1
+    for (uint32_t spin = 1;; spin++) {
+        if (mbar_try_wait(bar, parity)) return;
+        if (sleep_ns != 0u) __nanosleep(sleep_ns);
+        if ((spin & 31u) == 0u) {
+            if (*abort_flag != 0) return;
+            if (clock64() - t0 > INKQ_SPIN_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                atomicExch(dev_flag, 1);
+                return;
+            }
+        }
+    }
+}
+
+// One arrival per warp without a divergent branch: the elected lane arrives, predicated.
+__device__ __forceinline__ void mbar_arrive_elect(uint64_t *bar)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 st;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "@p mbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar))
+        : "memory");
 }
 
 // Two fp32 values in one 64-bit register and the IEEE (round-to-nearest) packed
@@ -149,23 +182,10 @@ __device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigne
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
     return r;
 }
-
-__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b)
-{
-    unsigned long long r;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-// Two block dots -> packed fp32 pair, exactly.
+// Two block dots -> packed fp32 pair, exactly (a block dot is at most 32 * 128 * 15 = 61440 in magnitude).
 __device__ __forceinline__ unsigned long long cvt2_exact(uint32_t v0, uint32_t v1)
 {
-#if defined(INKQ_CVT_MAGIC2)
-    // integer add on the ALU pipe, one packed float add for both halves
-    return add2(pack2(__int_as_float(static_cast<int>(v0 + 0x4B400000u)), __int_as_float(static_cast<int>(v1 + 0x4B400000u))),
-                pack2(-12582912.0f, -12582912.0f));
-#else
-    return pack2(s32_to_f32_exact(v0), s32_to_f32_exact(v1));
-#endif
+    return pack2(static_cast<float>(static_cast<int32_t>(v0)), static_cast<float>(static_cast<int32_t>(v1)));
 }
 
 // Loads N consecutive TMEM columns of this thread's lane; N a multiple of 4 up to 16.
@@ -192,6 +212,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                const TcParams prm)
 {
     constexpr int BLOCK_M = 4 * CW;
+    constexpr int ACC_SLOTS = acc_slots_for(BLOCK_M);
+    constexpr int SLOT_COLS = 2 * BLOCK_M;   // low block at +0, high block at +BLOCK_M
     // 1024-byte alignment (128-byte swizzle atoms) by an offset from the shared array itself, so
     // that every access below stays a shared-space (not generic) load or store
     extern __shared__ __align__(1024) unsigned char smem_dyn[];
@@ -200,11 +222,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     unsigned char *u8_base = raw_base + RAW_STAGES * RAW_STAGE_BYTES;
     unsigned char *sc_base = u8_base + U8_STAGES * U8_STAGE_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(sc_base + SC_STAGES * SC_STAGE_BYTES);
-    uint64_t *raw_full = bars, *raw_empty = raw_full + RAW_STAGES;
-    uint64_t *u8_full = raw_empty + RAW_STAGES, *u8_empty = u8_full + U8_STAGES;
-    uint64_t *acc_full = u8_empty + U8_STAGES, *acc_empty = acc_full + ACC_STAGES;
-    uint64_t *sc_full = acc_empty + ACC_STAGES, *sc_empty = sc_full + SC_STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sc_empty + SC_STAGES);
+    uint64_t *raw_full = bars, *stage_done = raw_full + RAW_STAGES;
+    uint64_t *u8_full = stage_done + DONE_RING;
+    uint64_t *acc_full = u8_full + U8_STAGES, *acc_empty = acc_full + MAX_ACC_SLOTS;
+    uint64_t *sc_full = acc_empty + MAX_ACC_SLOTS, *sc_empty = sc_full + SC_STAGES;
+    uint64_t *drain_bar = sc_empty + SC_STAGES;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(drain_bar + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -212,15 +235,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     const int k_stages = (prm.pairs + STAGE_PAIRS - 1) / STAGE_PAIRS;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < RAW_STAGES; i++) {
-            mbar_init(&raw_full[i], 1);
-            mbar_init(&raw_empty[i], 4 + 1);  // 4 unpack warps + the MMA commit
-        }
-        for (int i = 0; i < U8_STAGES; i++) {
-            mbar_init(&u8_full[i], 128);
-            mbar_init(&u8_empty[i], 1);
-        }
-        for (int i = 0; i < ACC_STAGES; i++) {
+        for (int i = 0; i < RAW_STAGES; i++) mbar_init(&raw_full[i], 1);
+        for (int i = 0; i < DONE_RING; i++) mbar_init(&stage_done[i], 1);   // one tcgen05.commit per K-stage
+        for (int i = 0; i < U8_STAGES; i++) mbar_init(&u8_full[i], 4);      // one arrival per unpack warp
+        for (int i = 0; i < MAX_ACC_SLOTS; i++) {
             mbar_init(&acc_full[i], 1);
             mbar_init(&acc_empty[i], EPI_WARPS);
         }
@@ -228,6 +246,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             mbar_init(&sc_full[i], 1);
             mbar_init(&sc_empty[i], EPI_WARPS);
         }
+        mbar_init(drain_bar, 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -240,15 +259,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    // A failed (timed-out or aborted) wait: record it for the host and for the other roles.
-#define INKQ_GIVE_UP()            \
-    {                             \
-        *abort_flag = 1;          \
-        atomicExch(prm.flag, 1);  \
-        dead = true;              \
-        break;                    \
-    }
-
     if (warp < 4) setmaxnreg_dec<CTRL_REGS>();
     if (warp >= 4 && warp < 8) setmaxnreg_dec<UNPACK_REGS>();
     if (warp == 0) {
@@ -256,11 +266,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         if (lane == 0) {
             tma_prefetch_desc(&map_a);
             Ring raw(RAW_STAGES);
-            bool dead = false;
-            for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
+            uint32_t g = 0;   // K-stages issued so far (over all tiles of this CTA)
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
                 const int tn = prm.tn0 + tile / prm.tiles_m, tm = tile % prm.tiles_m;
-                for (int ks = 0; ks < k_stages; ks++) {
-                    if (!mbar_wait_abortable(abort_flag, &raw_empty[raw.idx], raw.phase ^ 1, 1000u)) INKQ_GIVE_UP();
+                for (int ks = 0; ks < k_stages; ks++, g++) {
+                    // the slot last held stage g - RAW_STAGES: free once that stage's MMAs have completed (which also
+                    // means the unpack warps are done with its packed weights)
+                    if (g >= RAW_STAGES) {
+                        const uint32_t h = g - RAW_STAGES;
+                        tc_wait(&stage_done[h % DONE_RING], (h / DONE_RING) & 1u, abort_flag, prm.flag, 200u);
+                    }
                     const int np = min(STAGE_PAIRS, prm.pairs - ks * STAGE_PAIRS);
                     unsigned char *st = raw_base + raw.idx * RAW_STAGE_BYTES;
                     const uint32_t tx = BLOCK_M * 128 + np * (TILE_N * 32) + np * (TILE_N * 2);
@@ -273,6 +288,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     raw.advance();
                 }
             }
+            if (*abort_flag != 0) {
+                // copies of stages nobody consumed may still be in flight: wait (bounded) for each stage's last fill
+                for (int s = 0; s < RAW_STAGES; s++)
+                    tc_wait(&raw_full[s], static_cast<uint32_t>(s) < raw.idx ? raw.phase : raw.phase ^ 1, abort_flag, prm.flag, 100u);
+            }
         }
         __syncwarp();
     } else if (warp == 3) {
@@ -281,18 +301,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             tma_prefetch_desc(&map_d);
             if (HAS_MIN) tma_prefetch_desc(&map_s);
             Ring sc(SC_STAGES);
-            bool dead = false;
-            for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
-                const int tm = tile % prm.tiles_m;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+                const int tn = prm.tn0 + tile / prm.tiles_m, tm = tile % prm.tiles_m;
                 for (int ks = 0; ks < k_stages; ks++) {
-                    if (!mbar_wait_abortable(abort_flag, &sc_empty[sc.idx], sc.phase ^ 1, 1000u)) INKQ_GIVE_UP();
+                    tc_wait(&sc_empty[sc.idx], sc.phase ^ 1, abort_flag, prm.flag, 200u);
+                    const int np = min(STAGE_PAIRS, prm.pairs - ks * STAGE_PAIRS);
                     unsigned char *st = sc_base + sc.idx * SC_STAGE_BYTES;
                     const uint32_t plane = STAGE_BLOCKS * BLOCK_M * 4;  // the box is always full size; out-of-range parts arrive as zeros
-                    mbar_arrive_expect_tx(&sc_full[sc.idx], HAS_MIN ? 2 * plane : plane);
+                    mbar_arrive_expect_tx(&sc_full[sc.idx], (HAS_MIN ? 2 * plane : plane) + np * (TILE_N * 16));
                     tma_tensor2d_g2s(st, &map_d, tm * BLOCK_M, ks * STAGE_BLOCKS, &sc_full[sc.idx]);
                     if (HAS_MIN) tma_tensor2d_g2s(st + SC_PLANE_BYTES, &map_s, tm * BLOCK_M, ks * STAGE_BLOCKS, &sc_full[sc.idx]);
+                    const size_t slab = static_cast<size_t>(tn) * prm.pairs + static_cast<size_t>(ks) * STAGE_PAIRS;
+                    tma_bulk_g2s(st + 2 * SC_PLANE_BYTES, prm.sc32 + slab * TILE_N, np * (TILE_N * 16), &sc_full[sc.idx]);
                     sc.advance();
                 }
+            }
+            if (*abort_flag != 0) {
+                for (int s = 0; s < SC_STAGES; s++)
+                    tc_wait(&sc_full[s], static_cast<uint32_t>(s) < sc.idx ? sc.phase : sc.phase ^ 1, abort_flag, prm.flag, 100u);
             }
         }
         __syncwarp();
@@ -300,26 +326,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_i8(TILE_N, BLOCK_M);
-            Ring raw(RAW_STAGES), u8(U8_STAGES), acc(ACC_STAGES);
-            bool dead = false;
-#ifdef INKQ_ROLE_TIMERS
-            long long tacc[3] = {0, 0, 0};
-            long long mma_lat = 0, mma_cnt = 0;
-#endif
-            for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
-                for (int ks = 0; ks < k_stages && !dead; ks++) {
-                    {
-                        T_BEGIN();
-                        if (!mbar_wait_abortable(abort_flag, &raw_full[raw.idx], raw.phase, 0u)) INKQ_GIVE_UP();
-                        T_ADD(0);
-                    }
-                    {
-                        T_BEGIN();
-                        if (!mbar_wait_abortable(abort_flag, &u8_full[u8.idx], u8.phase, 0u)) INKQ_GIVE_UP();
-                        T_ADD(1);
-                    }
+            Ring raw(RAW_STAGES), u8(U8_STAGES), acc(ACC_SLOTS);
+            uint32_t g = 0;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+                for (int ks = 0; ks < k_stages; ks++, g++) {
+                    tc_wait(&raw_full[raw.idx], raw.phase, abort_flag, prm.flag, 0u);
+                    tc_wait(&u8_full[u8.idx], u8.phase, abort_flag, prm.flag, 0u);
                     tc_fence_after_sync();
-                    const int nblk = 2 * min(STAGE_PAIRS, prm.pairs - ks * STAGE_PAIRS);
+                    const int np = min(STAGE_PAIRS, prm.pairs - ks * STAGE_PAIRS);
                     // A: unpacked weights, no swizzle: element (row r, k) of a block at (k / 16) * 2048 + r * 16 + (k % 16):
                     //    the two K halves 2048 B apart (leading offset), 8-row core matrices 128 B apart (stride offset);
                     //    consecutive blocks of the stage are 4096 B apart.
@@ -329,40 +343,27 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     const uint64_t b_desc0 = umma_smem_desc(smem_u32(raw_base + raw.idx * RAW_STAGE_BYTES), 16, 1024, 2);
 #pragma unroll
                     for (int pp = 0; pp < STAGE_PAIRS; pp++) {
-                        if (2 * pp >= nblk) break;
-                        {
-                            T_BEGIN();
-                            if (!mbar_wait_abortable(abort_flag, &acc_empty[acc.idx], acc.phase ^ 1, 0u)) INKQ_GIVE_UP();
-                            T_ADD(2);
-                        }
-                        tc_fence_after_sync();
-#ifdef INKQ_ROLE_TIMERS
-                        const long long t_issue = clock64();
-#endif
+                        if (pp < np) {
+                            tc_wait(&acc_empty[acc.idx], acc.phase ^ 1, abort_flag, prm.flag, 0u);
+                            tc_fence_after_sync();
 #pragma unroll
-                        for (int hi = 0; hi < 2; hi++) {
-                            const int j = 2 * pp + hi;
-                            umma_i8(tmem_base + acc.idx * ACC_COLS + hi * 128, a_desc0 + static_cast<uint64_t>(j * (U8_BLOCK_BYTES >> 4)),
-                                    b_desc0 + static_cast<uint64_t>(j * (32 >> 4)), idesc, 0u);
+                            for (int hi = 0; hi < 2; hi++) {
+                                const int j = 2 * pp + hi;
+                                umma_i8(tmem_base + acc.idx * SLOT_COLS + hi * BLOCK_M, a_desc0 + static_cast<uint64_t>(j * (U8_BLOCK_BYTES >> 4)),
+                                        b_desc0 + static_cast<uint64_t>(j * (32 >> 4)), idesc, 0u);
+                            }
+                            umma_commit(&acc_full[acc.idx]);
+                            acc.advance();
                         }
-                        umma_commit(&acc_full[acc.idx]);
-#ifdef INKQ_ROLE_TIMERS
-                        mma_lat += clock64() - t_issue;   // development only: cycles the issue + commit hold the thread
-                        mma_cnt++;
-#endif
-                        acc.advance();
                     }
-                    if (dead) break;
-                    umma_commit(&raw_empty[raw.idx]);
-                    umma_commit(&u8_empty[u8.idx]);
+                    umma_commit(&stage_done[g % DONE_RING]);   // frees the stage's raw and unpacked buffers (one commit: each costs tensor-pipe time)
                     raw.advance();
                     u8.advance();
                 }
             }
-#ifdef INKQ_ROLE_TIMERS
-            for (int i = 0; i < 3; i++) prm.timers[blockIdx.x * 16 + i] = tacc[i];
-            prm.timers[blockIdx.x * 16 + 3] = mma_cnt ? mma_lat / mma_cnt : 0;
-#endif
+            // every MMA issued above has completed before tensor memory is released
+            umma_commit(drain_bar);
+            tc_wait(drain_bar, 0u, abort_flag, prm.flag, 100u);
         }
         __syncwarp();
     } else if (warp >= 4 && warp < 8) {
@@ -374,32 +375,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         const int rr = (lane & 7) + 8 * (lane >> 4);
         const int chunk = (lane >> 3) & 1;
         Ring raw(RAW_STAGES), u8(U8_STAGES);
-        bool dead = false;
-#ifdef INKQ_ROLE_TIMERS
-        long long tacc[3] = {0, 0, 0};
-        const long long t_role0 = clock64();
-#endif
-        for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
-            for (int ks = 0; ks < k_stages; ks++) {
-                {
-                    T_BEGIN();
-                    if (!mbar_wait_abortable(abort_flag, &raw_full[raw.idx], raw.phase, 200u)) INKQ_GIVE_UP();
-                    T_ADD(0);
-                }
-                {
-                    T_BEGIN();
-                    if (!mbar_wait_abortable(abort_flag, &u8_empty[u8.idx], u8.phase ^ 1, 500u)) INKQ_GIVE_UP();
-                    T_ADD(1);
+        uint32_t g = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            for (int ks = 0; ks < k_stages; ks++, g++) {
+                tc_wait(&raw_full[raw.idx], raw.phase, abort_flag, prm.flag, 100u);
+                if (g >= U8_STAGES) {   // the unpacked slot last held stage g - U8_STAGES
+                    const uint32_t h = g - U8_STAGES;
+                    tc_wait(&stage_done[h % DONE_RING], (h / DONE_RING) & 1u, abort_flag, prm.flag, 100u);
                 }
                 const int np = min(STAGE_PAIRS, prm.pairs - ks * STAGE_PAIRS);
                 const unsigned char *wsrc = raw_base + raw.idx * RAW_STAGE_BYTES + RAW_A_BYTES;
                 const unsigned char *zsrc = wsrc + RAW_W_BYTES;
                 unsigned char *dst = u8_base + u8.idx * U8_STAGE_BYTES;
-#ifdef INKQ_EXP_NOUNPACK
-                for (int pp = 0; pp < 0; pp++) {
-#else
                 for (int pp = 0; pp < np; pp++) {
-#endif
 #pragma unroll
                     for (int it = 0; it < 2; it++) {
                         const int r = (it * 4 + uw) * 16 + rr;
@@ -420,123 +408,86 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     }
                 }
                 fence_proxy_async_smem();
-                mbar_arrive(&u8_full[u8.idx]);
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&raw_empty[raw.idx]);
+                mbar_arrive_elect(&u8_full[u8.idx]);
                 raw.advance();
                 u8.advance();
             }
         }
-#ifdef INKQ_ROLE_TIMERS
-        if (threadIdx.x == 128) {
-            prm.timers[blockIdx.x * 16 + 4] = tacc[0];
-            prm.timers[blockIdx.x * 16 + 5] = tacc[1];
-            prm.timers[blockIdx.x * 16 + 6] = clock64() - t_role0;
-        }
-#endif
     } else if (warp >= 8) {
         // ------------------------------ epilogue ------------------------------
-        // Software pipeline: the accumulator columns of a block are read in NCH chunks; while the
-        // arithmetic of one chunk runs, the tcgen05.ld of the next chunk (of this block or of the
-        // next one) is in flight into the other register buffer, so the TMEM round trip and the
-        // probe of the accumulator barrier are off the critical path.
+        // Software pipeline: a pair's accumulator columns are read in items (low block: chunks of CH
+        // columns, then the high block's); while the arithmetic of one item runs, the tcgen05.ld of
+        // the next item (of this pair or of the next one) is in flight into the other register
+        // buffer, so the TMEM round trip and the probe of the accumulator barrier are off the
+        // critical path.  The number of items per pair is even, so a given item always uses the
+        // same buffer.
         setmaxnreg_inc<EPI_REGS>();
-        constexpr int CH = (CW > 16) ? 16 : CW;    // columns per chunk
-        constexpr int NCH = (CW + CH - 1) / CH;    // 1 or 2 chunks (CW <= 32); the last one may be shorter
+        constexpr int CH = (CW > INKQ_TC_CHUNK) ? INKQ_TC_CHUNK : CW;    // columns per item
+        constexpr int NCH = (CW + CH - 1) / CH;
         constexpr int CH_LAST = CW - (NCH - 1) * CH;
+        constexpr int ITEMS = 2 * NCH;
         const int quad = warp & 3;             // TMEM lane quadrant this warp may read
         const int cq = (warp - 8) >> 2;        // which quarter of the accumulator columns
         const int row = quad * 32 + lane;      // weight row inside the tile = TMEM lane
         const int nbk = 2 * prm.pairs;
         const int col0 = cq * CW;              // first column of this warp inside the tile
-        Ring acc(ACC_STAGES), sc(SC_STAGES);
-        bool dead = false;
-#ifdef INKQ_ROLE_TIMERS
-        long long tacc[4] = {0, 0, 0, 0};
-        const long long t_role0 = clock64();
-#endif
-        for (int tile = blockIdx.x; tile < total_tiles && !dead; tile += gridDim.x) {
+        const uint32_t tmem_warp = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + col0;
+        Ring acc(ACC_SLOTS), sc(SC_STAGES);
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int tn = prm.tn0 + tile / prm.tiles_m, tm = tile % prm.tiles_m;
             const int n = tn * TILE_N + row;
             unsigned long long accp[CW / 2];
 #pragma unroll
             for (int j = 0; j < CW / 2; j++) accp[j] = 0ull;
-            uint32_t rbuf[2][CH];                 // the two chunk buffers
-            uint32_t taddr_pair = 0;              // TMEM address of the pair whose chunks are being loaded
-            uint32_t acc_loading = 0;             // its slot in the accumulator ring
+            uint32_t rbuf[2][CH];                 // the two item buffers
 
-            // waits for the next pair of the ring to be computed and starts the load of its first chunk
-            auto begin_pair = [&](uint32_t *dst) -> bool {
-                T_BEGIN();
-                if (!mbar_wait_abortable(abort_flag, &acc_full[acc.idx], acc.phase, 0u)) return false;
-                T_ADD(1);
-                tc_fence_after_sync();
-                taddr_pair = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc.idx * ACC_COLS + col0;
-                acc_loading = acc.idx;
-                acc.advance();
-                if (NCH == 1) tmem_ld_cols<CH_LAST>(taddr_pair, dst);
-                else tmem_ld_cols<CH>(taddr_pair, dst);
-                return true;
-            };
-            // completes the outstanding load; when it was the pair's last chunk, hands the TMEM slot back
-            auto finish_load = [&](bool last_chunk_of_pair) {
-                T_BEGIN();
-                tmem_ld_wait();
-                T_ADD(2);
-                if (last_chunk_of_pair) {
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_empty[acc_loading]);
-                }
-            };
-            // this row's weight scales {d_lo, d_hi, m_lo, m_hi} of a pair, fetched one pair ahead
-            auto load_wsc = [&](int pair) -> float4 {
-                const size_t rec = (static_cast<size_t>(tn) * prm.pairs + min(pair, prm.pairs - 1)) * TILE_N + row;
-                if (prm.sc32 != nullptr) return prm.sc32[rec];
-                const uint2 pk = prm.sc16[rec];
-                const float2 x0 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.x));
-                const float2 x1 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.y));
-                return make_float4(x0.x, x0.y, x1.x, x1.y);
-            };
+            // pipeline prologue: first item of the tile's first pair
+            tc_wait(&acc_full[acc.idx], acc.phase, abort_flag, prm.flag, 0u);
+            tc_fence_after_sync();
+            uint32_t taddr_cur = tmem_warp + acc.idx * SLOT_COLS;   // pair being consumed
+            uint32_t slot_cur = acc.idx;
+            acc.advance();
+            tmem_ld_cols<(NCH == 1) ? CH_LAST : CH>(taddr_cur, rbuf[0]);
 
-            // pipeline prologue: first chunk of the tile's first pair
-            if (!begin_pair(rbuf[0])) INKQ_GIVE_UP();
-            finish_load(false);
-            float4 wsc_next = load_wsc(0);
-
-            for (int p = 0; p < prm.pairs && !dead; p++) {
-                const float4 wsc = wsc_next;
-                wsc_next = load_wsc(p + 1);
+#pragma unroll 1
+            for (int p = 0; p < prm.pairs; p++) {
                 const int pj = p & (STAGE_PAIRS - 1);
-                if (pj == 0 && !DUMP) {
-                    T_BEGIN();
-                    if (!mbar_wait_abortable(abort_flag, &sc_full[sc.idx], sc.phase, 0u)) INKQ_GIVE_UP();
-                    T_ADD(0);
-                }
-                const float *sd_lo = reinterpret_cast<const float *>(sc_base + sc.idx * SC_STAGE_BYTES) + (2 * pj) * BLOCK_M + col0;
-                const float *ss_lo = sd_lo + SC_PLANE_BYTES / 4;   // s_a of the low block; the high block's follows
-                const uint32_t taddr_cur = taddr_pair;             // the pair being consumed (begin_pair below re-targets taddr_pair)
+                if (pj == 0 && !DUMP) tc_wait(&sc_full[sc.idx], sc.phase, abort_flag, prm.flag, 0u);
+                const unsigned char *scst = sc_base + sc.idx * SC_STAGE_BYTES;
+                const float *sd_lo = reinterpret_cast<const float *>(scst) + (2 * pj) * BLOCK_M + col0;   // d_a of the low block; the high block's follows
+                const float *ss_lo = sd_lo + SC_PLANE_BYTES / 4;                                         // s_a likewise
+                float4 wsc = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (!DUMP) wsc = *reinterpret_cast<const float4 *>(scst + 2 * SC_PLANE_BYTES + (pj * TILE_N + row) * 16);
+                const unsigned long long mlo = pack2(wsc.z, wsc.z), mhi = pack2(wsc.w, wsc.w);
+                uint32_t taddr_next = taddr_cur, slot_next = slot_cur;
 #pragma unroll
-                for (int it = 0; it < 2 * NCH; it++) {   // items of the pair: (low, chunks...), (high, chunks...)
+                for (int it = 0; it < ITEMS; it++) {   // items of the pair: (low, chunks...), (high, chunks...)
                     const int hi = it / NCH, c = it % NCH;
-                    const int b = 2 * p + hi;
-                    const float dw = hi ? wsc.y : wsc.x;
-                    const float *sd = sd_lo + hi * BLOCK_M;          // d_a of this block
-                    // item `it` sits in rbuf[it & 1]; start the load of the item after it into the other buffer
                     const int cur = it & 1, nxt = cur ^ 1;
-                    bool loading = false;
-                    if (it + 1 < 2 * NCH) {   // next chunk of the same pair
+                    tmem_ld_wait();   // item `it` has arrived in rbuf[cur]
+                    if (it == ITEMS - 1) {
+                        // that was the pair's last load: hand the TMEM slot back
+                        tc_fence_before_sync();
+                        mbar_arrive_elect(&acc_empty[slot_cur]);
+                    }
+                    // start the load of the item after it into the other buffer
+                    if (it + 1 < ITEMS) {
                         const int nhi = (it + 1) / NCH, nc = (it + 1) % NCH;
-                        if (nc == NCH - 1) tmem_ld_cols<CH_LAST>(taddr_cur + nhi * 128 + nc * CH, rbuf[nxt]);
-                        else tmem_ld_cols<CH>(taddr_cur + nhi * 128 + nc * CH, rbuf[nxt]);
-                        loading = true;
-                    } else if (p + 1 < prm.pairs) {   // first chunk of the next pair
-                        if (!begin_pair(rbuf[nxt])) INKQ_GIVE_UP();
-                        loading = true;
+                        if (nc == NCH - 1) tmem_ld_cols<CH_LAST>(taddr_cur + nhi * BLOCK_M + nc * CH, rbuf[nxt]);
+                        else tmem_ld_cols<CH>(taddr_cur + nhi * BLOCK_M + nc * CH, rbuf[nxt]);
+                    } else if (p + 1 < prm.pairs) {   // first item of the next pair
+                        tc_wait(&acc_full[acc.idx], acc.phase, abort_flag, prm.flag, 0u);
+                        tc_fence_after_sync();
+                        taddr_next = tmem_warp + acc.idx * SLOT_COLS;
+                        slot_next = acc.idx;
+                        acc.advance();
+                        tmem_ld_cols<(NCH == 1) ? CH_LAST : CH>(taddr_next, rbuf[nxt]);
                     }
                     const uint32_t *raw = rbuf[cur];
                     const int ncols = (c == NCH - 1) ? CH_LAST : CH;
                     if (DUMP) {
+                        const int b = 2 * p + hi;
 #pragma unroll
                         for (int j = 0; j < CH; j++) {
                             const int m = tm * BLOCK_M + col0 + c * CH + j;
@@ -544,20 +495,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                                 prm.dots[(static_cast<size_t>(m) * prm.rows + n) * nbk + b] = static_cast<int32_t>(raw[j]);
                         }
                     } else {
+                        const float dw = hi ? wsc.y : wsc.x;
+                        const unsigned long long dw2 = pack2(dw, dw);
+                        const float *sd = sd_lo + hi * BLOCK_M + c * CH;   // d_a of this block, this item's columns
 #pragma unroll
                         for (int j4 = 0; j4 < CH; j4 += 4) {
                             if (j4 < ncols) {
                                 // 128-bit shared loads straight into 64-bit register pairs: (d_a[m], d_a[m+1]) is already the
-                                // packed operand of the f32x2 instructions, no pack moves
-                                const ulonglong2 da = *reinterpret_cast<const ulonglong2 *>(sd + c * CH + j4);
-                                const unsigned long long dw2 = pack2(dw, dw);
+                                // packed operand of the f32x2 instructions
+                                const ulonglong2 da = *reinterpret_cast<const ulonglong2 *>(sd + j4);
                                 const int a0 = (c * CH + j4) / 2;
                                 accp[a0] = fma2(cvt2_exact(raw[j4], raw[j4 + 1]), mul2(da.x, dw2), accp[a0]);
                                 accp[a0 + 1] = fma2(cvt2_exact(raw[j4 + 2], raw[j4 + 3]), mul2(da.y, dw2), accp[a0 + 1]);
                                 if (HAS_MIN && hi) {
                                     const ulonglong2 s0 = *reinterpret_cast<const ulonglong2 *>(ss_lo + c * CH + j4);
                                     const ulonglong2 s1 = *reinterpret_cast<const ulonglong2 *>(ss_lo + BLOCK_M + c * CH + j4);
-                                    const unsigned long long mlo = pack2(wsc.z, wsc.z), mhi = pack2(wsc.w, wsc.w);
                                     accp[a0] = fma2(mlo, s0.x, accp[a0]);
                                     accp[a0] = fma2(mhi, s1.x, accp[a0]);
                                     accp[a0 + 1] = fma2(mlo, s0.y, accp[a0 + 1]);
@@ -566,17 +518,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                             }
                         }
                     }
-                    if (loading) finish_load(it + 1 == 2 * NCH - 1);
                 }
-                if (dead) break;
+                taddr_cur = taddr_next;
+                slot_cur = slot_next;
                 if (!DUMP && (pj == STAGE_PAIRS - 1 || p == prm.pairs - 1)) {
                     // this warp is done with the stage's scales
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&sc_empty[sc.idx]);
+                    mbar_arrive_elect(&sc_empty[sc.idx]);
                     sc.advance();
                 }
             }
-            if (!dead && !DUMP && n < prm.rows) {
+            if (!DUMP && n < prm.rows) {
                 float accf[CW];
 #pragma unroll
                 for (int j = 0; j < CW / 2; j++) unpack2(accp[j], accf[2 * j], accf[2 * j + 1]);
@@ -598,17 +550,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 }
             }
         }
-#ifdef INKQ_ROLE_TIMERS
-        if (threadIdx.x == 256 || threadIdx.x == 256 + 12 * 32) {
-            const int o = (threadIdx.x == 256) ? 8 : 12;
-            prm.timers[blockIdx.x * 16 + o + 0] = tacc[0];
-            prm.timers[blockIdx.x * 16 + o + 1] = tacc[1];
-            prm.timers[blockIdx.x * 16 + o + 2] = tacc[2];
-            prm.timers[blockIdx.x * 16 + o + 3] = clock64() - t_role0;
-        }
-#endif
     }
-#undef INKQ_GIVE_UP
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 2) {
@@ -621,20 +563,29 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// The opt-in for large dynamic shared memory is a per-device function attribute: remember per device
+// (and per instantiation, through the template's own statics) whether it has been set.
+constexpr int MAX_DEVICES = 64;
+
 template <int CW, bool HAS_MIN, bool DUMP>
 static int launch_one(inkq_ctx *ctx, const CUtensorMap *maps, const TcParams &prm, int grid)
 {
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncAttributes attr;
-        cudaError_t e = cudaFuncGetAttributes(&attr, k_qgemm_tc<CW, HAS_MIN, DUMP>);
-        if (e != cudaSuccess) return fail(ctx, INKQ_ERR_CUDA, std::string("cudaFuncGetAttributes(k_qgemm_tc): ") + cudaGetErrorString(e));
-        if (attr.numRegs != LAUNCH_REGS)   // the in-kernel register re-balancing is sized for exactly this launch value
-            return fail(ctx, INKQ_ERR_UNSUPPORTED, "k_qgemm_tc was compiled to " + std::to_string(attr.numRegs) + " registers per thread, expected " +
-                                                       std::to_string(LAUNCH_REGS));
-        e = cudaFuncSetAttribute(k_qgemm_tc<CW, HAS_MIN, DUMP>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
-        if (e != cudaSuccess) return fail(ctx, INKQ_ERR_CUDA, std::string("cudaFuncSetAttribute(k_qgemm_tc): ") + cudaGetErrorString(e));
-        configured = true;
+    static std::mutex mu;
+    static bool configured[MAX_DEVICES] = {};
+    if (ctx->device < 0 || ctx->device >= MAX_DEVICES) return fail(ctx, INKQ_ERR_UNSUPPORTED, "device index beyond the launch table");
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (!configured[ctx->device]) {
+            cudaFuncAttributes attr;
+            cudaError_t e = cudaFuncGetAttributes(&attr, k_qgemm_tc<CW, HAS_MIN, DUMP>);
+            if (e != cudaSuccess) return fail(ctx, INKQ_ERR_CUDA, std::string("cudaFuncGetAttributes(k_qgemm_tc): ") + cudaGetErrorString(e));
+            if (attr.numRegs != LAUNCH_REGS)   // the in-kernel register re-balancing is sized for exactly this launch value
+                return fail(ctx, INKQ_ERR_UNSUPPORTED, "k_qgemm_tc was compiled to " + std::to_string(attr.numRegs) + " registers per thread, expected " +
+                                                           std::to_string(LAUNCH_REGS));
+            e = cudaFuncSetAttribute(k_qgemm_tc<CW, HAS_MIN, DUMP>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
+            if (e != cudaSuccess) return fail(ctx, INKQ_ERR_CUDA, std::string("cudaFuncSetAttribute(k_qgemm_tc): ") + cudaGetErrorString(e));
+            configured[ctx->device] = true;
+        }
     }
     k_qgemm_tc<CW, HAS_MIN, DUMP><<<grid, TC_THREADS, TC_SMEM_BYTES, ctx->stream>>>(maps[0], maps[1], maps[2], prm);
     return after_launch(ctx, "k_qgemm_tc");
@@ -670,24 +621,27 @@ static int encode2d(inkq_ctx *ctx, CUtensorMap *map, CUtensorMapDataType dt, int
     return INKQ_OK;
 }
 
+// Relative cost of one tile by its width block_m = 16 * index (any common factor cancels; measured on a B200 with
+// one tile per SM): narrow tiles are bounded by the serial chain of K=32 MMAs, wide ones by the epilogue arithmetic.
+static const float tile_cost[9] = {0.f, 1.00f, 1.05f, 1.11f, 1.28f, 1.47f, 1.66f, 1.72f, 1.98f};
+
 int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc, int32_t *dots, const ExtraDst *extra, int tn_begin, int tn_count)
 {
     if (tn_count < 0) tn_count = w->tiles - tn_begin;   // default: every tile from tn_begin on
     if (ctx->encode_tiled == nullptr) return fail(ctx, INKQ_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled entry point not available");
+    if (w->sc32 == nullptr) return fail(ctx, INKQ_ERR_INVALID, "this weight holds no fp32 scale records (weight-only layers use inkq_gemm_w41_f16act)");
     const int M = a->M;
-    // Split of the M activation rows into tiles of block_m columns (a multiple of 16, at most 128).  A tile's time
-    // has a floor set by the serial K=32 MMAs and grows with block_m only above ~48 columns (measured on a B200,
-    // one tile per SM, K=4096, in us; only the ratios matter).  With few weight tiles (a shard of a column-sharded
-    // layer) narrower tiles fill more SMs; the choice minimises waves x tile time.  It depends on the shapes and
-    // the SM count only, and every choice gives the same bits (the per-output operation order never changes).
-    static const float tile_us[9] = {0.f, 43.5f, 45.5f, 48.3f, 55.6f, 64.0f, 72.4f, 75.0f, 86.3f};   // block_m = 16 * index
+    // Split of the M activation rows into tiles of block_m columns (a multiple of 16, at most 128).  With few
+    // weight tiles (a shard of a column-sharded layer) narrower tiles fill more SMs; the choice minimises
+    // waves x tile cost.  It depends on the shapes and the SM count only, and every choice gives the same bits
+    // (the per-output operation order never changes).
     int tiles_m = (M + 127) / 128, block_m = 128;
     {
         float best = 0.f;
         for (int tm = (M + 127) / 128; tm <= (M + 15) / 16; tm++) {
             const int bm = (((M + tm - 1) / tm) + 15) & ~15;
             const long long total = static_cast<long long>(tn_count) * tm;
-            const float cost = static_cast<float>((total + ctx->num_sms - 1) / ctx->num_sms) * tile_us[bm / 16];
+            const float cost = static_cast<float>((total + ctx->num_sms - 1) / ctx->num_sms) * tile_cost[bm / 16];
             if (best == 0.f || cost < best * 0.999f) {
                 best = cost;
                 tiles_m = tm;
@@ -707,7 +661,6 @@ int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int l
     TcParams prm;
     prm.nibT = w->nibT;
     prm.sc32 = w->sc32;
-    prm.sc16 = w->sc16;
     prm.zpT = w->zpT;
     prm.C = C;
     prm.extra = ExtraDst{};
@@ -715,40 +668,17 @@ int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int l
     prm.dots = dots;
     prm.flag = ctx->dev_flag;
     prm.M = M;
-    prm.M_ld = a->M_ld;
     prm.rows = w->rows;
-    prm.K = w->K;
     prm.pairs = w->pairs;
     prm.tn0 = tn_begin;
     prm.tiles_n = tn_count;
     prm.tiles_m = tiles_m;
-    prm.block_m = block_m;
     prm.ldc = ldc;
-#ifdef INKQ_ROLE_TIMERS
-    static long long *timers_dev = nullptr;
-    if (timers_dev == nullptr) cudaMalloc(reinterpret_cast<void **>(&timers_dev), 256 * 16 * sizeof(long long));
-    prm.timers = timers_dev;
-#endif
     const int total = prm.tiles_n * prm.tiles_m;
     const int grid = total < ctx->num_sms ? total : ctx->num_sms;
-    int rc2;
-    if (dots != nullptr) rc2 = launch_cw<false, true>(ctx, block_m / 4, maps, prm, grid);
-    else if (w->scheme == INKQ_A81W41) rc2 = launch_cw<true, false>(ctx, block_m / 4, maps, prm, grid);
-    else rc2 = launch_cw<false, false>(ctx, block_m / 4, maps, prm, grid);
-#ifdef INKQ_ROLE_TIMERS
-    {
-        static long long host_t[256 * 16];
-        cudaMemcpy(host_t, prm.timers, sizeof(host_t), cudaMemcpyDeviceToHost);
-        const char *names[16] = {"mma.wait_raw_full", "mma.wait_u8_full", "mma.wait_acc_empty", "-", "unpack.wait_raw_full", "unpack.wait_u8_empty", "unpack.total", "-",
-                                 "epi0.wait_sc_full", "epi0.wait_acc_full", "epi0.tmem_ld", "epi0.total", "epi12.wait_sc_full", "epi12.wait_acc_full", "epi12.tmem_ld", "epi12.total"};
-        for (int i = 0; i < 16; i++) {
-            double sum = 0;
-            for (int b = 0; b < grid; b++) sum += static_cast<double>(host_t[b * 16 + i]);
-            fprintf(stderr, "[role timers] %-24s %12.0f cycles avg per CTA\n", names[i], sum / grid);
-        }
-    }
-#endif
-    return rc2;
+    if (dots != nullptr) return launch_cw<false, true>(ctx, block_m / 4, maps, prm, grid);
+    if (w->scheme == INKQ_A81W41) return launch_cw<true, false>(ctx, block_m / 4, maps, prm, grid);
+    return launch_cw<false, false>(ctx, block_m / 4, maps, prm, grid);
 }
 
 }  // namespace inkq

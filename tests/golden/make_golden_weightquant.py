@@ -18,7 +18,9 @@ import torch
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden_weightquant.py /path/to/Qwen3.Ink.Cpp")
+    ref = sys.argv[1]
     sys.path.insert(0, os.path.join(ref, "notebooks"))
     import quantize_methods as qm   # the reference's own code
 

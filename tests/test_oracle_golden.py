@@ -4,7 +4,7 @@ and, where oracle/_ref is present, against the reference kernels run live."""
 import numpy as np
 import pytest
 
-from conftest import f16
+from conftest import f16, rel_err
 from oracle.inkq_oracle import Q4_FP16, Q4_FP32, Q8_FP16, Q8_FP32
 
 
@@ -170,3 +170,45 @@ def test_live_reference_a81w41(oracle, reference, pkg, M, N, K):
     q1, d1, s1 = oracle.quantize(x[:1], 1)
     assert np.array_equal(oracle.gemm(0, q1, d1, s1, w["nib"], f16(d_any), f16(w["m"])).view(np.uint32),
                           reference.matmul("gemv_repack_A81W41_fp16", A1, B1, 1, N, K).view(np.uint32))
+
+
+# ------------------------------------------------------------------ schemes that exist only in the reference's notebooks
+def rms_err(got, ref):
+    ref = np.asarray(ref, np.float64)
+    return float(np.abs(np.asarray(got, np.float64) - ref).max() / np.sqrt(np.mean(ref * ref)))
+
+
+def test_a80w4z_matches_the_notebook(oracle, golden):
+    """Fixture: outputs of the reference's own notebook cell (QuantizedLinear + pseudo_quantize_tensor_q4_zero_point,
+    evaluate-qwen3_8b_A8W4.ipynb) run by tests/golden/make_golden_notebook.py.  With the notebook's own activation
+    codes and fp32 scales the oracle's integer form sum_b d_a*d_w*(I - zp*sum(q_a)) equals the notebook's
+    dequantise-then-linear to summation-order accuracy: this pins the scheme's math.  Through the real path (the
+    reference's Q8_0 quantizer stores the activation scale as fp16, the packed weights carry fp16 scales; the notebook
+    keeps both in fp32) the two fp16 roundings of the scales show: a few 1e-3 of the output's rms."""
+    g = golden("ref_notebook_schemes.npz")
+    y = oracle.gemm(2, g["w4z_xq"], g["w4z_xd"], None, g["w4z_nib"], g["w4z_d"], None, g["w4z_zp"])
+    assert rel_err(y, g["w4z_y"]) < 1e-3
+    q, d, _ = oracle.quantize(g["w4z_x"], 0)
+    assert np.array_equal(q, g["w4z_xq"])                     # same integer codes as the notebook's fake quantizer
+    y16 = oracle.gemm(2, q, d, None, g["w4z_nib"], f16(g["w4z_d"]), None, g["w4z_zp"])
+    assert rms_err(y16, g["w4z_y"]) < 3e-3
+
+
+def test_w41_matches_the_notebook(oracle, golden):
+    """Fixture: the reference's weight-only notebook (evaluate-qwen3_8b_W4.ipynb: fp16 model, weights overwritten with
+    pseudo_quantize_tensor_q41's output, stock fp16 F.linear).  The notebook rounds q*s to fp16 and then adds the
+    minimum (two roundings); this library rounds q*d + m once: the dequantised weights differ by at most one fp16 ulp
+    of the intermediate product q*s (half of them are identical).
+    Its output is fp16 (this library's is fp32): agreement to the fp16 rounding of the output, a few 1e-3 of its rms."""
+    g = golden("ref_notebook_schemes.npz")
+    K = g["w41_x"].shape[1]
+    ours = oracle.gemm_w41_f16act(np.eye(K, dtype=np.float16), g["w41_nib"], g["w41_d"], g["w41_m"]).T    # one-hot rows read the weights back
+    theirs = g["w41_wf"].astype(np.float32)
+    nib = g["w41_nib"].reshape(g["w41_nib"].shape[0], -1, 32)
+    q = np.stack([nib & 15, nib >> 4], axis=2).reshape(theirs.shape).astype(np.float32)      # undo the AWQ interleave
+    prod = q * np.repeat(g["w41_d"], 32, axis=1)
+    ulp = np.spacing(np.maximum(np.abs(prod), np.abs(theirs)).astype(np.float16)).astype(np.float32)
+    assert np.all(np.abs(ours - theirs) <= ulp)
+    assert np.mean(ours == theirs) > 0.5
+    y = oracle.gemm_w41_f16act(g["w41_x"], g["w41_nib"], g["w41_d"], g["w41_m"])
+    assert rms_err(y, g["w41_y"].astype(np.float32)) < 4e-3

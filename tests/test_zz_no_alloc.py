@@ -35,6 +35,27 @@ def test_two_calls_in_a_row_match_the_regular_forward(pkg, gpu):
         assert np.array_equal(g[:, :N], r)        # same kernels on the same data: in fact identical
 
 
+def test_calls_leave_the_free_device_memory_unchanged(pkg, gpu):
+    """The property in the entry point's name: around calls of it, cudaMemGetInfo reports the same free figure.
+    Everything the test itself needs is allocated first, and one call is made before the measurement because the
+    first use of a kernel makes the driver load its code."""
+    import torch
+    N, K = 4096, 4096
+    w = pkg.synth.weights(N, K, 21)
+    wh = gpu.weight(pkg.A81W41, pkg.SCALES_F16, w["nib"], w["d"], w["m"])
+    x = torch.from_numpy(pkg.synth.activations(1, K, 21)).cuda()
+    out = torch.empty((1, N), device="cuda")
+    gpu.linear_m1_static(wh, x, out)
+    gpu.synchronize()
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(5):
+        gpu.linear_m1_static(wh, x, out)
+    gpu.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, f"free device memory changed by {free_before - free_after} bytes across the calls"
+
+
 def test_sizes_beyond_the_static_scratch_are_rejected(pkg, gpu):
     import torch
     K = 16384 + 64
