@@ -19,12 +19,19 @@ shape: M=322 activations x K=4096, N=12288 A81W41 weights (fp32 block scales).
 The line also carries the roofline of the dominant kernel, the reference's CPU kernels timed on
 this box, the decode QGEMV sweep, the scheme matrix and pp322 / tg128 of a synthetic Qwen3-8B
 (--no-gemv / --no-model skip the last three).  Other workloads (--workload): qgemv_sweep,
-qgemm_m2048, qgemm_m8192.
+qgemm_m2048, qgemm_m8192, lmhead_m8192 (fp16 lm_head 151936 x 4096 for 8192 rows on the tensor cores).
+The K timed steps are repeated back to back until the timed region lasts --min-seconds (default 1 s), so
+that the clock samples fall inside it; "repeats" says how often.
+  --case NAME [ARGS]   runs one small fixed case of one kernel a few times and exits: what the profiler
+          captures summarised under profiles/ run (qgemm [M], qgemv [N K], quantize [M], model [layers],
+          w41 [M], lmhead [M])
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -104,6 +111,29 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def base_config(wl, M, N, K):
+    """The workload description both arms print (identical keys and values)."""
+    if wl == "lmhead_m8192":
+        return {"workload": wl, "M": M, "N": N, "K": K, "weights": "fp16", "activations": "fp32"}
+    return {"workload": wl, "M": M, "N": N, "K": K, "scheme": "A81W41", "weight_scales": "fp32"}
+
+
+def host_threads():
+    """Pins the OpenMP team of the CPU checkers to every core this process may use (torchrun exports
+    OMP_NUM_THREADS=1) and returns the team size OpenMP then reports."""
+    try:
+        want = len(os.sched_getaffinity(0))
+    except AttributeError:
+        want = os.cpu_count() or 1
+    os.environ["OMP_NUM_THREADS"] = str(want)
+    try:
+        gomp = ctypes.CDLL("libgomp.so.1", mode=ctypes.RTLD_GLOBAL)
+        gomp.omp_set_num_threads(want)
+        return int(gomp.omp_get_max_threads())
+    except OSError:
+        return want
+
+
 def cuda_time_ms(torch, fn, iters):
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
@@ -123,7 +153,7 @@ def run_reference(args, rank, world):
     M, K, N = M_PP, K_PP, N_PP
     x = pkg.synth.activations(M, K)
     w = pkg.synth.weights(N, K)
-    cores = os.cpu_count() or 1
+    cores = host_threads()
     kind = "reference" if Reference.available_path()[0] else "port"
     isa = "scalar"
     if kind == "reference":
@@ -134,7 +164,8 @@ def run_reference(args, rank, world):
         def step():
             A = ref.quantize_struct(x, 2, pad_rows=6 * K // 64, prefill=0)     # quantize_row_q8_1_repack_fp32
             return ref.matmul("gemm_repack_A81W41_fp32", A, B, M, N, K)       # gemm_repack_A81W41_fp32
-        sample = f"full workload: quantize_row_q8_1_repack_fp32 + gemm_repack_A81W41_fp32 at {M}x{N}x{K}, all {cores} host threads"
+        sample = (f"full workload: quantize_row_q8_1_repack_fp32 (1 thread, as the reference) + gemm_repack_A81W41_fp32 at {M}x{N}x{K} "
+                  f"with an OpenMP team of {cores} threads (omp_get_max_threads after omp_set_num_threads)")
         ops = 2.0 * M * N * K
     else:
         orc = Oracle()
@@ -148,14 +179,20 @@ def run_reference(args, rank, world):
     for _ in range(args.warmup):
         step()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    step()
+    est = time.perf_counter() - t0
+    repeats = max(1, min(50, int(math.ceil(args.min_seconds / max(est * args.steps, 1e-6)))))
+    t0 = time.perf_counter()
+    for _ in range(args.steps * repeats):
         step()
-    dt = (time.perf_counter() - t0) / args.steps
+    total = time.perf_counter() - t0
+    dt = total / (args.steps * repeats)
     tops = ops / dt / 1e12
     line = {"impl": "reference", "metric": "qgemm_int8_tops_pp322", "value": tops, "unit": "TOPS", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 * (2.0 * M * N * K / ops), "higher_is_better": True,
+            "steps": args.steps, "warmup": args.warmup, "repeats": repeats, "timed_region_s": total,
+            "ms_per_step": dt * 1e3 * (2.0 * M * N * K / ops), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "s8 x u4 -> s32, fp32 scale/accumulate", "data": "synthetic",
-            "config": {"workload": "qgemm_pp322", "M": M, "N": N, "K": K, "scheme": "A81W41", "isa": isa},
+            "config": base_config("qgemm_pp322", M, N, K), "host": {"isa": isa, "omp_threads": cores},
             "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cores, "kind": kind, "sample": sample},
             "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
@@ -165,7 +202,7 @@ def run_reference(args, rank, world):
 def cpu_baseline_pp322(pkg, x, w):
     from oracle.inkq_oracle import Oracle, Reference
     M, K, N = M_PP, K_PP, N_PP
-    cores = os.cpu_count() or 1
+    cores = host_threads()
     if Reference.available_path()[0]:
         ref = Reference()
         B = ref.repack(w["nib"], w["d"], w["m"], 2)
@@ -375,6 +412,308 @@ def model_pp_tg(pkg, torch, ctx, prompt_len=322, new_tokens=128, reps=3):
     return out
 
 
+def model_tp(pkg, torch, dist, ctx, world, rank, prompt_len=322, new_tokens=128, batch=8):
+    """The synthetic Qwen3-8B with every linear column-sharded over `world` GPUs (outputs exchanged by the kernels' own
+    peer stores + a barrier kernel per linear; norms, attention and caches replicated): pp322, tg128 (separate operators
+    per decode step, captured as one CUDA graph) and the prefill of `batch` prompts of 322 tokens as one batch.
+    Times are the maximum over ranks."""
+    cfg = pkg.qwen3_forward.Qwen3Config(max_pos=prompt_len + new_tokens + 32, decode_mode="separate")
+    model = pkg.qwen3_forward.Qwen3Synthetic(pkg, ctx, cfg, seed=7, world=world, rank=rank, dist=dist if world > 1 else None,
+                                             batch=batch, max_rows=batch * prompt_len)
+    prompt = torch.from_numpy(pkg.synth.tokens(prompt_len, cfg.vocab)).cuda()
+    prompts = torch.from_numpy(np.stack([pkg.synth.tokens(prompt_len, cfg.vocab, 1007 + i) for i in range(batch)])).cuda()
+
+    def mx(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    model.reset()
+    model.prefill(prompt)
+    model.decode_step()
+    model.capture_decode()
+    torch.cuda.synchronize()
+    pp_ms, tg_ms, pb_ms = [], [], []
+    for _ in range(2):
+        model.reset()
+        if world > 1:
+            dist.barrier()
+        a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        a.record()
+        model.prefill(prompt)
+        b.record()
+        for _ in range(new_tokens):
+            model.graph.replay()
+        c.record()
+        torch.cuda.synchronize()
+        pp_ms.append(mx(a.elapsed_time(b)))
+        tg_ms.append(mx(b.elapsed_time(c)))
+        model.reset()
+        if world > 1:
+            dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        model.prefill_batch(prompts)
+        b.record()
+        torch.cuda.synchronize()
+        pb_ms.append(mx(a.elapsed_time(b)))
+    out = {"n_gpus": world, "pp322_tok_s": prompt_len / (min(pp_ms) * 1e-3), "tg128_tok_s": new_tokens / (min(tg_ms) * 1e-3),
+           "prefill_ms": min(pp_ms), "decode_ms_per_token": min(tg_ms) / new_tokens,
+           "batch_prefill": {"prompts": batch, "tokens_each": prompt_len, "ms": min(pb_ms), "tok_s": batch * prompt_len / (min(pb_ms) * 1e-3)},
+           "decode_mode": "separate operators (17 launches per layer" + (" + 5 barrier kernels" if world > 1 else "") + "), one CUDA graph per step",
+           "sharding": "every linear column-sharded, outputs exchanged by peer stores from the kernels' epilogues" if world > 1 else "none"}
+    model.close()
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
+# --------------------------------------------------------------------------- helpers of our arm
+def timed_region(torch, dist, world, run_k_steps, est_ms_per_k, min_seconds):
+    """Runs `run_k_steps()` (K steps) R times back to back between two CUDA events, R chosen so that the region lasts
+    about min_seconds; returns (total ms = max over ranks, R)."""
+    repeats = max(1, min(20000, int(math.ceil(min_seconds * 1e3 / max(est_ms_per_k, 1e-3)))))
+    if world > 1:
+        t = torch.tensor([repeats], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)      # every rank runs the same number of steps
+        repeats = int(t.item())
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = cuda_time_ms(torch, lambda i: run_k_steps(), repeats)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    return ms, repeats
+
+
+def capture_steps(torch, ctx, step, k):
+    """K steps as one CUDA graph (a sharded step is tens of microseconds of GPU work; one Python process per GPU
+    cannot enqueue its launches that fast).  Returns the graph, or None when capture is not possible."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    try:
+        with torch.cuda.stream(side):
+            ctx.set_stream(side.cuda_stream)
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(k):
+                    step(i)
+    except Exception:
+        graph = None
+    finally:
+        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    return graph
+
+
+def tp_check(pkg, torch, dist, ctx, scatter, w_shard, wt, x, M, N, rank):
+    """The exchange under test against one GPU: rank 0 computes the unsharded [M][N] once and broadcasts it, every
+    rank runs one sharded step and compares its assembled matrix bit for bit."""
+    full = torch.empty((M, N), device="cuda")
+    if rank == 0:
+        w_full = ctx.weight(pkg.A81W41, pkg.SCALES_F32, wt["nib"], wt["d"], wt["m"])
+        ctx.linear(w_full, x, M, full, N)
+        ctx.synchronize()
+        w_full.close()
+    dist.broadcast(full, 0)
+    scatter.linear(w_shard, x, 0)
+    scatter.barrier()
+    ctx.synchronize()
+    ok = torch.tensor([1 if torch.equal(scatter.result(0), full) else 0], device="cuda")
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    return bool(ok.item())
+
+
+def scaling_m8192(pkg, torch, dist, ctx, world, rank, pk, min_seconds=0.3):
+    """The column-sharded large-M workloads of the scaling configuration, timed like the headline step (K steps in a
+    graph when sharded, max over ranks): the M=8192 prefill QGEMM (12288 x 4096) and the fp16 lm_head GEMM
+    (151936 x 4096 for 8192 rows, activations rounded to fp16: one pass over the weights)."""
+    out = {}
+    M, K = 8192, K_PP
+    x = torch.randn((M, K), device="cuda", generator=torch.Generator(device="cuda").manual_seed(5))
+    # ---- QGEMM
+    N = N_PP
+    n0, n1 = pkg.tp.shard_range(N, world, rank)
+    wt = pkg.synth.weights(N, K)
+    sets = 3
+    ws = [ctx.weight(pkg.A81W41, pkg.SCALES_F32, wt["nib"], wt["d"], wt["m"], None, n0, n1) for _ in range(sets)]
+    sc = pkg.tp.PeerScatter(pkg, ctx, dist, M, N, world, rank, slots=2) if world > 1 else None
+    Cl = torch.empty((M, n1 - n0), device="cuda") if world == 1 else None
+
+    def step(i):
+        if sc is None:
+            ctx.linear(ws[i % sets], x, M, Cl, n1 - n0)
+        else:
+            sc.linear(ws[i % sets], x, i % 2)
+            sc.barrier()
+    k = 6
+    for i in range(3):
+        step(i)
+    torch.cuda.synchronize()
+    g = capture_steps(torch, ctx, step, k) if world > 1 else None
+    run = (lambda: g.replay()) if g is not None else (lambda: [step(i) for i in range(k)])
+    run()
+    torch.cuda.synchronize()
+    est = cuda_time_ms(torch, lambda i: run(), 1)
+    ms, reps = timed_region(torch, dist, world, run, est, min_seconds)
+    per = ms / (reps * k)
+    out["qgemm"] = {"M": M, "N": N, "K": K, "ms_per_step": per, "TOPS": 2.0 * M * N * K / (per * 1e-3) / 1e12,
+                    "timing": "graph" if g is not None else "eager", "exchange": "peer stores from the epilogue + barrier kernel" if sc else "none"}
+    for h in ws:
+        h.close()
+    if sc is not None:
+        sc.close()
+    del sc, Cl, g
+    torch.cuda.empty_cache()
+    # ---- fp16 lm_head
+    vocab = 151936
+    v0, v1 = pkg.tp.shard_range(vocab, world, rank)
+    gen = torch.Generator(device="cuda").manual_seed(1006)
+    w16 = (torch.randn((v1 - v0, K), device="cuda", generator=gen) * 0.02).half()
+    wh = ctx.f16w_dev(w16, v1 - v0, K)
+    del w16
+    sc = pkg.tp.PeerScatter(pkg, ctx, dist, M, vocab, world, rank, slots=1) if world > 1 else None
+    Cl = torch.empty((M, v1 - v0), device="cuda") if world == 1 else None
+
+    def lstep(i):
+        if sc is None:
+            ctx.f16w_matmul_prec(wh, x, M, Cl, v1 - v0, 1)
+        else:
+            ctx.f16w_matmul_scatter(wh, x, M, sc.ps, pkg.tp.scatter_offset(0, M, vocab, v0, pkg.PEER_RESERVED_BYTES), vocab, 1)
+            sc.barrier()
+    for i in range(2):
+        lstep(i)
+    torch.cuda.synchronize()
+    est = cuda_time_ms(torch, lambda i: lstep(i), 1)
+    ms, reps = timed_region(torch, dist, world, lambda: lstep(0), est, min_seconds)
+    per = ms / reps
+    out["lm_head"] = {"M": M, "N": vocab, "K": K, "ms_per_step": per, "TFLOPS": 2.0 * M * vocab * K / (per * 1e-3) / 1e12,
+                      "frac_of_bf16_burst": 2.0 * M * vocab * K / (per * 1e-3) / 1e12 / pk["bf16_tflops"], "activations": "fp16 (one pass)",
+                      "timing": "eager", "exchange": "peer stores from the epilogue + barrier kernel" if sc else "none"}
+    wh.close()
+    if sc is not None:
+        sc.close()
+    return out
+
+
+# --------------------------------------------------------------------------- the lm_head workload (one GPU)
+def run_lmhead(args, pkg, torch, ctx, pk, local_rank):
+    M, K, N = 8192, K_PP, 151936
+    gen = torch.Generator(device="cuda").manual_seed(1006)
+    w16 = (torch.randn((N, K), device="cuda", generator=gen) * 0.02).half()
+    wh = ctx.f16w_dev(w16, N, K)
+    del w16
+    x_host = pkg.synth.activations(M, K)
+    x = torch.from_numpy(x_host).cuda()
+    C = torch.empty((M, N), device="cuda")
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    res = {}
+    for name, prec in (("fp16_activations_one_pass", 1), ("fp32_grade_two_passes", 0)):
+        for _ in range(max(1, args.warmup // 2)):
+            ctx.f16w_matmul_prec(wh, x, M, C, N, prec)
+        torch.cuda.synchronize()
+        l0 = ctx.launches
+        est = cuda_time_ms(torch, lambda i: ctx.f16w_matmul_prec(wh, x, M, C, N, prec), 1)
+        k = max(1, min(args.steps, 10))
+        ms, reps = timed_region(torch, None, 1, lambda: [ctx.f16w_matmul_prec(wh, x, M, C, N, prec) for _ in range(k)], est * k, args.min_seconds)
+        res[name] = {"ms_per_step": ms / (reps * k), "steps": k, "repeats": reps, "launches": ctx.launches - l0}
+    clocks = sampler.stop()
+    flop = 2.0 * M * N * K
+    one = res["fp16_activations_one_pass"]
+    tf = flop / (one["ms_per_step"] * 1e-3) / 1e12
+    line = {"metric": "lmhead_fp16w_tflops_m8192", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": one["steps"], "warmup": args.warmup,
+            "repeats": one["repeats"], "ms_per_step": one["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "fp16 x fp16 -> fp32 (tcgen05 kind::f16), activations rounded from fp32", "data": "synthetic",
+            "config": base_config("lmhead_m8192", M, N, K), "clocks": clocks, "gpu_launches": int(one["launches"]),
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": tf / pk["bf16_tflops"],
+                         "traffic": None, "kernel": "k_gemm_f16w_tc", "peak_note": f"{pk['source']} dense bf16 burst figure"},
+            "fp32_grade_two_passes": {"ms_per_step": res["fp32_grade_two_passes"]["ms_per_step"],
+                                      "TFLOPS_nominal": flop / (res["fp32_grade_two_passes"]["ms_per_step"] * 1e-3) / 1e12,
+                                      "note": "inkq_f16w_matmul's default: the activations enter as fp16 hi + lo, two passes over the weights"},
+            "e2e": None, "cpu_baseline": None}
+    print(json.dumps(line), flush=True)
+    wh.close()
+
+
+# --------------------------------------------------------------------------- small fixed cases for profiler captures
+def run_case(args):
+    import torch
+    pkg = load_package()
+    what, nums = args.case[0], [int(a) for a in args.case[1:]]
+    torch.cuda.set_device(0)
+    ctx = pkg.Context(0, torch.cuda.current_stream().cuda_stream)
+    if what == "qgemm":
+        M, N, K = (nums + [M_PP])[0], N_PP, K_PP
+        w = pkg.synth.weights(N, K)
+        wh = ctx.weight(pkg.A81W41, pkg.SCALES_F32, w["nib"], w["d"], w["m"])
+        x = torch.from_numpy(pkg.synth.activations(M, K)).cuda()
+        C = torch.empty((M, N), device="cuda")
+        act = ctx.act(M, K)
+        for _ in range(3):
+            ctx.quantize(act, x, M, pkg.Q8_1_F32)
+            ctx.gemm(act, wh, C, N)
+        ctx.synchronize()
+        print("qgemm ok", M, N, K, float(C.abs().mean()))
+    elif what == "qgemv":
+        N, K = (nums + [12288, 4096])[:2]
+        w = pkg.synth.weights(N, K)
+        whs = [ctx.weight(pkg.A81W41, pkg.SCALES_F16, w["nib"], w["d"], w["m"]) for _ in range(12)]   # distinct sets: > L2 in total
+        x = torch.from_numpy(pkg.synth.activations(1, K)).cuda()
+        C = torch.empty((1, N), device="cuda")
+        act = ctx.act(1, K)
+        ctx.quantize(act, x, 1, pkg.Q8_1_F16)
+        for wh in whs:
+            ctx.gemv(act, wh, C)
+        ctx.synchronize()
+        print("qgemv ok", N, K, float(C.abs().mean()))
+    elif what == "quantize":
+        M, K = (nums + [8192])[0], K_PP
+        x = torch.randn((M, K), device="cuda")
+        act = ctx.act(M, K)
+        for _ in range(3):
+            ctx.quantize(act, x, M, pkg.Q8_1_F32)
+        ctx.synchronize()
+        print("quantize ok", M, K)
+    elif what == "model":
+        layers = (nums + [2])[0]
+        cfg = pkg.qwen3_forward.Qwen3Config(layers=layers, max_pos=512)
+        model = pkg.qwen3_forward.Qwen3Synthetic(pkg, ctx, cfg, seed=7)
+        prompt = torch.from_numpy(pkg.synth.tokens(322, cfg.vocab)).cuda()
+        model.reset()
+        model.prefill(prompt)
+        for _ in range(3):
+            model.decode_step()
+        ctx.synchronize()
+        print("model ok", layers, model.generated_tokens())
+    elif what == "w41":
+        M, N, K = (nums + [2048])[0], N_PP, K_PP
+        w = pkg.synth.weights(N, K)
+        wh = ctx.weight(pkg.W41, pkg.SCALES_F16, w["nib"], w["d"], w["m"])
+        a16 = torch.from_numpy(pkg.synth.activations(M, K)).cuda().half()
+        C = torch.empty((M, N), device="cuda")
+        for _ in range(3):
+            ctx.gemm_w41_f16act(a16, M, wh, C, N)
+        ctx.synchronize()
+        print("w41 ok", M, N, K, float(C.abs().mean()))
+    elif what == "lmhead":
+        M, N, K = (nums + [2048])[0], 32768, K_PP            # a slice of the vocabulary: > L2, a few hundred MB on the device
+        w16 = (torch.randn((N, K), device="cuda") * 0.02).half()
+        wh = ctx.f16w_dev(w16, N, K)
+        x = torch.randn((M, K), device="cuda")
+        C = torch.empty((M, N), device="cuda")
+        for _ in range(3):
+            ctx.f16w_matmul_prec(wh, x, M, C, N, 1)
+        ctx.synchronize()
+        print("lmhead ok", M, N, K, float(C.abs().mean()))
+    else:
+        raise SystemExit("unknown case " + what)
+
+
 # --------------------------------------------------------------------------- our arm
 def run_ours(args, rank, world, local_rank):
     import torch
@@ -390,6 +729,10 @@ def run_ours(args, rank, world, local_rank):
     ctx = pkg.Context(local_rank, torch.cuda.current_stream().cuda_stream)
 
     wl = args.workload
+    if wl == "lmhead_m8192":
+        if world > 1:
+            raise SystemExit("the lm_head workload is a one-GPU line; its sharded form is part of `scaling_m8192` of the N > 1 headline run")
+        return run_lmhead(args, pkg, torch, ctx, pk, local_rank)
     M = {"qgemm_pp322": M_PP, "qgemm_m2048": 2048, "qgemm_m8192": 8192, "qgemv_sweep": M_PP}[wl]
     K, N = K_PP, N_PP
     n0, n1 = pkg.tp.shard_range(N, world, rank)
@@ -402,7 +745,7 @@ def run_ours(args, rank, world, local_rank):
     sets = int(max(3, min(16, 1.5 * L2_BYTES // w_bytes_one + 2)))
     ws = [ctx.weight(pkg.A81W41, pkg.SCALES_F32, wt["nib"], wt["d"], wt["m"], None, n0, n1) for _ in range(sets)]
     xs = [torch.from_numpy(x_host).cuda() for _ in range(sets)]
-    scatter, exchange = None, "single GPU"
+    scatter, exchange, tp_equal = None, "single GPU", None
     if world > 1:
         cg = pkg.tp.ColumnGather(dist, M, N, world, rank, "cuda", torch.float32)   # in-place all-gather target
         Cs = [cg.local]
@@ -424,79 +767,140 @@ def run_ours(args, rank, world, local_rank):
         scatter.barrier()
 
     step = step_scatter if scatter is not None else step_gather
+    if scatter is not None:
+        tp_equal = tp_check(pkg, torch, dist, ctx, scatter, ws[0], wt, xs[0], M, N, rank)
 
-    # clocks are sampled from the warm-up on: the timed region itself lasts only a few milliseconds, less than the
-    # sampling period of nvidia-smi, and the warm-up steps put the same load on the GPU
     sampler = ClockSampler(local_rank)
-    sampler.start()
     for i in range(args.warmup):
         step(i)
     torch.cuda.synchronize()
-    graph = None
-    if scatter is not None:
-        # A sharded step is short (tens of microseconds of GPU work) and one Python process per GPU cannot enqueue
-        # its three launches that fast: the K timed steps are captured once as a CUDA graph and replayed.  The
-        # barrier kernel keeps its count in device memory, so a replay is a valid sequence of K more barriers.
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.stream(side):
-            ctx.set_stream(side.cuda_stream)
-            with torch.cuda.graph(graph, stream=side):
-                for i in range(args.steps):
-                    step(i)
-        ctx.set_stream(torch.cuda.current_stream().cuda_stream)
-        torch.cuda.current_stream().wait_stream(side)
-        graph.replay()                       # untimed: every rank runs the same K steps
-        torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    l0 = ctx.launches
+    # a sharded step is replayed from a CUDA graph of the K steps; the barrier kernel keeps its count in device memory,
+    # so a replay is a valid sequence of K more barriers
+    graph = capture_steps(torch, ctx, step, args.steps) if scatter is not None else None
+    run_k = (lambda: graph.replay()) if graph is not None else (lambda: [step(i) for i in range(args.steps)])
+    run_k()                                  # untimed: every rank runs the same K steps
     torch.cuda.synchronize()
-    if graph is not None:
-        ms = cuda_time_ms(torch, lambda i: graph.replay(), 1)
-        launches = 3 * args.steps            # quantizer, QGEMM, barrier kernel per step, replayed from the graph
-    else:
-        ms = cuda_time_ms(torch, step, args.steps)
-        launches = ctx.launches - l0
     if world > 1:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
         dist.barrier()
-    ctx.synchronize()
+    est = cuda_time_ms(torch, lambda i: run_k(), 1)
+    l0 = ctx.launches
+    sampler.start()                          # clocks are sampled over the timed region
+    ms, repeats = timed_region(torch, dist, world, run_k, est, args.min_seconds)
     clocks = sampler.stop()
+    launches = (3 * args.steps * repeats) if graph is not None else (ctx.launches - l0)   # quantizer, QGEMM (+ barrier kernel) per step
+    ctx.synchronize()
     ops = 2.0 * M * N * K
-    tops = ops * args.steps / (ms * 1e-3) / 1e12
-    gather_tops = None
-    if scatter is not None:          # the library-collective variant of the same step, for comparison
+    n_steps = args.steps * repeats
+    tops = ops * n_steps / (ms * 1e-3) / 1e12
+
+    gather_cmp = None
+    if scatter is not None:          # the library-collective variant of the same step, timed the same way
         for i in range(args.warmup):
             step_gather(i)
         torch.cuda.synchronize()
         dist.barrier()
-        ms2 = cuda_time_ms(torch, step_gather, args.steps)
-        t = torch.tensor([ms2], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        gather_tops = ops * args.steps / (float(t.item()) * 1e-3) / 1e12
+        g2 = capture_steps(torch, ctx, step_gather, args.steps)
+        run2 = (lambda: g2.replay()) if g2 is not None else (lambda: [step_gather(i) for i in range(args.steps)])
+        run2()
+        torch.cuda.synchronize()
         dist.barrier()
+        est2 = cuda_time_ms(torch, lambda i: run2(), 1)
+        ms2, rep2 = timed_region(torch, dist, world, run2, est2, min(args.min_seconds, 0.3))
+        gather_cmp = {"TOPS": ops * args.steps * rep2 / (ms2 * 1e-3) / 1e12, "timing": "graph" if g2 is not None else "eager"}
         ctx.synchronize()
 
     line = {"metric": "qgemm_int8_tops_pp322" if wl in ("qgemm_pp322", "qgemv_sweep") else f"qgemm_int8_tops_{wl.split('_')[1]}",
-            "value": tops, "unit": "TOPS", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "value": tops, "unit": "TOPS", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "repeats": repeats,
+            "timed_region_s": ms * 1e-3, "ms_per_step": ms / n_steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "s8 x u4 -> s32 block dots (tcgen05 kind::i8), fp32 scale/accumulate", "data": "synthetic",
-            "config": {"workload": wl if wl != "qgemv_sweep" else "qgemm_pp322", "M": M, "N": N, "K": K, "scheme": "A81W41",
-                       "weight_scales": "fp32", "parallelism": exchange,
-                       "l2": f"{sets} distinct weight sets ({sets * w_bytes_one / 1e6:.0f} MB per rank) rotated between steps, > 126 MB L2"},
+            "config": base_config(wl if wl != "qgemv_sweep" else "qgemm_pp322", M, N, K),
+            "run": {"parallelism": exchange, "timing": "CUDA graph of the K steps, replayed" if graph is not None else "eager launches",
+                    "l2": f"{sets} distinct weight sets ({sets * w_bytes_one / 1e6:.0f} MB per rank) rotated between steps, > 126 MB L2"},
             "clocks": clocks, "gpu_launches": int(launches)}
-    if gather_tops is not None:
-        line["config"]["same_step_with_nccl_all_gather_tops"] = gather_tops
+    if clocks.get("sm_mhz"):
+        line["clocks"]["ms_per_step_x_sm_mhz"] = ms / n_steps * clocks["sm_mhz"]
+    if tp_equal is not None:
+        line["tp_equals_1gpu"] = tp_equal
+    if gather_cmp is not None:
+        line["run"]["same_step_with_nccl_all_gather"] = gather_cmp
+
+    # ---- end to end through host buffers, every N: pinned host activations in, the [M][N] result out to the host
+    it = max(10, args.steps)
+    if world == 1:
+        xh = torch.from_numpy(x_host).pin_memory()
+        ch = torch.empty((M, N), dtype=torch.float32).pin_memory()
+        for i in range(3):
+            ctx.linear_host(ws[i % sets], xh, M, ch, N)
+        t0 = time.perf_counter()
+        for i in range(it):
+            ctx.linear_host(ws[i % sets], xh, M, ch, N)
+        dt = (time.perf_counter() - t0) / it
+        e2e = {"value": ops / dt / 1e12, "unit": "TOPS", "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * 4, "ms_per_step": dt * 1e3,
+               "path": "inkq_linear_host (four launches over quarters of the weight tiles, finished columns copied back meanwhile)"}
+    elif scatter is not None:
+        xh = torch.from_numpy(x_host).pin_memory()
+        ch = torch.empty((M, N), dtype=torch.float32).pin_memory() if rank == 0 else None
+
+        def e2e_step(i):
+            xs[i % sets].copy_(xh, non_blocking=True)                   # every rank uploads the activations
+            step_scatter(i)
+            if rank == 0:
+                ch.copy_(scatter.result(i % 2), non_blocking=True)      # rank 0 delivers the assembled result to the host
+        for i in range(3):
+            e2e_step(i)
+        torch.cuda.synchronize()
+        dist.barrier()
+        ms_e = cuda_time_ms(torch, e2e_step, it)
+        t = torch.tensor([ms_e], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item()) * 1e-3 / it
+        e2e = {"value": ops / dt / 1e12, "unit": "TOPS", "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * 4, "ms_per_step": dt * 1e3,
+               "path": "pinned host activations to every rank, sharded step, rank 0 copies the [M][N] result to pinned host memory"}
+        dist.barrier()
+    else:
+        e2e = None
+    line["e2e"] = e2e
+
+    scal = None
+    if world > 1 and scatter is not None and args.scaling:
+        for h in ws:
+            h.close()
+        ws = []
+        scatter.close()
+        scatter = None
+        del cg, Cs
+        torch.cuda.empty_cache()
+        try:
+            scal = scaling_m8192(pkg, torch, dist, ctx, world, rank, pk)
+        except Exception as e:
+            scal = {"error": repr(e)[:300]}
+    elif world == 1 and args.scaling and wl == "qgemm_pp322":
+        try:
+            scal = scaling_m8192(pkg, torch, None, ctx, 1, 0, pk)
+        except Exception as e:
+            scal = {"error": repr(e)[:300]}
+    if scal is not None:
+        line["scaling_m8192"] = scal
+    if world > 1 and args.model:
+        if scatter is not None:
+            scatter.close()
+            scatter = None
+        for h in ws:
+            h.close()
+        ws = []
+        torch.cuda.empty_cache()
+        try:
+            line["model"] = model_tp(pkg, torch, dist, ctx, world, rank)
+        except Exception as e:
+            line["model"] = {"error": repr(e)[:300]}
 
     if rank == 0:
         # ---- kernel-only figures for the roofline (dominant kernel: the tensor-core QGEMM) ----
+        if not ws:
+            ws = [ctx.weight(pkg.A81W41, pkg.SCALES_F32, wt["nib"], wt["d"], wt["m"], None, n0, n1) for _ in range(sets)]
         act = ctx.act(M, K)
         ctx.quantize(act, xs[0], M, pkg.Q8_1_F32)
-        Ck = Cs[0]
+        Ck = torch.empty((M, n_loc), device="cuda")
         for i in range(3):
             ctx.gemm(act, ws[i % sets], Ck, n_loc)
         torch.cuda.synchronize()
@@ -505,44 +909,29 @@ def run_ours(args, rank, world, local_rank):
         ms_q = cuda_time_ms(torch, lambda i: ctx.quantize(act, xs[i % sets], M, pkg.Q8_1_F32), it) / it
         ach = 2.0 * M * n_loc * K / (ms_g * 1e-3) / 1e12
         int8_peak = 2.0 * pk["bf16_tflops"]
+        full_shape = wl in ("qgemm_pp322", "qgemv_sweep") and world == 1
         line["roofline"] = {"bound": "tensor", "achieved": ach, "peak": int8_peak, "unit": "TOP/s", "frac": ach / int8_peak,
-                            "traffic": 41.12e6 if (wl in ("qgemm_pp322", "qgemv_sweep") and world == 1) else None,
-                            "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one launch at this shape (ncu capture summarised under "
-                                            "profiles/): 41.01 MB read = the compulsory operand bytes, 0.11 MB written (the 15.8 MB result stays in L2)",
+                            "traffic": 41.12e6 if full_shape else None,
+                            "traffic_source": "profiles/qgemm_tc_pp322.md: dram__bytes_read.sum + dram__bytes_write.sum of one launch at this shape "
+                                              "(not measured by this run)" if full_shape else None,
                             "kernel": "k_qgemm_tc", "us_per_launch": ms_g * 1e3,
                             "peak_note": f"2 x the {pk['source']} dense bf16 figure ({pk['bf16_tflops']} TFLOP/s); int8 itself is not in MEASURED_PEAKS.json",
                             "cuda_core_note": "every K=32 MMA is followed by an fp32 scale+accumulate of its whole tile on the CUDA cores "
                                               "(M*N*K/32 block dots per launch); that, not the tensor pipe, bounds this kernel"}
-        # the second roof of this kernel: the per-block fp32 epilogue on the CUDA cores.  Per block dot and lane the exact
-        # arithmetic needs one int->float conversion, half a packed multiply (d_a*d_w), one packed fma pair (main and min
-        # terms) and half a shared load: 3 issue slots per warp-level block dot.
+        # the second roof of this kernel: the per-block fp32 epilogue on the CUDA cores.  The exact operation order needs, per
+        # block dot, three fp32 operations on the FMA pipe (scale product, main term, min term); the packed f32x2 forms occupy
+        # the pipe for two cycles, so the floor is 3 FMA-pipe lane-cycles per block dot at 128 lanes per SM.
         tiles_m = -(-M // 128)
         bm = -(-(-(-M // tiles_m)) // 16) * 16
         dots = float(tiles_m * bm) * n_loc * (K // 32)
         sm_clock = (clocks.get("sm_mhz") or 1965.0) * 1e6
         n_sms = torch.cuda.get_device_properties(local_rank).multi_processor_count
-        t_min = dots * 3.0 / 32.0 / (n_sms * 4) / sm_clock
-        line["roofline"]["cuda_core_roof"] = {"block_dots_per_launch": dots, "issue_slots_per_warp_block_dot": 3.0,
+        t_min = dots * 3.0 / 128.0 / n_sms / sm_clock
+        line["roofline"]["cuda_core_roof"] = {"block_dots_per_launch": dots, "fma_pipe_ops_per_block_dot": 3.0,
                                               "min_us": t_min * 1e6, "frac": t_min / (ms_g * 1e-3)}
         line["quantizer"] = {"us_per_launch": ms_q * 1e3, "GBs": M * K * 5.375 / (ms_q * 1e-3) / 1e9, "frac_of_hbm": M * K * 5.375 / (ms_q * 1e-3) / 1e9 / pk["hbm_gbs"]}
         act.close()
 
-        # ---- end to end through the host-buffer entry point ----
-        if world == 1:
-            xh = torch.from_numpy(x_host).pin_memory()
-            ch = torch.empty((M, N), dtype=torch.float32).pin_memory()
-            for i in range(3):
-                ctx.linear_host(ws[i % sets], xh, M, ch, N)
-            it = max(10, args.steps)
-            t0 = time.perf_counter()
-            for i in range(it):
-                ctx.linear_host(ws[i % sets], xh, M, ch, N)
-            dt = (time.perf_counter() - t0) / it
-            line["e2e"] = {"value": ops / dt / 1e12, "unit": "TOPS", "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * 4,
-                           "ms_per_step": dt * 1e3}
-        else:
-            line["e2e"] = {"value": None, "unit": "TOPS", "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * 4,
-                           "note": "measured at N=1 only"}
         if world == 1 and wl in ("qgemm_pp322", "qgemv_sweep"):
             line["cpu_baseline"] = cpu_baseline_pp322(pkg, x_host, wt)
         if world == 1 and (wl == "qgemv_sweep" or args.gemv):
@@ -555,6 +944,7 @@ def run_ours(args, rank, world, local_rank):
         if world == 1 and args.model:
             try:
                 line["model"] = model_pp_tg(pkg, torch, ctx)
+                line["model"]["same_operators_as_the_sharded_runs"] = model_tp(pkg, torch, None, ctx, 1, 0)
             except Exception as e:   # the headline metric above stands on its own
                 line["model"] = {"error": repr(e)[:300]}
         print(json.dumps(line), flush=True)
@@ -571,10 +961,15 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="qgemm_pp322", choices=["qgemm_pp322", "qgemv_sweep", "qgemm_m2048", "qgemm_m8192"])
+    ap.add_argument("--workload", default="qgemm_pp322", choices=["qgemm_pp322", "qgemv_sweep", "qgemm_m2048", "qgemm_m8192", "lmhead_m8192"])
+    ap.add_argument("--min-seconds", type=float, default=1.0, help="repeat the K timed steps until the timed region lasts this long")
     ap.add_argument("--no-gemv", dest="gemv", action="store_false", help="skip the decode QGEMV sweep figures")
     ap.add_argument("--no-model", dest="model", action="store_false", help="skip the synthetic Qwen3-8B pp322/tg128 figures")
+    ap.add_argument("--no-scaling", dest="scaling", action="store_false", help="skip the M=8192 QGEMM / lm_head figures of the scaling configuration")
+    ap.add_argument("--case", nargs="+", default=None, help="run one small fixed case for a profiler capture and exit")
     args = ap.parse_args()
+    if args.case:
+        return run_case(args)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

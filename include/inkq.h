@@ -198,6 +198,9 @@ int inkq_peerset_from_pointers(inkq_ctx *ctx, int world, int rank, void *const *
 int inkq_peerset_destroy(inkq_peerset *ps);
 int inkq_linear_scatter(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, int M, inkq_peerset *ps, size_t byte_offset, int ldc);
 int inkq_peer_barrier(inkq_ctx *ctx, inkq_peerset *ps, int timeout_ms);
+/* inkq_f16w_matmul_prec of a row shard of the fp16 matrix (inkq_f16w_create with [n_begin, n_end)), the output columns
+ * stored into every rank's buffer like inkq_linear_scatter (lm_head of QwenForCausalLM.cc:43-46, column-sharded). */
+int inkq_f16w_matmul_scatter(inkq_ctx *ctx, const inkq_f16w *w, const float *x_dev, int M, inkq_peerset *ps, size_t byte_offset, int ldc, int precision);
 
 /* ---- weight-only W41 (fp16 activations) and fp16 lm_head ---------------------
  * No C++ kernel exists in the reference for these two; they follow
@@ -209,7 +212,14 @@ int inkq_gemm_w41_f16act_simt(inkq_ctx *ctx, const uint16_t *a16_dev, int M, con
 int inkq_f16w_create(inkq_ctx *ctx, int N, int K, const uint16_t *w16_host, int n_begin, int n_end, inkq_f16w **out);
 int inkq_f16w_create_dev(inkq_ctx *ctx, int N, int K, const uint16_t *w16_dev, int n_begin, int n_end, inkq_f16w **out);
 int inkq_f16w_destroy(inkq_f16w *w);
+/* C[m][n] = sum_k x[m][k] * w[n][k].  M < 16: bandwidth-bound CUDA-core kernel, fp32 activations, exact products.
+ * M >= 16 (and K % 64 == 0): tensor cores; the fp32 activations enter as fp16 hi + lo parts (22 significant bits, the
+ * K loop runs over both; result within ~1e-5 of the output's rms of an fp32 evaluation) or, with INKQ_F16W_ACT_FP16,
+ * as one fp16 value (half the work; each activation rounded with relative error <= 2^-11, about 1e-3 of the
+ * output's rms).  inkq_f16w_matmul = INKQ_F16W_ACT_FP32. */
+typedef enum { INKQ_F16W_ACT_FP32 = 0, INKQ_F16W_ACT_FP16 = 1 } inkq_f16w_precision;
 int inkq_f16w_matmul(inkq_ctx *ctx, const inkq_f16w *w, const float *x_dev, int M, float *C_dev, int ldc);
+int inkq_f16w_matmul_prec(inkq_ctx *ctx, const inkq_f16w *w, const float *x_dev, int M, float *C_dev, int ldc, int precision);
 
 #ifdef __cplusplus
 }

@@ -34,9 +34,9 @@ SYMBOLS = [
     "inkq_launch_count", "inkq_weight_create", "inkq_weight_create_dev", "inkq_weight_destroy", "inkq_weight_info",
     "inkq_weight_export", "inkq_act_create", "inkq_act_destroy", "inkq_quantize", "inkq_act_export", "inkq_act_import", "inkq_quantize_host", "inkq_gemm_host", "inkq_gemv_host", "inkq_gemm",
     "inkq_gemv", "inkq_gemm_simt", "inkq_debug_block_dots", "inkq_debug_block_dots_tc", "inkq_linear",
-    "inkq_linear_host", "inkq_linear_m1_static", "inkq_gemm_w41_f16act", "inkq_gemm_w41_f16act_simt", "inkq_f16w_create", "inkq_f16w_create_dev", "inkq_f16w_destroy",
+    "inkq_linear_host", "inkq_linear_m1_static", "inkq_gemm_w41_f16act", "inkq_gemm_w41_f16act_simt", "inkq_f16w_create", "inkq_f16w_create_dev", "inkq_f16w_destroy", "inkq_f16w_matmul_prec",
     "inkq_f16w_matmul", "inkq_peer_export", "inkq_peerset_open", "inkq_peerset_from_pointers", "inkq_peerset_destroy",
-    "inkq_linear_scatter", "inkq_peer_barrier", "inkq_weight_quantize_dev",
+    "inkq_linear_scatter", "inkq_peer_barrier", "inkq_f16w_matmul_scatter", "inkq_weight_quantize_dev",
 ]
 
 
@@ -256,6 +256,9 @@ class Context:
         """inkq_linear whose epilogue stores the shard's columns into every rank's buffer of the peer set."""
         self.check(self.L.inkq_linear_scatter(self.h, w.h, _dp(x), M, ps.h, C.c_size_t(byte_offset), ldc))
 
+    def f16w_matmul_scatter(self, w, x, M: int, ps, byte_offset: int, ldc: int, precision: int = 0):
+        self.check(self.L.inkq_f16w_matmul_scatter(self.h, w.h, _dp(x), M, ps.h, C.c_size_t(byte_offset), ldc, precision))
+
     def peer_barrier(self, ps, timeout_ms: int = 2000):
         self.check(self.L.inkq_peer_barrier(self.h, ps.h, timeout_ms))
 
@@ -269,6 +272,10 @@ class Context:
     def gemm_w41_f16act_simt(self, a16, M: int, w, Cdev, ldc: int):
         """CUDA-core cross-check of gemm_w41_f16act (slow)."""
         self.check(self.L.inkq_gemm_w41_f16act_simt(self.h, _dp(a16), M, w.h, _dp(Cdev), ldc))
+
+    def f16w_matmul_prec(self, w, x, M: int, Cdev, ldc: int, precision: int):
+        """precision 0: fp32-grade activations (fp16 hi + lo, two passes), 1: activations rounded to fp16 (one pass)."""
+        self.check(self.L.inkq_f16w_matmul_prec(self.h, w.h, _dp(x), M, _dp(Cdev), ldc, precision))
 
     def f16w_matmul(self, w, x, M: int, Cdev, ldc: int):
         self.check(self.L.inkq_f16w_matmul(self.h, w.h, _dp(x), M, _dp(Cdev), ldc))

@@ -22,7 +22,7 @@ namespace inkq {
 
 template <int MT>
 __global__ void __launch_bounds__(256) k_f16w_gemv(const uint16_t *__restrict__ w, const float *__restrict__ x, int m0, int M, int rows, int K,
-                                                   float *__restrict__ C, int ldc)
+                                                   float *__restrict__ C, int ldc, const ExtraDst extra)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float *xs = reinterpret_cast<float *>(smem_raw);  // [MT][K]
@@ -81,25 +81,33 @@ __global__ void __launch_bounds__(256) k_f16w_gemv(const uint16_t *__restrict__ 
             float v = acc[j];
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
-            if (lane == 0 && j < mt) C[static_cast<size_t>(m0 + j) * ldc + n] = v;
+            if (lane == 0 && j < mt) {
+                const size_t off = static_cast<size_t>(m0 + j) * ldc + n;
+                C[off] = v;
+#pragma unroll
+                for (int e = 0; e < MAX_PEERS - 1; e++)   // further destinations (peers of a row-sharded matrix)
+                    if (e < extra.n) extra.p[e][off] = v;
+            }
         }
     }
 }
 
-int launch_f16w_matmul(inkq_ctx *ctx, const F16W *w, const float *x, int M, float *C, int ldc)
+int launch_f16w_matmul(inkq_ctx *ctx, const F16W *w, const float *x, int M, float *C, int ldc, const ExtraDst *extra_in)
 {
+    ExtraDst extra = {};
+    if (extra_in != nullptr) extra = *extra_in;
     const int grid = min((w->rows + 7) / 8, ctx->num_sms * 8);
     if (M == 1) {
         const size_t smem = static_cast<size_t>(w->K) * sizeof(float);
         if (smem > 48 * 1024) cudaFuncSetAttribute(k_f16w_gemv<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        k_f16w_gemv<1><<<grid, 256, smem, ctx->stream>>>(w->w, x, 0, M, w->rows, w->K, C, ldc);
+        k_f16w_gemv<1><<<grid, 256, smem, ctx->stream>>>(w->w, x, 0, M, w->rows, w->K, C, ldc, extra);
         return after_launch(ctx, "k_f16w_gemv");
     }
     const size_t smem = 4 * static_cast<size_t>(w->K) * sizeof(float);
     if (smem > 200 * 1024) return fail(ctx, INKQ_ERR_UNSUPPORTED, "K too large for the fp16-weight matmul");
     if (smem > 48 * 1024) cudaFuncSetAttribute(k_f16w_gemv<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     for (int m0 = 0; m0 < M; m0 += 4) {
-        k_f16w_gemv<4><<<grid, 256, smem, ctx->stream>>>(w->w, x, m0, M, w->rows, w->K, C, ldc);
+        k_f16w_gemv<4><<<grid, 256, smem, ctx->stream>>>(w->w, x, m0, M, w->rows, w->K, C, ldc, extra);
         int rc = after_launch(ctx, "k_f16w_gemv");
         if (rc) return rc;
     }

@@ -144,7 +144,11 @@ int inkq_ctx_create(int device, void *stream, inkq_ctx **out)
     ctx->stream = static_cast<cudaStream_t>(stream);
     ctx->launches = 0;
     ctx->scratch_act = nullptr;
+    ctx->scratch_planes = 0;
     ctx->scratch_elems = 0;
+    ctx->f16_x = nullptr;
+    ctx->f16_scale = nullptr;
+    ctx->f16_x_cap = ctx->f16_scale_cap = 0;
     ctx->lin_x = ctx->lin_c = nullptr;
     ctx->lin_x_cap = ctx->lin_c_cap = 0;
     ctx->pin_x = ctx->pin_c = nullptr;
@@ -189,6 +193,8 @@ int inkq_ctx_destroy(inkq_ctx *ctx)
         free_act(ctx->scratch_act);
         delete static_cast<inkq_act *>(ctx->scratch_act);
     }
+    cudaFree(ctx->f16_x);
+    cudaFree(ctx->f16_scale);
     cudaFree(ctx->lin_x);
     cudaFree(ctx->lin_c);
     cudaFree(ctx->dev_flag);
@@ -554,14 +560,16 @@ int inkq_debug_block_dots_tc(inkq_ctx *ctx, const inkq_act *act, const inkq_weig
 static int ensure_scratch_act(inkq_ctx *ctx, int M, int K)
 {
     const size_t need = static_cast<size_t>(M) * K;
+    const size_t need_planes = static_cast<size_t>(K / QK) * ((static_cast<size_t>(M) + 3) & ~static_cast<size_t>(3));   // [K/32][round_up(M, 4)]
     Act *a = ctx->scratch_act;
-    if (a == nullptr || ctx->scratch_elems < need) {
+    if (a == nullptr || ctx->scratch_elems < need || ctx->scratch_planes < need_planes) {
         if (a != nullptr) {
             cudaStreamSynchronize(ctx->stream);
             free_act(a);
             delete static_cast<inkq_act *>(a);
             ctx->scratch_act = nullptr;
             ctx->scratch_elems = 0;
+            ctx->scratch_planes = 0;
         }
         size_t elems = need < (static_cast<size_t>(512) * 12288) ? static_cast<size_t>(512) * 12288 : need;
         inkq_act *na = new (std::nothrow) inkq_act();
@@ -570,7 +578,8 @@ static int ensure_scratch_act(inkq_ctx *ctx, int M, int K)
         na->q = nullptr;
         na->d = na->s = nullptr;
         na->isum = nullptr;
-        const size_t planes = elems / QK + 65536;   // [K/32][round_up(M, 4)] fits for every M*K <= elems with K <= 2^21
+        size_t planes = elems / QK + 65536;   // room for the row padding of every shape with M*K <= elems and K <= 2^19
+        if (planes < need_planes) planes = need_planes;   // longer rows: the exact need of this shape (checked on every call)
         int rc = dev_alloc(ctx, &na->q, elems);
         if (!rc) rc = dev_alloc(ctx, &na->d, planes);
         if (!rc) rc = dev_alloc(ctx, &na->s, planes);
@@ -582,6 +591,7 @@ static int ensure_scratch_act(inkq_ctx *ctx, int M, int K)
         }
         ctx->scratch_act = na;
         ctx->scratch_elems = elems;
+        ctx->scratch_planes = planes;
         a = na;
     }
     a->K = K;
@@ -752,13 +762,48 @@ int inkq_f16w_destroy(inkq_f16w *w)
     return INKQ_OK;
 }
 
-int inkq_f16w_matmul(inkq_ctx *ctx, const inkq_f16w *w, const float *x_dev, int M, float *C_dev, int ldc)
+int inkq_f16w_matmul_prec(inkq_ctx *ctx, const inkq_f16w *w, const float *x_dev, int M, float *C_dev, int ldc, int precision)
+{
+    return inkq::f16w_matmul_impl(ctx, w, x_dev, M, C_dev, ldc, precision, nullptr);
+}
+
+}  // extern "C"
+
+int inkq::f16w_matmul_impl(inkq_ctx *ctx, const inkq_f16w *w, const float *x_dev, int M, float *C_dev, int ldc, int precision, const ExtraDst *extra)
 {
     int rc = use(ctx);
     if (rc) return rc;
     INKQ_REQUIRE(ctx, w != nullptr && x_dev != nullptr && C_dev != nullptr, "null handle, input or output");
     INKQ_REQUIRE(ctx, M >= 1 && ldc >= w->rows, "bad M or ldc");
-    return launch_f16w_matmul(ctx, w, x_dev, M, C_dev, ldc);
+    INKQ_REQUIRE(ctx, precision == INKQ_F16W_ACT_FP32 || precision == INKQ_F16W_ACT_FP16, "unknown precision");
+    // few rows: the weights are streamed once per 4 rows by the CUDA-core kernel (fp32 activations, exact products)
+    const bool aligned = w->rows % 4 == 0 && ldc % 4 == 0 && (reinterpret_cast<uintptr_t>(C_dev) & 15) == 0;
+    if (M < 16 || w->K % 64 != 0 || !aligned) return launch_f16w_matmul(ctx, w, x_dev, M, C_dev, ldc, extra);
+    INKQ_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(x_dev) & 15) == 0, "x must be 16-byte aligned");
+    const int passes = precision == INKQ_F16W_ACT_FP32 ? 2 : 1;
+    const size_t need = static_cast<size_t>(M) * w->K * passes;
+    if (ctx->f16_x_cap < need) {
+        INKQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // earlier launches may still read the old buffer
+        cudaFree(ctx->f16_x);
+        ctx->f16_x_cap = 0;
+        if ((rc = dev_alloc(ctx, &ctx->f16_x, need))) return rc;
+        ctx->f16_x_cap = need;
+    }
+    if (ctx->f16_scale_cap < static_cast<size_t>(M)) {
+        INKQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        cudaFree(ctx->f16_scale);
+        ctx->f16_scale_cap = 0;
+        if ((rc = dev_alloc(ctx, &ctx->f16_scale, static_cast<size_t>(M)))) return rc;
+        ctx->f16_scale_cap = static_cast<size_t>(M);
+    }
+    return launch_f16w_gemm_tc(ctx, w, x_dev, M, C_dev, ldc, passes, ctx->f16_x, ctx->f16_scale, extra);
+}
+
+extern "C" {
+
+int inkq_f16w_matmul(inkq_ctx *ctx, const inkq_f16w *w, const float *x_dev, int M, float *C_dev, int ldc)
+{
+    return inkq_f16w_matmul_prec(ctx, w, x_dev, M, C_dev, ldc, INKQ_F16W_ACT_FP32);
 }
 
 }  // extern "C"

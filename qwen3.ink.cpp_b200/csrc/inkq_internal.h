@@ -95,10 +95,15 @@ struct inkq_ctx {
     int *dev_flag;        // device word set by a kernel whose bounded wait ran out
     inkq::Act *scratch_act;  // activation scratch of inkq_linear (grown on demand)
     size_t scratch_elems;    // its capacity in activation elements (M * K)
+    size_t scratch_planes;   // capacity of each of its per-block planes, in entries
     float *lin_x, *lin_c;    // device staging of inkq_linear_host
     size_t lin_x_cap, lin_c_cap;
     float *pin_x, *pin_c;    // pinned host staging of inkq_linear_host
     size_t pin_x_cap, pin_c_cap;
+    uint16_t *f16_x;         // fp16 (hi, lo) form of the activations of inkq_f16w_matmul's tensor-core path (grown on demand)
+    size_t f16_x_cap;        // in halves
+    float *f16_scale;        // its per-row power-of-two factors
+    size_t f16_scale_cap;
     void *encode_tiled;      // cuTensorMapEncodeTiled entry point
     cudaStream_t copy_stream;   // inkq_linear_host: device-to-host copies of finished column chunks (created on first use)
     cudaEvent_t chunk_ev[4];
@@ -165,6 +170,11 @@ int launch_gemm_w41_tc(inkq_ctx *ctx, const uint16_t *a16, int M, const Weight *
 int launch_gemv_w41(inkq_ctx *ctx, const uint16_t *a16, const Weight *w, float *C);                        // M == 1, bandwidth-bound
 // inkq_linear with further destinations for every output element (defined in inkq_api.cu)
 int linear_impl(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, int M, float *C_dev, int ldc, const ExtraDst *extra);
-int launch_f16w_matmul(inkq_ctx *ctx, const F16W *w, const float *x, int M, float *C, int ldc);
+int launch_f16w_matmul(inkq_ctx *ctx, const F16W *w, const float *x, int M, float *C, int ldc, const ExtraDst *extra = nullptr);   // CUDA cores (bandwidth-bound, M small)
+// inkq_f16w_matmul_prec with further destinations for every output element (defined in inkq_api.cu)
+int f16w_matmul_impl(inkq_ctx *ctx, const inkq_f16w *w, const float *x_dev, int M, float *C_dev, int ldc, int precision, const ExtraDst *extra);
+// tensor cores, M >= 16; passes 2: activations as fp16 hi + lo (22 significant bits), 1: hi only
+int launch_f16w_gemm_tc(inkq_ctx *ctx, const F16W *w, const float *x, int M, float *C, int ldc, int passes, uint16_t *x16, float *row_scale,
+                        const ExtraDst *extra = nullptr);
 
 }  // namespace inkq

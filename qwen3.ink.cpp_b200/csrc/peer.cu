@@ -226,6 +226,22 @@ int inkq_linear_scatter(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev,
     return linear_impl(ctx, w, x_dev, M, reinterpret_cast<float *>(ps->ptr[ps->rank] + byte_offset), ldc, &extra);
 }
 
+int inkq_f16w_matmul_scatter(inkq_ctx *ctx, const inkq_f16w *w, const float *x_dev, int M, inkq_peerset *ps, size_t byte_offset, int ldc, int precision)
+{
+    if (ctx == nullptr) return fail(nullptr, INKQ_ERR_INVALID, "null context");
+    int rc = check_set(ctx, ps);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, w != nullptr && M >= 1, "null weight handle or M < 1");
+    INKQ_REQUIRE(ctx, byte_offset >= INKQ_PEER_RESERVED_BYTES && byte_offset % 4 == 0, "the offset must be a multiple of 4 past the reserved head");
+    INKQ_REQUIRE(ctx, ldc >= w->rows, "ldc is smaller than the number of weight rows");
+    const size_t last = byte_offset + (static_cast<size_t>(M - 1) * ldc + w->rows) * sizeof(float);
+    INKQ_REQUIRE(ctx, last <= ps->bytes, "the output does not fit into the peer buffers");
+    ExtraDst extra = {};
+    for (int p = 0; p < ps->world; p++)
+        if (p != ps->rank) extra.p[extra.n++] = reinterpret_cast<float *>(ps->ptr[p] + byte_offset);
+    return f16w_matmul_impl(ctx, w, x_dev, M, reinterpret_cast<float *>(ps->ptr[ps->rank] + byte_offset), ldc, precision, &extra);
+}
+
 int inkq_peer_barrier(inkq_ctx *ctx, inkq_peerset *ps, int timeout_ms)
 {
     if (ctx == nullptr) return fail(nullptr, INKQ_ERR_INVALID, "null context");

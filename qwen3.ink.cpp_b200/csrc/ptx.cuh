@@ -67,6 +67,19 @@ __device__ __forceinline__ bool mbar_wait_abortable(volatile int *abort, uint64_
         if ((spin & 63u) == 0u && (*abort != 0 || clock64() - t0 > INKQ_SPIN_LIMIT_CYCLES)) return false;
     }
 }
+// Wait used when a kernel leaves after a failed wait: its own asynchronous copies may still be in flight and must
+// land before the CTA's shared memory is given up.  Ignores any abort word; bounded by `limit_cycles` (copies complete
+// within microseconds; the default is about a millisecond).
+__device__ __forceinline__ bool mbar_wait_drain(uint64_t *bar, uint32_t parity, long long limit_cycles = 2000000LL)
+{
+    const long long t0 = clock64();
+#pragma unroll 1
+    for (;;) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(200u);
+        if (clock64() - t0 > limit_cycles) return false;
+    }
+}
 // ---- fences -------------------------------------------------------------------
 // Make generic-proxy shared-memory writes visible to the async proxy (UMMA / TMA reads).
 __device__ __forceinline__ void fence_proxy_async_smem()

@@ -290,8 +290,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             }
             if (*abort_flag != 0) {
                 // copies of stages nobody consumed may still be in flight: wait (bounded) for each stage's last fill
-                for (int s = 0; s < RAW_STAGES; s++)
-                    tc_wait(&raw_full[s], static_cast<uint32_t>(s) < raw.idx ? raw.phase : raw.phase ^ 1, abort_flag, prm.flag, 100u);
+                for (int s = 0; s < RAW_STAGES; s++) mbar_wait_drain(&raw_full[s], static_cast<uint32_t>(s) < raw.idx ? raw.phase : raw.phase ^ 1);
             }
         }
         __syncwarp();
@@ -317,8 +316,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 }
             }
             if (*abort_flag != 0) {
-                for (int s = 0; s < SC_STAGES; s++)
-                    tc_wait(&sc_full[s], static_cast<uint32_t>(s) < sc.idx ? sc.phase : sc.phase ^ 1, abort_flag, prm.flag, 100u);
+                for (int s = 0; s < SC_STAGES; s++) mbar_wait_drain(&sc_full[s], static_cast<uint32_t>(s) < sc.idx ? sc.phase : sc.phase ^ 1);
             }
         }
         __syncwarp();
@@ -363,7 +361,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             }
             // every MMA issued above has completed before tensor memory is released
             umma_commit(drain_bar);
-            tc_wait(drain_bar, 0u, abort_flag, prm.flag, 100u);
+            mbar_wait_drain(drain_bar, 0u);
         }
         __syncwarp();
     } else if (warp >= 4 && warp < 8) {

@@ -272,7 +272,8 @@ int inkq_glue_decode_gemv(inkq_ctx *ctx, const inkq_weight *w, const inkq_act *i
         INKQ_REQUIRE(ctx, out != nullptr, "this epilogue writes a quantized row: out is required");
         INKQ_REQUIRE(ctx, out_qmode == INKQ_Q8_1_F16 || out_qmode == INKQ_Q8_0_F16 || out_qmode == INKQ_Q8_1_F32, "bad output quantization mode");
         const int out_K = (epilogue == EPI_PAIR_SILUQ) ? w->rows / 2 : w->rows;
-        INKQ_REQUIRE(ctx, w->rows % (epilogue == EPI_PAIR_SILUQ ? 64 : 32) == 0, "the row count must be a multiple of 32 (64 for gate/up pairs)");
+        // gate/up pairs: one CTA per 64 rows writes output block blockIdx.x, and the grid covers whole 128-row tiles
+        INKQ_REQUIRE(ctx, w->rows % (epilogue == EPI_PAIR_SILUQ ? 128 : 32) == 0, "the row count must be a multiple of 32 (128 for gate/up pairs)");
         INKQ_REQUIRE(ctx, out->K == out_K && out != in, "the output activation handle must have been created for K = the produced row length, and differ from the input");
         epi.out = quant_out_of(out, out_K, out_qmode);
     }

@@ -12,7 +12,11 @@
 // Weights: repack_* writes the reference's superblock layout into the caller's buffer (so a
 // copied buffer still works, the reference deep-copies its layers) and uploads the re-tiled
 // weights once, remembered by buffer address; the matmuls look the buffer up and fall back
-// to rebuilding the upload from the superblocks when the address is unknown.
+// to rebuilding the upload from the superblocks when the address is unknown.  The cache is
+// keyed by address: a buffer that is refilled with other weights must go through repack_*
+// again (or inkq_refshim_forget), and a freed buffer should be forgotten; one lock is held from
+// the look-up to the end of the matmul, so a concurrent re-registration cannot free an entry
+// in use.
 #include <cstdint>
 #include <cstring>
 #include <map>
@@ -68,10 +72,14 @@ float f16_to_f32(fp16_t h)
     return f;
 }
 
+struct Entry {
+    inkq_weight *w;
+    int scale_mode;
+};
 struct Gpu {
     inkq_ctx *ctx = nullptr;
-    std::mutex mu;
-    std::map<const void *, inkq_weight *> weights;   // by B_repack address
+    std::recursive_mutex mu;
+    std::map<const void *, Entry> weights;   // by B_repack address
     inkq_act *act = nullptr;
     int act_rows = 0, act_k = 0;
     Gpu()
@@ -101,7 +109,7 @@ Gpu &gpu()
 void quantize_to_structs(const float *x, void *vy, int64_t k, int qmode)
 {
     Gpu &g = gpu();
-    std::lock_guard<std::mutex> lk(g.mu);
+    std::lock_guard<std::recursive_mutex> lk(g.mu);
     // blocks are independent, so the whole [m*k] vector is quantized as one row of k elements
     const int K = static_cast<int>(k);
     inkq_act *a = g.activation(1, K);
@@ -196,43 +204,41 @@ void read_superblocks(int K, int N, const SB *in, std::vector<uint8_t> &nib, std
 void remember(const void *key, int scheme, int scale_mode, int N, int K, const uint8_t *nib, const float *d, const float *m)
 {
     Gpu &g = gpu();
-    std::lock_guard<std::mutex> lk(g.mu);
+    std::lock_guard<std::recursive_mutex> lk(g.mu);
     auto it = g.weights.find(key);
     if (it != g.weights.end()) {
-        inkq_weight_destroy(it->second);
+        inkq_weight_destroy(it->second.w);
         g.weights.erase(it);
     }
     inkq_weight *w = nullptr;
     g.check(inkq_weight_create(g.ctx, scheme, scale_mode, N, K, nib, d, m, nullptr, 0, N, &w));
-    g.weights[key] = w;
+    g.weights[key] = Entry{w, scale_mode};
 }
 
+// Call with g.mu held (the caller keeps it until the matmul that uses the handle has returned).
 template <typename SB>
 inkq_weight *lookup(const void *B_repack, int scheme, int scale_mode, int N, int K)
 {
     Gpu &g = gpu();
-    {
-        std::lock_guard<std::mutex> lk(g.mu);
-        auto it = g.weights.find(B_repack);
-        if (it != g.weights.end()) {
-            int rows = 0, k = 0, sch = 0;
-            inkq_weight_info(it->second, &rows, &k, &sch, nullptr);
-            if (rows == N && k == K && sch == scheme) return it->second;
-        }
+    auto it = g.weights.find(B_repack);
+    if (it != g.weights.end()) {
+        int rows = 0, k = 0, sch = 0;
+        inkq_weight_info(it->second.w, &rows, &k, &sch, nullptr);
+        if (rows == N && k == K && sch == scheme && it->second.scale_mode == scale_mode) return it->second.w;
     }
     std::vector<uint8_t> nib;
     std::vector<float> d, m;
     read_superblocks(K, N, static_cast<const SB *>(B_repack), nib, d, m);
     remember(B_repack, scheme, scale_mode, N, K, nib.data(), d.data(), scheme == INKQ_A81W41 ? m.data() : nullptr);
-    std::lock_guard<std::mutex> lk(g.mu);
-    return g.weights[B_repack];
+    return g.weights[B_repack].w;
 }
 
-template <typename AS>
-void matmul(int scheme, int qmode, const void *A_repack, inkq_weight *w, float *C, int M, int N, int K, bool gemv)
+template <typename AS, typename SB>
+void matmul(int scheme, int scale_mode, int qmode, const void *A_repack, const void *B_repack, float *C, int M, int N, int K, bool gemv)
 {
     Gpu &g = gpu();
-    std::lock_guard<std::mutex> lk(g.mu);
+    std::lock_guard<std::recursive_mutex> lk(g.mu);
+    inkq_weight *w = lookup<SB>(B_repack, scheme, scale_mode, N, K);
     const int nb = K / 32, npair = K / 64;
     std::vector<int8_t> q(static_cast<size_t>(M) * K);
     std::vector<float> d(static_cast<size_t>(M) * nb), s(static_cast<size_t>(M) * nb, 0.0f);
@@ -288,17 +294,29 @@ void repack_w81_weight_fp32(const int K, const int N, const int /*Q_BLK_SIZE*/, 
 
 void gemm_repack_A81W41_fp32(void *A_repack, void *B_repack, float *C, const int M, const int N, const int K)
 {
-    matmul<q8_1x2_f32>(INKQ_A81W41, INKQ_Q8_1_F32, A_repack, lookup<q4_2x8_f32>(B_repack, INKQ_A81W41, INKQ_SCALES_F32, N, K), C, M, N, K, false);
+    matmul<q8_1x2_f32, q4_2x8_f32>(INKQ_A81W41, INKQ_SCALES_F32, INKQ_Q8_1_F32, A_repack, B_repack, C, M, N, K, false);
 }
 void gemv_repack_A81W41_fp16(void *A_repack, void *B_repack, float *C, const int M, const int N, const int K)
 {
-    matmul<q8_1x2_f16>(INKQ_A81W41, INKQ_Q8_1_F16, A_repack, lookup<q4_2x8_f16>(B_repack, INKQ_A81W41, INKQ_SCALES_F16, N, K), C, M, N, K, true);
+    matmul<q8_1x2_f16, q4_2x8_f16>(INKQ_A81W41, INKQ_SCALES_F16, INKQ_Q8_1_F16, A_repack, B_repack, C, M, N, K, true);
 }
 void gemm_repack_A80W40(void *A_repack, void *B_repack, float *C, const int M, const int N, const int K)
 {
-    matmul<q8_1x2_f16>(INKQ_A80W40, INKQ_Q8_0_F16, A_repack, lookup<q4_2x8_f16>(B_repack, INKQ_A80W40, INKQ_SCALES_F16, N, K), C, M, N, K, false);
+    matmul<q8_1x2_f16, q4_2x8_f16>(INKQ_A80W40, INKQ_SCALES_F16, INKQ_Q8_0_F16, A_repack, B_repack, C, M, N, K, false);
 }
 void gemv_repack_A80W40(void *A_repack, void *B_repack, float *C, const int M, const int N, const int K)
 {
-    matmul<q8_1x2_f16>(INKQ_A80W40, INKQ_Q8_0_F16, A_repack, lookup<q4_2x8_f16>(B_repack, INKQ_A80W40, INKQ_SCALES_F16, N, K), C, M, N, K, true);
+    matmul<q8_1x2_f16, q4_2x8_f16>(INKQ_A80W40, INKQ_SCALES_F16, INKQ_Q8_0_F16, A_repack, B_repack, C, M, N, K, true);
+}
+
+// Drops the device copy remembered for a weight buffer (call before freeing or refilling the buffer outside repack_*).
+void inkq_refshim_forget(const void *B_repack)
+{
+    Gpu &g = gpu();
+    std::lock_guard<std::recursive_mutex> lk(g.mu);
+    auto it = g.weights.find(B_repack);
+    if (it != g.weights.end()) {
+        inkq_weight_destroy(it->second.w);
+        g.weights.erase(it);
+    }
 }

@@ -13,6 +13,14 @@ csrc/glue_ops.cu.  In a decode step (one token) the norms, SiLU*up, the activati
 additions run in the epilogues of the kernels that produce each row (inkq_glue_decode_gemv,
 inkq_glue_attention_quant): 5 launches per layer instead of 17.  One decode step is captured once as a CUDA
 graph and replayed.
+
+Column-sharded form (world > 1, one process per GPU): every linear holds the weight rows [rank*N/P, (rank+1)*N/P) of the
+same seeded matrix, its epilogue stores the shard's output columns into every rank's copy of the output buffer over
+peer-mapped memory (tp.PeerArena) and a barrier kernel follows; norms, attention, SiLU*up and the residual additions
+run replicated on every rank on the assembled rows, as do the KV caches.  Per-column arithmetic is the one-GPU
+arithmetic, so logits are bit-identical at every rank count.  The sharded decode step uses the separate operators
+(the fused epilogues need a whole row inside one kernel).  `prefill_batch` runs several prompts of equal length as
+one batch through the linears (M = prompts x tokens) with per-prompt KV caches.
 """
 from __future__ import annotations
 
@@ -44,10 +52,16 @@ def _p(t):
 
 
 class Qwen3Synthetic:
-    def __init__(self, pkg, ctx, cfg: Qwen3Config, seed: int = 0):
+    def __init__(self, pkg, ctx, cfg: Qwen3Config, seed: int = 0, world: int = 1, rank: int = 0, dist=None, batch: int = 1, max_rows: int = 0):
+        """world / rank / dist: column-sharded over `world` processes (dist = torch.distributed, initialised).  batch: number
+        of per-prompt KV caches (prefill_batch).  max_rows: the largest number of rows (prompts x tokens) any call will pass;
+        needed up front only when sharded (the peer-mapped output buffers are sized once)."""
         import torch
         assert cfg.head_dim == 128, "the glue kernels are written for head_dim 128"
         self.pkg, self.ctx, self.cfg, self.torch = pkg, ctx, cfg, torch
+        self.world, self.rank, self.dist, self.batch = world, rank, dist, batch
+        if world > 1:
+            cfg.decode_mode = "separate"
         self.L = pkg.lib()
         g = torch.Generator(device="cuda")
         g.manual_seed(seed)
@@ -66,7 +80,9 @@ class Qwen3Synthetic:
             m = (-7.5 * d * (1.0 + 0.02 * torch.randn((N, K // 32), device="cuda", generator=g))).half().float()
             if row_perm is not None:
                 nib, d, m = nib[row_perm].contiguous(), d[row_perm].contiguous(), m[row_perm].contiguous()
-            w = ctx.weight_dev(pkg.A81W41, pkg.SCALES_F16, N, K, nib, d, m)
+            n0, n1 = pkg.tp.shard_range(N, world, rank)      # every rank draws the same matrix and keeps its rows
+            w = ctx.weight_dev(pkg.A81W41, pkg.SCALES_F16, N, K, nib, d, m, None, n0, n1)
+            w.n_begin = n0
             return w
 
         # fused gate_up projection stored in (32 gate rows, 32 up rows) groups: stored row 64b + e is gate row 32b + e,
@@ -81,13 +97,15 @@ class Qwen3Synthetic:
                 ln1=torch.ones(H, device="cuda"), ln2=torch.ones(H, device="cuda"),
                 qn=torch.ones(cfg.head_dim, device="cuda"), kn=torch.ones(cfg.head_dim, device="cuda"),
                 qkv=qlinear(qkv_n, H), o=qlinear(H, cfg.nq * cfg.head_dim), gate_up=qlinear(2 * F, H, gu_perm), down=qlinear(H, F),
-                k_cache=torch.zeros((cfg.nkv, cfg.max_pos, cfg.head_dim), dtype=torch.float16, device="cuda"),
-                v_cache=torch.zeros((cfg.nkv, cfg.max_pos, cfg.head_dim), dtype=torch.float16, device="cuda")))
+                k_cache=torch.zeros((batch, cfg.nkv, cfg.max_pos, cfg.head_dim), dtype=torch.float16, device="cuda"),
+                v_cache=torch.zeros((batch, cfg.nkv, cfg.max_pos, cfg.head_dim), dtype=torch.float16, device="cuda")))
         self.final_norm = torch.ones(H, device="cuda")
         self.embed = (torch.randn((V, H), device="cuda", generator=g) * 0.02).half()
         if cfg.lm_head_fp16:
             head = (torch.randn((V, H), device="cuda", generator=g) * 0.02).half()
-            self.lm_head = ctx.f16w_dev(head, V, H)
+            v0, v1 = pkg.tp.shard_range(V, world, rank)
+            self.lm_head = ctx.f16w_dev(head, V, H, v0, v1)
+            self.lm_head.n_begin = v0
             del head
         else:
             self.lm_head = qlinear(V, H)
@@ -105,6 +123,26 @@ class Qwen3Synthetic:
         self.act_h = ctx.act(1, H)                        # input of qkv / gate_up
         self.act_attn = ctx.act(1, cfg.nq * cfg.head_dim)  # input of o_proj
         self.act_f = ctx.act(1, F)                        # input of down_proj
+        self.arena = None
+        if world > 1:
+            rows = max(max_rows, 1)
+            self.arena = pkg.tp.PeerArena(pkg, ctx, dist, world, rank, dict(qkv=(rows, qkv_n), proj=(rows, H), gu=(rows, 2 * F),
+                                                                             logits=(max(batch, 1), V)))
+
+    def close(self):
+        if self.arena is not None:
+            self.arena.close()
+            self.arena = None
+
+    def _linear(self, name, w, x, T, out):
+        """One quantized linear over T rows: on one GPU into `out`; sharded, into region `name` of every rank's arena
+        (the returned tensor is then the assembled [T][N] matrix)."""
+        if self.arena is None:
+            self.ctx.linear(w, x, T, out, out.shape[1])
+            return out
+        self.arena.linear(name, w, x, T, w.n_begin)
+        self.arena.barrier()
+        return self.arena.view(name, T)
 
     # ------------------------------------------------------------------ buffers
     def _buffers(self, T):
@@ -121,10 +159,13 @@ class Qwen3Synthetic:
         self.ctx.check(rc)
 
     # ------------------------------------------------------------------ one forward over T tokens (tokens_dev int32 [T])
-    def forward(self, tokens_dev, T, advance):
-        """Runs the T tokens at positions pos .. pos+T-1 through the model, takes the last token's logits,
-        stores their argmax in self.token (and the generated list) and advances pos by `advance`."""
+    def forward(self, tokens_dev, T, advance, nseq: int = 1):
+        """Runs the T tokens (nseq prompts of T / nseq tokens each, every prompt at positions pos .. pos + T/nseq - 1 of its
+        own cache) through the model, takes the last token's logits of each prompt, stores the argmax of the first
+        prompt's in self.token (and the generated list) and advances pos by `advance`."""
         cfg, L, h, b = self.cfg, self.L, self.ctx.h, self._buffers(T)
+        Ts = T // nseq
+        assert nseq * Ts == T and nseq <= self.batch
         H, F = cfg.hidden, cfg.ffn
         scale = 1.0 / float(np.sqrt(cfg.head_dim))
         self._chk(L.inkq_glue_embedding(h, _p(self.embed), _p(tokens_dev), T, H, cfg.vocab, _p(b["x"])))
@@ -138,8 +179,8 @@ class Qwen3Synthetic:
             for i, ly in enumerate(self.layers):
                 self._chk(L.inkq_glue_decode_gemv(h, ly["qkv"].h, self.act_h.h, _p(b["qkv"]), 0, None, eps, None, Q, None))
                 self._chk(L.inkq_glue_qknorm_rope_cache(h, _p(b["qkv"]), _p(ly["qn"]), _p(ly["kn"]), _p(self.cos), _p(self.sin), _p(self.pos), T,
-                                                        cfg.nq, cfg.nkv, cfg.max_pos, eps, _p(b["q"]), _p(ly["k_cache"]), _p(ly["v_cache"])))
-                self._chk(L.inkq_glue_attention_quant(h, _p(b["q"]), _p(ly["k_cache"]), _p(ly["v_cache"]), _p(self.pos), cfg.nq, cfg.nkv,
+                                                        cfg.nq, cfg.nkv, cfg.max_pos, eps, _p(b["q"]), _p(ly["k_cache"][0]), _p(ly["v_cache"][0])))
+                self._chk(L.inkq_glue_attention_quant(h, _p(b["q"]), _p(ly["k_cache"][0]), _p(ly["v_cache"][0]), _p(self.pos), cfg.nq, cfg.nkv,
                                                       cfg.max_pos, C.c_float(scale), self.act_attn.h, Q))
                 self._chk(L.inkq_glue_decode_gemv(h, ly["o"].h, self.act_attn.h, _p(b["x"]), 2, _p(ly["ln2"]), eps, self.act_h.h, Q, None))
                 self._chk(L.inkq_glue_decode_gemv(h, ly["gate_up"].h, self.act_h.h, None, 3, None, eps, self.act_f.h, Q, None))
@@ -152,37 +193,62 @@ class Qwen3Synthetic:
             # the residual connection in its epilogue (x += ...)
             self._chk(L.inkq_glue_linear_m1(h, ly["qkv"].h, _p(b["x"]), 1, _p(ly["ln1"]), eps, _p(b["qkv"]), 0))
             self._chk(L.inkq_glue_qknorm_rope_cache(h, _p(b["qkv"]), _p(ly["qn"]), _p(ly["kn"]), _p(self.cos), _p(self.sin), _p(self.pos), T,
-                                                    cfg.nq, cfg.nkv, cfg.max_pos, eps, _p(b["q"]), _p(ly["k_cache"]), _p(ly["v_cache"])))
-            self._chk(L.inkq_glue_attention(h, _p(b["q"]), _p(ly["k_cache"]), _p(ly["v_cache"]), _p(self.pos), T, cfg.nq, cfg.nkv, cfg.max_pos,
+                                                    cfg.nq, cfg.nkv, cfg.max_pos, eps, _p(b["q"]), _p(ly["k_cache"][0]), _p(ly["v_cache"][0])))
+            self._chk(L.inkq_glue_attention(h, _p(b["q"]), _p(ly["k_cache"][0]), _p(ly["v_cache"][0]), _p(self.pos), T, cfg.nq, cfg.nkv, cfg.max_pos,
                                             C.c_float(scale), _p(b["attn"])))
             self._chk(L.inkq_glue_linear_m1(h, ly["o"].h, _p(b["attn"]), 0, None, eps, _p(b["x"]), 1))
             self._chk(L.inkq_glue_linear_m1(h, ly["gate_up"].h, _p(b["x"]), 1, _p(ly["ln2"]), eps, _p(b["gu"]), 0))
             self._chk(L.inkq_glue_linear_m1(h, ly["down"].h, _p(b["gu"]), 2, None, eps, _p(b["x"]), 1))
         for ly in (self.layers if mode == "separate" else []):
             self._chk(L.inkq_glue_rmsnorm(h, _p(b["x"]), _p(ly["ln1"]), T, H, C.c_float(cfg.eps), _p(b["xn"])))
-            self.ctx.linear(ly["qkv"], b["xn"], T, b["qkv"], b["qkv"].shape[1])
-            self._chk(L.inkq_glue_qknorm_rope_cache(h, _p(b["qkv"]), _p(ly["qn"]), _p(ly["kn"]), _p(self.cos), _p(self.sin), _p(self.pos), T,
-                                                    cfg.nq, cfg.nkv, cfg.max_pos, C.c_float(cfg.eps), _p(b["q"]), _p(ly["k_cache"]),
-                                                    _p(ly["v_cache"])))
-            self._chk(L.inkq_glue_attention(h, _p(b["q"]), _p(ly["k_cache"]), _p(ly["v_cache"]), _p(self.pos), T, cfg.nq, cfg.nkv, cfg.max_pos,
-                                            C.c_float(scale), _p(b["attn"])))
-            self.ctx.linear(ly["o"], b["attn"], T, b["proj"], H)
-            self._chk(L.inkq_glue_add_inplace(h, _p(b["x"]), _p(b["proj"]), C.c_longlong(T * H)))
+            qkv = self._linear("qkv", ly["qkv"], b["xn"], T, b["qkv"])
+            for sq in range(nseq):            # per prompt: its own positions and KV cache
+                rows = slice(sq * Ts, (sq + 1) * Ts)
+                self._chk(L.inkq_glue_qknorm_rope_cache(h, _p(qkv[rows]), _p(ly["qn"]), _p(ly["kn"]), _p(self.cos), _p(self.sin), _p(self.pos), Ts,
+                                                        cfg.nq, cfg.nkv, cfg.max_pos, C.c_float(cfg.eps), _p(b["q"][rows]), _p(ly["k_cache"][sq]),
+                                                        _p(ly["v_cache"][sq])))
+                self._chk(L.inkq_glue_attention(h, _p(b["q"][rows]), _p(ly["k_cache"][sq]), _p(ly["v_cache"][sq]), _p(self.pos), Ts, cfg.nq, cfg.nkv,
+                                                cfg.max_pos, C.c_float(scale), _p(b["attn"][rows])))
+            proj = self._linear("proj", ly["o"], b["attn"], T, b["proj"])
+            self._chk(L.inkq_glue_add_inplace(h, _p(b["x"]), _p(proj), C.c_longlong(T * H)))
             self._chk(L.inkq_glue_rmsnorm(h, _p(b["x"]), _p(ly["ln2"]), T, H, C.c_float(cfg.eps), _p(b["xn"])))
-            self.ctx.linear(ly["gate_up"], b["xn"], T, b["gu"], 2 * F)       # fused gate_up projection, (32 gate, 32 up) column groups
-            self._chk(L.inkq_glue_silu_mul_rows(h, _p(b["gu"]), T, F, _p(b["act"])))
-            self.ctx.linear(ly["down"], b["act"], T, b["proj"], H)
-            self._chk(L.inkq_glue_add_inplace(h, _p(b["x"]), _p(b["proj"]), C.c_longlong(T * H)))
+            gu = self._linear("gu", ly["gate_up"], b["xn"], T, b["gu"])       # fused gate_up projection, (32 gate, 32 up) column groups
+            self._chk(L.inkq_glue_silu_mul_rows(h, _p(gu), T, F, _p(b["act"])))
+            proj = self._linear("proj", ly["down"], b["act"], T, b["proj"])
+            self._chk(L.inkq_glue_add_inplace(h, _p(b["x"]), _p(proj), C.c_longlong(T * H)))
         if mode != "epilogue":      # (in that mode the last down_proj's epilogue has written the normalized row)
-            last = b["x"][T - 1:T]
-            self._chk(L.inkq_glue_rmsnorm(h, _p(last), _p(self.final_norm), 1, H, C.c_float(cfg.eps), _p(b["xn"])))
-        if cfg.lm_head_fp16:
-            self.ctx.f16w_matmul(self.lm_head, b["xn"], 1, b["logits"], cfg.vocab)
+            if nseq == 1:
+                last = b["x"][T - 1:T]
+            else:
+                last = b["x"][Ts - 1::Ts].contiguous()       # the last token of every prompt
+            self._chk(L.inkq_glue_rmsnorm(h, _p(last), _p(self.final_norm), nseq, H, C.c_float(cfg.eps), _p(b["xn"])))
+        logits = b["logits"] if nseq == 1 else self._batch_logits(nseq)
+        if self.arena is not None:
+            if cfg.lm_head_fp16:
+                self.arena.f16w("logits", self.lm_head, b["xn"], nseq, self.lm_head.n_begin)
+            else:
+                self.arena.linear("logits", self.lm_head, b["xn"], nseq, self.lm_head.n_begin)
+            self.arena.barrier()
+            logits = self.arena.view("logits", nseq)
+        elif cfg.lm_head_fp16:
+            self.ctx.f16w_matmul(self.lm_head, b["xn"], nseq, logits, cfg.vocab)
         else:
-            self.ctx.linear(self.lm_head, b["xn"], 1, b["logits"], cfg.vocab)
-        self._chk(L.inkq_glue_argmax_advance(h, _p(b["logits"]), cfg.vocab, _p(self.token), _p(self.pos), advance, _p(self.generated),
+            self.ctx.linear(self.lm_head, b["xn"], nseq, logits, cfg.vocab)
+        self._chk(L.inkq_glue_argmax_advance(h, _p(logits), cfg.vocab, _p(self.token), _p(self.pos), advance, _p(self.generated),
                                              self.generated.numel()))
-        return b["logits"]
+        return logits
+
+    def _batch_logits(self, nseq):
+        key = ("logits", nseq)
+        if key not in self.bufs:
+            self.bufs[key] = self.torch.empty((nseq, self.cfg.vocab), device="cuda", dtype=self.torch.float32)
+        return self.bufs[key]
+
+    def prefill_batch(self, prompts_dev):
+        """prompts_dev int32 [B][T]: B prompts of equal length as one batch (B <= the `batch` the model was built with).
+        Returns the logits [B][vocab] of each prompt's last token; pos advances by T."""
+        B, T = int(prompts_dev.shape[0]), int(prompts_dev.shape[1])
+        return self.forward(prompts_dev.reshape(-1), B * T, T, nseq=B)
 
     def reset(self):
         self.pos.zero_()

@@ -113,3 +113,63 @@ class PeerScatter:
             self.ctx.synchronize()
             self.dist.barrier()   # nobody unmaps while a peer may still store
         self.ps.close()
+
+
+class PeerArena:
+    """One peer-mapped byte buffer per rank holding several named fp32 [rows][cols] regions (the outputs of a model's
+    column-sharded linears).  `linear(name, w_shard, x, M, n_begin)` runs the sharded forward and stores the shard's
+    columns of region `name` on every rank; `f16w(name, ...)` does the same for an fp16 matrix; `barrier()` completes
+    the exchange.  A region may be rewritten only after every rank has passed a barrier that follows its last reader,
+    which holds whenever consecutive linears use different regions and each is followed by a barrier."""
+
+    def __init__(self, pkg, ctx, dist, world: int, rank: int, regions: dict):
+        import torch
+        self.pkg, self.ctx, self.dist, self.world, self.rank = pkg, ctx, dist, world, rank
+        self.off, self.shape = {}, {}
+        pos = pkg.PEER_RESERVED_BYTES
+        for name, (rows, cols) in regions.items():
+            self.off[name], self.shape[name] = pos, (rows, cols)
+            pos += (4 * rows * cols + 255) // 256 * 256
+        self.buf = torch.zeros(pos, dtype=torch.uint8, device="cuda")
+        torch.cuda.synchronize()
+        err = None
+        try:
+            blob = ctx.peer_export(self.buf)
+        except Exception as e:
+            err, blob = e, b""
+        blobs = [None] * world
+        dist.all_gather_object(blobs, blob)
+        self.ps = None
+        if all(len(b) == pkg.PEER_HANDLE_BYTES for b in blobs):
+            try:
+                self.ps = ctx.peerset_open(world, rank, self.buf, blobs)
+            except Exception as e:
+                err = e
+        oks = [None] * world
+        dist.all_gather_object(oks, self.ps is not None)
+        if not all(oks):
+            if self.ps is not None:
+                self.ps.close()
+            raise RuntimeError(f"peer buffers could not be mapped on every rank (this rank: {err!r})")
+
+    def view(self, name, rows=None):
+        import torch
+        r, c = self.shape[name]
+        rows = r if rows is None else rows
+        return self.buf[self.off[name]:self.off[name] + 4 * rows * c].view(torch.float32).view(rows, c)
+
+    def linear(self, name, w, x, M: int, n_begin: int):
+        cols = self.shape[name][1]
+        self.ctx.linear_scatter(w, x, M, self.ps, self.off[name] + 4 * n_begin, cols)
+
+    def f16w(self, name, w, x, M: int, n_begin: int, precision: int = 0):
+        cols = self.shape[name][1]
+        self.ctx.f16w_matmul_scatter(w, x, M, self.ps, self.off[name] + 4 * n_begin, cols, precision)
+
+    def barrier(self, timeout_ms: int = 2000):
+        self.ctx.peer_barrier(self.ps, timeout_ms)
+
+    def close(self):
+        self.ctx.synchronize()
+        self.dist.barrier()   # nobody unmaps while a peer may still store
+        self.ps.close()

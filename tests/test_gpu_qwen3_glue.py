@@ -250,3 +250,21 @@ def test_decode_gemv_epilogues_equal_separate_kernels(pkg, gpu):
     gpu.synchronize()
     for got, want_ in zip(a_att.export(1), a_ref.export(1)):
         assert np.array_equal(got, want_)
+
+
+def test_batched_prefill_equals_separate_prefills(pkg, gpu):
+    """Several prompts as one batch through the linears (M = prompts x tokens, per-prompt KV caches): each prompt's
+    last-token logits equal those of its own prefill bit for bit (rows of a QGEMM are independent)."""
+    import torch
+    B, T = 3, 21
+    model = pkg.qwen3_forward.Qwen3Synthetic(pkg, gpu, small_cfg(pkg), seed=2, batch=B)
+    prompts = torch.from_numpy(np.stack([pkg.synth.tokens(T, 1024, 30 + i) for i in range(B)])).cuda()
+    model.reset()
+    batched = model.prefill_batch(prompts).clone()
+    gpu.synchronize()
+    assert int(model.pos.item()) == T
+    for i in range(B):
+        model.reset()
+        one = model.prefill(prompts[i].contiguous()).clone()
+        gpu.synchronize()
+        assert torch.equal(batched[i:i + 1], one)

@@ -76,3 +76,56 @@ def test_two_rank_shards_equal_single_gpu(tmp_path):
     mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
     for r in range(2):
         assert open(tmp_path / f"rank{r}.txt").read() == "ok"
+
+
+def _model_worker(rank, world, port, out_dir):
+    """Column-sharded synthetic forward: logits of prefill, decode steps and a batched prefill equal the one-GPU model's."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    ctx = pkg.Context(rank, torch.cuda.current_stream().cuda_stream)
+    mk = lambda: pkg.qwen3_forward.Qwen3Config(layers=2, hidden=256, nq=4, nkv=2, head_dim=128, ffn=512, vocab=1024, max_pos=64,
+                                               lm_head_fp16=True, decode_mode="separate")
+    T, B = 19, 3
+    single = pkg.qwen3_forward.Qwen3Synthetic(pkg, ctx, mk(), seed=3, batch=B)
+    shard = pkg.qwen3_forward.Qwen3Synthetic(pkg, ctx, mk(), seed=3, world=world, rank=rank, dist=dist, batch=B, max_rows=B * T)
+    tokens = torch.from_numpy(pkg.synth.tokens(T, 1024, 9)).cuda()
+    ok = True
+    for model in (single, shard):
+        model.reset()
+    a = single.prefill(tokens).clone()
+    b = shard.prefill(tokens).clone()
+    ctx.synchronize()
+    ok = ok and bool(torch.equal(a, b))
+    for _ in range(3):
+        a = single.decode_step().clone()
+        b = shard.decode_step().clone()
+        ctx.synchronize()
+        ok = ok and bool(torch.equal(a, b)) and int(single.token.item()) == int(shard.token.item())
+    prompts = torch.from_numpy(np.stack([pkg.synth.tokens(T, 1024, 20 + i) for i in range(B)])).cuda()
+    for model in (single, shard):
+        model.reset()
+    a = single.prefill_batch(prompts).clone()
+    b = shard.prefill_batch(prompts).clone()
+    ctx.synchronize()
+    ok = ok and bool(torch.equal(a, b))
+    shard.close()
+    with open(os.path.join(out_dir, f"model_rank{rank}.txt"), "w") as f:
+        f.write("ok" if ok else "mismatch")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_model_forward_equals_single_gpu(tmp_path):
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    mp.spawn(_model_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        assert open(tmp_path / f"model_rank{r}.txt").read() == "ok"
