@@ -153,15 +153,23 @@ __global__ void __launch_bounds__(NT) k_attention(const float *__restrict__ q, c
     for (int j = tid; j < nkeys; j += NT) {
         const uint4 *kr = reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(j) * HEAD_DIM);
         float acc = 0.0f;
-#pragma unroll 4
-        for (int c = 0; c < HEAD_DIM / 8; c++) {
-            const uint4 pk = kr[c];
-            const uint32_t wd[4] = {pk.x, pk.y, pk.z, pk.w};
+        // the key's 256 bytes as two groups of eight independent 16-byte loads: the row is latency-bound (a decode step has
+        // one CTA per head), so the loads in flight per thread set its speed; summation order: c ascending
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&wd[i]));
-                acc = fmaf(qs[c * 8 + 2 * i], f.x, acc);
-                acc = fmaf(qs[c * 8 + 2 * i + 1], f.y, acc);
+        for (int c8 = 0; c8 < HEAD_DIM / 8; c8 += 8) {
+            uint4 pk[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) pk[u] = kr[c8 + u];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int c = c8 + u;
+                const uint32_t wd[4] = {pk[u].x, pk[u].y, pk[u].z, pk[u].w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&wd[i]));
+                    acc = fmaf(qs[c * 8 + 2 * i], f.x, acc);
+                    acc = fmaf(qs[c * 8 + 2 * i + 1], f.y, acc);
+                }
             }
         }
         acc *= scale;
@@ -190,7 +198,7 @@ __global__ void __launch_bounds__(NT) k_attention(const float *__restrict__ q, c
     for (int i = 0; i < NW; i++) den += red[NW + i];
     const float inv = 1.0f / den;
     float a[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
+#pragma unroll 8
     for (int j = warp; j < nkeys; j += NW) {
         const float p = sc[j];
         const uint2 pk = reinterpret_cast<const uint2 *>(vb + static_cast<size_t>(j) * HEAD_DIM)[lane];

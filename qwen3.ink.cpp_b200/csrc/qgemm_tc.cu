@@ -620,8 +620,9 @@ static int encode2d(inkq_ctx *ctx, CUtensorMap *map, CUtensorMapDataType dt, int
 }
 
 // Relative cost of one tile by its width block_m = 16 * index (any common factor cancels; measured on a B200 with
-// one tile per SM): narrow tiles are bounded by the serial chain of K=32 MMAs, wide ones by the epilogue arithmetic.
-static const float tile_cost[9] = {0.f, 1.00f, 1.05f, 1.11f, 1.28f, 1.47f, 1.66f, 1.72f, 1.98f};
+// one tile per SM at K = 4096: 32.2, 35.4, 39.3, 45.7, 51.7, 58.4, 66.0, 76.6 us): narrow tiles are bounded by the chain of
+// K=32 MMAs and their commits, wide ones by the epilogue arithmetic.  The ratios hardly depend on K (both terms are per block).
+static const float tile_cost[9] = {0.f, 1.00f, 1.10f, 1.22f, 1.42f, 1.61f, 1.81f, 2.05f, 2.38f};
 
 int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc, int32_t *dots, const ExtraDst *extra, int tn_begin, int tn_count)
 {
