@@ -258,6 +258,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // Launched with programmatic stream serialization: everything above (barriers, tensor-memory allocation) may overlap
+    // the tail of the kernel before this one in the stream (normally the quantizer that writes the activations); nothing
+    // below may, and a dependent kernel launched the same way may begin its own set-up from here on.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp < 4) setmaxnreg_dec<CTRL_REGS>();
     if (warp >= 4 && warp < 8) setmaxnreg_dec<UNPACK_REGS>();
@@ -585,7 +590,8 @@ static int launch_one(inkq_ctx *ctx, const CUtensorMap *maps, const TcParams &pr
             configured[ctx->device] = true;
         }
     }
-    k_qgemm_tc<CW, HAS_MIN, DUMP><<<grid, TC_THREADS, TC_SMEM_BYTES, ctx->stream>>>(maps[0], maps[1], maps[2], prm);
+    cudaError_t le = launch_pdl(k_qgemm_tc<CW, HAS_MIN, DUMP>, dim3(grid), dim3(TC_THREADS), TC_SMEM_BYTES, ctx->stream, maps[0], maps[1], maps[2], prm);
+    if (le != cudaSuccess) return fail(ctx, INKQ_ERR_CUDA, std::string("k_qgemm_tc launch: ") + cudaGetErrorString(le));
     return after_launch(ctx, "k_qgemm_tc");
 }
 
