@@ -2,10 +2,14 @@
 //
 // Same names, constructor arguments, forward() signature and error behaviour as
 // Qwen_Linear_with_bias_Int4 (qwen3/include/qwen/QwenOperator.h:86-231,
-// qwen3/src/qwen/QwenOperator.cc:80-124), so the model code that owns such layers
-// (QwenAttention.cc:29-30, QwenDecoderLayer.cc:21-23, QwenForCausalLM.cc:121) compiles
-// against it unchanged.  The weights live on the GPU; forward() copies the activations
-// in and the result out (inkq_linear_host).
+// qwen3/src/qwen/QwenOperator.cc:80-124), for a host that owns such layers the way the
+// reference's model code does (QwenAttention.cc:29-30, QwenDecoderLayer.cc:21-23,
+// QwenForCausalLM.cc:121).  The weights live on the GPU; forward() copies the activations
+// in and the result out (inkq_linear_host).  It is a stand-alone class, not a replacement
+// header for the reference tree: the reference's own class and ModelContext (which also
+// carries the KV caches and the CPU staging buffers) run on the GPU unchanged when the
+// reference's QwenOperator.cc is linked against libinkq_refshim.so (ref_names.cc) instead
+// of its quantized_gemx_kernels.cc.
 //
 // When this header is used inside the reference tree, define INK_USE_REFERENCE_COMMON
 // before including it so that the reference's own Matrix3D (qwen3/include/common.h) is
@@ -43,9 +47,10 @@ class Matrix3D {
 };
 #endif
 
-// Stands in for the reference's ModelContext (QwenOperator.h:34-43): instead of the CPU
-// staging and activation scratch buffers it carries the device context, which owns the
-// activation scratch on the GPU.
+// The part of the reference's ModelContext (QwenOperator.h:34-43) this class needs: the
+// reference's CPU staging and activation scratch are replaced by the device context, which
+// owns the activation scratch on the GPU; the KV caches belong to the attention operator
+// and have no place here.
 struct ModelContext {
     inkq_ctx *gpu = nullptr;
     explicit ModelContext(int device = 0)
