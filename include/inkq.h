@@ -197,6 +197,8 @@ int inkq_peerset_open(inkq_ctx *ctx, int world, int rank, void *local_ptr, const
 int inkq_peerset_from_pointers(inkq_ctx *ctx, int world, int rank, void *const *ptrs, size_t bytes, inkq_peerset **out);
 int inkq_peerset_destroy(inkq_peerset *ps);
 int inkq_linear_scatter(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev, int M, inkq_peerset *ps, size_t byte_offset, int ldc);
+/* inkq_gemm (rows already quantized into `act`, M > 1) with the same multi-destination epilogue. */
+int inkq_gemm_scatter(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, inkq_peerset *ps, size_t byte_offset, int ldc);
 int inkq_peer_barrier(inkq_ctx *ctx, inkq_peerset *ps, int timeout_ms);
 /* inkq_f16w_matmul_prec of a row shard of the fp16 matrix (inkq_f16w_create with [n_begin, n_end)), the output columns
  * stored into every rank's buffer like inkq_linear_scatter (lm_head of QwenForCausalLM.cc:43-46, column-sharded). */

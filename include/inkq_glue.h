@@ -65,6 +65,17 @@ int inkq_glue_rmsnorm_quant(inkq_ctx *ctx, const float *x_dev, const float *norm
                             float *xn_out_dev);
 int inkq_glue_attention_quant(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev,
                               int nq, int nkv, int max_pos, float scale, inkq_act *out, int out_qmode);
+/* ---- prompt path with the element-wise operators folded into the quantizer ------------------
+ * No counterpart in the reference (separate operators on host matrices, QwenDecoderLayer.cc:57-105).  Both write the
+ * quantized rows straight into an activation handle (inkq_act_create(ctx, rows >= M, K)) that inkq_gemm then
+ * consumes; the bits equal those of the separate operators followed by inkq_quantize.
+ *   inkq_glue_add_rmsnorm_quant_rows: x[M][K] += delta[M][K] (skipped when delta_dev is NULL; x is updated in place),
+ *       then RMSNorm(x; norm_w, eps) quantized into `out` (xn_out_dev, if not NULL, also receives the normalized rows)
+ *   inkq_glue_silu_mul_quant_rows: gu [M][2F] in (32 gate, 32 up) column groups -> SiLU(gate) * up quantized into `out`
+ * out_qmode: INKQ_Q8_1_F32 for an A81W41 layer with M > 1 (what inkq_linear uses), INKQ_Q8_0_F16 for the A80 schemes. */
+int inkq_glue_add_rmsnorm_quant_rows(inkq_ctx *ctx, float *x_dev, const float *delta_dev, const float *norm_w_dev, float eps, int M, int K,
+                                     inkq_act *out, int out_qmode, float *xn_out_dev);
+int inkq_glue_silu_mul_quant_rows(inkq_ctx *ctx, const float *gu_dev, int M, int F, inkq_act *out, int out_qmode);
 /* a += b (residual).  qwen3/src/qwen/QwenDecoderLayer.cc:73,105 */
 int inkq_glue_add_inplace(inkq_ctx *ctx, float *a_dev, const float *b_dev, long long n);
 /* Greedy sampling: *token_out = argmax(logits) (first index on ties), appended to generated

@@ -232,6 +232,50 @@ class Reference:
             self.fn[name](K, N, 32, _ptr(out), _ptr(d), _ptr(m), _ptr(nib))
         return out.view(dt)
 
+    # ---- the reference's operators around the linear layer (oracle/ref_ops_driver.cc)
+    def _op(self, name):
+        fn = getattr(self.lib, name)
+        fn.restype = None
+        return fn
+
+    def rmsnorm(self, x, w, eps: float = 1e-6) -> np.ndarray:
+        """Qwen3RMSNorm::forward over the last axis of x [rows][heads][dim] (or [rows][dim])."""
+        x, w = _c(x, np.float32), _c(w, np.float32)
+        shape = x.shape
+        x3 = x.reshape(shape[0], -1, shape[-1])
+        out = np.empty_like(x3)
+        self._op("refop_rmsnorm")(_ptr(x3), _ptr(w), x3.shape[0], x3.shape[1], x3.shape[2], C.c_float(eps), _ptr(out))
+        return out.reshape(shape)
+
+    def silu_mul(self, a, b) -> np.ndarray:
+        a, b = _c(a, np.float32), _c(b, np.float32)
+        out = np.empty_like(a)
+        self._op("refop_silu_mul")(_ptr(a), _ptr(b), a.shape[0], a.shape[1], _ptr(out))
+        return out
+
+    def add(self, a, b) -> np.ndarray:
+        a, b = _c(a, np.float32), _c(b, np.float32)
+        out = np.empty_like(a)
+        self._op("refop_add")(_ptr(a), _ptr(b), a.shape[0], a.shape[1], _ptr(out))
+        return out
+
+    def rope(self, q, k, start: int, cos, sin):
+        """RotaryPosEmb::apply on q [nq][len][hd], k [nk][len][hd]; returns the rotated copies."""
+        q, k = _c(q, np.float32).copy(), _c(k, np.float32).copy()
+        cos, sin = _c(cos, np.float32), _c(sin, np.float32)
+        self._op("refop_rope")(_ptr(q), _ptr(k), q.shape[0], k.shape[0], q.shape[1], q.shape[2], start, _ptr(cos), _ptr(sin), cos.shape[0])
+        return q, k
+
+    def attention(self, q, k_cache, v_cache, past: int, alpha: float) -> np.ndarray:
+        """The attention core of Qwen3Attention::forward: q [nq][sq][hd], caches [nkv][max_len][hd] (fp32) holding
+        past + sq positions; returns [sq][nq * hd]."""
+        q, k_cache, v_cache = _c(q, np.float32), _c(k_cache, np.float32), _c(v_cache, np.float32)
+        nq, sq, hd = q.shape
+        out = np.empty((sq, nq * hd), np.float32)
+        self._op("refop_attention")(_ptr(q), _ptr(k_cache), _ptr(v_cache), nq, k_cache.shape[0], sq, past, hd, k_cache.shape[1], C.c_float(alpha),
+                                    _ptr(out))
+        return out
+
     def matmul(self, name: str, A: np.ndarray, B: np.ndarray, M: int, N: int, K: int) -> np.ndarray:
         """name in {gemm,gemv}_repack_*.  A must carry readable padding rows: the
         reference GEMMs read up to 5 (A81W41) or 1 (A80W40) activation rows past M

@@ -36,14 +36,14 @@ SYMBOLS = [
     "inkq_gemv", "inkq_gemm_simt", "inkq_debug_block_dots", "inkq_debug_block_dots_tc", "inkq_linear",
     "inkq_linear_host", "inkq_linear_m1_static", "inkq_gemm_w41_f16act", "inkq_gemm_w41_f16act_simt", "inkq_f16w_create", "inkq_f16w_create_dev", "inkq_f16w_destroy", "inkq_f16w_matmul_prec",
     "inkq_f16w_matmul", "inkq_peer_export", "inkq_peerset_open", "inkq_peerset_from_pointers", "inkq_peerset_destroy",
-    "inkq_linear_scatter", "inkq_peer_barrier", "inkq_f16w_matmul_scatter", "inkq_weight_quantize_dev",
+    "inkq_linear_scatter", "inkq_gemm_scatter", "inkq_peer_barrier", "inkq_f16w_matmul_scatter", "inkq_weight_quantize_dev",
 ]
 
 
 # every symbol include/inkq_glue.h declares
 GLUE_SYMBOLS = ["inkq_glue_embedding", "inkq_glue_rmsnorm", "inkq_glue_qknorm_rope_cache", "inkq_glue_attention", "inkq_glue_silu_mul",
                 "inkq_glue_add_inplace", "inkq_glue_argmax_advance", "inkq_glue_silu_mul_rows", "inkq_glue_linear_m1", "inkq_glue_decode_gemv", "inkq_glue_rmsnorm_quant",
-                "inkq_glue_attention_quant"]
+                "inkq_glue_attention_quant", "inkq_glue_add_rmsnorm_quant_rows", "inkq_glue_silu_mul_quant_rows"]
 
 
 PEER_RESERVED_BYTES = 256   # INKQ_PEER_RESERVED_BYTES
@@ -255,6 +255,10 @@ class Context:
     def linear_scatter(self, w, x, M: int, ps, byte_offset: int, ldc: int):
         """inkq_linear whose epilogue stores the shard's columns into every rank's buffer of the peer set."""
         self.check(self.L.inkq_linear_scatter(self.h, w.h, _dp(x), M, ps.h, C.c_size_t(byte_offset), ldc))
+
+    def gemm_scatter(self, act, w, ps, byte_offset: int, ldc: int):
+        """inkq_gemm on rows already quantized into `act`, same multi-destination epilogue."""
+        self.check(self.L.inkq_gemm_scatter(self.h, act.h, w.h, ps.h, C.c_size_t(byte_offset), ldc))
 
     def f16w_matmul_scatter(self, w, x, M: int, ps, byte_offset: int, ldc: int, precision: int = 0):
         self.check(self.L.inkq_f16w_matmul_scatter(self.h, w.h, _dp(x), M, ps.h, C.c_size_t(byte_offset), ldc, precision))

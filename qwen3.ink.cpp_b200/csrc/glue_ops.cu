@@ -19,6 +19,9 @@
 #include <cuda_fp16.h>
 #include <math.h>
 
+#include <mutex>
+
+#include "glue_math.cuh"
 #include "inkq_glue.h"
 #include "inkq_internal.h"
 #include "qgemv_common.cuh"
@@ -47,8 +50,7 @@ __global__ void __launch_bounds__(256) k_rmsnorm(const float *__restrict__ x, co
     const float4 *xr = reinterpret_cast<const float4 *>(x + static_cast<size_t>(row) * dim);
     float ss = 0.0f;
     for (int i = threadIdx.x; i < dim / 4; i += 256) {
-        const float4 v = xr[i];
-        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        ss = add_sumsq4(ss, xr[i]);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -57,12 +59,89 @@ __global__ void __launch_bounds__(256) k_rmsnorm(const float *__restrict__ x, co
     float tot = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; i++) tot += red[i];
-    const float inv = 1.0f / sqrtf(tot / static_cast<float>(dim) + eps);
+    const float inv = rms_inv(tot, dim, eps);
     float4 *yr = reinterpret_cast<float4 *>(y + static_cast<size_t>(row) * dim);
     const float4 *wr = reinterpret_cast<const float4 *>(w);
-    for (int i = threadIdx.x; i < dim / 4; i += 256) {
-        const float4 v = xr[i], g = wr[i];
-        yr[i] = make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+    for (int i = threadIdx.x; i < dim / 4; i += 256) yr[i] = rms_scale4(xr[i], inv, wr[i]);
+}
+
+// Prompt path, one CTA per row: x += delta (the residual connection, optional), RMSNorm of the row, and the
+// activation quantizer of the layer that consumes it, in one pass: the row is read once, kept in shared memory
+// between the sum of squares and the scaling, and leaves as int8 + block scales.  Element arithmetic, summation
+// order and quantizer are those of k_add_inplace, k_rmsnorm and k_quantize_q8, so the quantized row is the one the
+// three kernels would produce.  Eight consecutive threads share a 32-element quantization block.
+__global__ void __launch_bounds__(256) k_add_rmsnorm_quant_rows(float *__restrict__ x, const float *__restrict__ delta, const float *__restrict__ w,
+                                                                int M, int dim, float eps, int M_ld, int mode, int8_t *__restrict__ q,
+                                                                float *__restrict__ d, float *__restrict__ s, int32_t *__restrict__ isum,
+                                                                float *__restrict__ xn_out)
+{
+    extern __shared__ __align__(16) float4 rowbuf[];
+    __shared__ float red[8];
+    const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n4 = dim / 4, nb = dim / QK;
+    if (row >= M) {   // padding rows of the scale planes read as zero
+        for (int b = threadIdx.x; b < nb; b += 256) {
+            const size_t pl = static_cast<size_t>(b) * M_ld + row;
+            d[pl] = 0.0f;
+            s[pl] = 0.0f;
+            isum[pl] = 0;
+        }
+        return;
+    }
+    float4 *xr = reinterpret_cast<float4 *>(x + static_cast<size_t>(row) * dim);
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < n4; i += 256) {
+        float4 v = xr[i];
+        if (delta != nullptr) {
+            const float4 y = reinterpret_cast<const float4 *>(delta + static_cast<size_t>(row) * dim)[i];
+            v = make_float4(v.x + y.x, v.y + y.y, v.z + y.z, v.w + y.w);
+            xr[i] = v;
+        }
+        rowbuf[i] = v;
+        ss = add_sumsq4(ss, v);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += red[i];
+    const float inv = rms_inv(tot, dim, eps);
+    const float4 *wr = reinterpret_cast<const float4 *>(w);
+    for (int base = 0; base < n4; base += 256) {   // trip count is the same for every thread: the shuffles below see whole warps
+        const int i = base + threadIdx.x;
+        const bool live = i < n4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live) {
+            v = rms_scale4(rowbuf[i], inv, wr[i]);
+            if (xn_out != nullptr) reinterpret_cast<float4 *>(xn_out + static_cast<size_t>(row) * dim)[i] = v;
+        }
+        float mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float dd = __fdiv_rn(mx, 127.0f);
+        const float id = (mx != 0.0f) ? __fdiv_rn(127.0f, mx) : 0.0f;
+        const int i0 = __float2int_rn(__fmul_rn(v.x, id)), i1 = __float2int_rn(__fmul_rn(v.y, id));
+        const int i2 = __float2int_rn(__fmul_rn(v.z, id)), i3 = __float2int_rn(__fmul_rn(v.w, id));
+        int sum = (i0 + i1) + (i2 + i3);
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (live) {
+            reinterpret_cast<uint32_t *>(q)[static_cast<size_t>(row) * n4 + i] = pack_sat_s8x4_m1(i0, i1, i2, i3);
+            if ((i & 7) == 0) {
+                const size_t pl = static_cast<size_t>(i >> 3) * M_ld + row;
+                const float sv = __fmul_rn(dd, static_cast<float>(sum));
+                if (mode == INKQ_Q8_1_F32) {
+                    d[pl] = dd;
+                    s[pl] = sv;
+                } else {
+                    d[pl] = __half2float(__float2half_rn(dd));
+                    s[pl] = (mode == INKQ_Q8_1_F16) ? __half2float(__float2half_rn(sv)) : 0.0f;
+                }
+                isum[pl] = sum;
+            }
+        }
     }
 }
 
@@ -229,8 +308,7 @@ __global__ void __launch_bounds__(256) k_silu_mul(const float4 *__restrict__ gat
     const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= n4) return;
     const float4 g = gate[i], u = up[i];
-    auto f = [](float a, float b) { return a / (1.0f + __expf(-a)) * b; };
-    out[i] = make_float4(f(g.x, u.x), f(g.y, u.y), f(g.z, u.z), f(g.w, u.w));
+    out[i] = make_float4(silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z), silu_mul(g.w, u.w));
 }
 
 // Prompt attention: one CTA per (block of 8 query tokens, kv head).  Warp w owns query token t0 + w and the
@@ -392,8 +470,7 @@ __global__ void __launch_bounds__(256) k_silu_mul_rows(const float4 *__restrict_
     const long long t = i / F4, c = i % F4;            // c: float4 index inside the row; 8 float4 per 32-element block
     const long long src = t * 2 * F4 + (c / 8) * 16 + (c % 8);
     const float4 g = gu[src], u = gu[src + 8];
-    auto f = [](float a, float b) { return a / (1.0f + __expf(-a)) * b; };
-    out[i] = make_float4(f(g.x, u.x), f(g.y, u.y), f(g.z, u.z), f(g.w, u.w));
+    out[i] = make_float4(silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z), silu_mul(g.w, u.w));
 }
 
 __global__ void __launch_bounds__(256) k_add_inplace(float4 *__restrict__ a, const float4 *__restrict__ b, long long n4)
@@ -601,6 +678,47 @@ int inkq_glue_linear_m1(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev,
     INKQ_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(x_dev) & 15) == 0 && (g_dev == nullptr || (reinterpret_cast<uintptr_t>(g_dev) & 15) == 0),
                  "x and g must be 16-byte aligned");
     return launch_gemv_fused(ctx, w, x_dev, pro, g_dev, eps, C_dev, accumulate);
+}
+
+int inkq_glue_add_rmsnorm_quant_rows(inkq_ctx *ctx, float *x_dev, const float *delta_dev, const float *norm_w_dev, float eps, int M, int K,
+                                     inkq_act *out, int out_qmode, float *xn_out_dev)
+{
+    int rc = glue_use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, x_dev != nullptr && norm_w_dev != nullptr && out != nullptr, "null argument");
+    INKQ_REQUIRE(ctx, M >= 1 && K >= QK && K % QK == 0 && K <= 32768, "K must be a multiple of 32, at most 32768");
+    INKQ_REQUIRE(ctx, out->K == K && M <= out->max_rows, "the activation handle was created for another K or for fewer rows");
+    INKQ_REQUIRE(ctx, out_qmode == INKQ_Q8_1_F16 || out_qmode == INKQ_Q8_0_F16 || out_qmode == INKQ_Q8_1_F32, "bad output quantization mode");
+    const int M_ld = (M + 3) & ~3;
+    const size_t smem = static_cast<size_t>(K) * sizeof(float);
+    if (smem + 64 > 48 * 1024) {   // the kernel also holds 32 bytes of static shared memory
+        static std::mutex mu;
+        static bool configured[64] = {};
+        std::lock_guard<std::mutex> g(mu);
+        if (ctx->device < 0 || ctx->device >= 64) return fail(ctx, INKQ_ERR_INVALID, "device index out of range");
+        if (!configured[ctx->device]) {
+            INKQ_CUDA(ctx, cudaFuncSetAttribute(k_add_rmsnorm_quant_rows, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
+            configured[ctx->device] = true;
+        }
+    }
+    k_add_rmsnorm_quant_rows<<<M_ld, 256, smem, ctx->stream>>>(x_dev, delta_dev, norm_w_dev, M, K, eps, M_ld, out_qmode, out->q, out->d, out->s,
+                                                                out->isum, xn_out_dev);
+    out->M = M;
+    out->M_ld = M_ld;
+    out->qmode = out_qmode;
+    return after_launch(ctx, "k_add_rmsnorm_quant_rows");
+}
+
+int inkq_glue_silu_mul_quant_rows(inkq_ctx *ctx, const float *gu_dev, int M, int F, inkq_act *out, int out_qmode)
+{
+    int rc = glue_use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, gu_dev != nullptr && out != nullptr, "null argument");
+    INKQ_REQUIRE(ctx, M >= 1 && F >= QK && F % QK == 0, "F must be a multiple of 32");
+    INKQ_REQUIRE(ctx, out->K == F && M <= out->max_rows, "the activation handle was created for another K or for fewer rows");
+    INKQ_REQUIRE(ctx, out_qmode == INKQ_Q8_1_F16 || out_qmode == INKQ_Q8_0_F16 || out_qmode == INKQ_Q8_1_F32, "bad output quantization mode");
+    INKQ_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(gu_dev) & 15) == 0, "the input must be 16-byte aligned");
+    return launch_silu_mul_quantize(ctx, out_qmode, gu_dev, M, F, out);
 }
 
 int inkq_glue_add_inplace(inkq_ctx *ctx, float *a_dev, const float *b_dev, long long n)

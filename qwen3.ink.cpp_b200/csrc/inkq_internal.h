@@ -154,6 +154,8 @@ int after_launch(inkq_ctx *ctx, const char *what);
 
 // kernels' host launchers (defined in the respective .cu files)
 int launch_quantize(inkq_ctx *ctx, int qmode, const float *x, int M, int K, Act *a);
+// gu [M][2K] in (32 gate, 32 up) column groups -> the quantized rows of SiLU(gate) * up
+int launch_silu_mul_quantize(inkq_ctx *ctx, int qmode, const float *gu, int M, int K, Act *a);
 int launch_block_isum(inkq_ctx *ctx, Act *a, int M, int M_ld);
 int launch_retile(inkq_ctx *ctx, Weight *w, const uint8_t *nib, const float *d, const float *m, const uint8_t *zp, int n_begin);
 int launch_export(inkq_ctx *ctx, const Weight *w, uint8_t *nib, float *d, float *m, uint8_t *zp);

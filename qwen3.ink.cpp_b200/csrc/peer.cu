@@ -226,6 +226,28 @@ int inkq_linear_scatter(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev,
     return linear_impl(ctx, w, x_dev, M, reinterpret_cast<float *>(ps->ptr[ps->rank] + byte_offset), ldc, &extra);
 }
 
+int inkq_gemm_scatter(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, inkq_peerset *ps, size_t byte_offset, int ldc)
+{
+    if (ctx == nullptr) return fail(nullptr, INKQ_ERR_INVALID, "null context");
+    int rc = check_set(ctx, ps);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, act != nullptr && w != nullptr, "null handle");
+    INKQ_REQUIRE(ctx, act->M > 1, "the activation handle must hold more than one quantized row (one row: inkq_linear_scatter)");
+    INKQ_REQUIRE(ctx, act->K == w->K, "activation and weight K differ");
+    INKQ_REQUIRE(ctx, w->scheme != INKQ_W41, "a weight-only layer takes fp16 activations");
+    INKQ_REQUIRE(ctx, (w->scheme == INKQ_A81W41) == (act->qmode != INKQ_Q8_0_F16),
+                 "activation quantizer mode does not match the weight scheme (Q8_1 for A81W41, Q8_0 otherwise)");
+    INKQ_REQUIRE(ctx, byte_offset >= INKQ_PEER_RESERVED_BYTES && byte_offset % 4 == 0, "the offset must be a multiple of 4 past the reserved head");
+    INKQ_REQUIRE(ctx, ldc >= w->rows, "ldc is smaller than the number of weight rows");
+    const size_t last = byte_offset + (static_cast<size_t>(act->M - 1) * ldc + w->rows) * sizeof(float);
+    INKQ_REQUIRE(ctx, last <= ps->bytes, "the output does not fit into the peer buffers");
+    INKQ_CUDA(ctx, cudaSetDevice(ctx->device));
+    ExtraDst extra = {};
+    for (int p = 0; p < ps->world; p++)
+        if (p != ps->rank) extra.p[extra.n++] = reinterpret_cast<float *>(ps->ptr[p] + byte_offset);
+    return launch_gemm_tc(ctx, act, w, reinterpret_cast<float *>(ps->ptr[ps->rank] + byte_offset), ldc, nullptr, &extra);
+}
+
 int inkq_f16w_matmul_scatter(inkq_ctx *ctx, const inkq_f16w *w, const float *x_dev, int M, inkq_peerset *ps, size_t byte_offset, int ldc, int precision)
 {
     if (ctx == nullptr) return fail(nullptr, INKQ_ERR_INVALID, "null context");

@@ -24,6 +24,7 @@
 // bytes + rows*4 output bytes, i.e. 0.625 B per weight for A81W41.
 #include <cuda_fp16.h>
 
+#include "glue_math.cuh"
 #include "inkq_internal.h"
 #include "ptx.cuh"
 #include "qgemv_common.cuh"
@@ -81,7 +82,7 @@ __device__ __forceinline__ void fused_prologue(const FusedM1 &f, int K, uint32_t
         __syncthreads();
         float tot = 0.0f;
         for (int w2 = 0; w2 < nwarps; w2++) tot += red[w2];
-        inv = 1.0f / sqrtf(tot / static_cast<float>(K) + f.eps);
+        inv = rms_inv(tot, K, f.eps);
         __syncthreads();   // red is reused for the slice partials
     }
     for (int blk = threadIdx.x >> 1; blk < nb; blk += blockDim.x >> 1) {   // both lanes of a pair run the same trip count
@@ -95,11 +96,10 @@ __device__ __forceinline__ void fused_prologue(const FusedM1 &f, int K, uint32_t
             else t = reinterpret_cast<const float4 *>(f.x)[i4];
             if (f.pro == PRO_RMSNORM) {
                 const float4 gg = reinterpret_cast<const float4 *>(f.g)[i4];
-                t = make_float4(t.x * inv * gg.x, t.y * inv * gg.y, t.z * inv * gg.z, t.w * inv * gg.w);
+                t = rms_scale4(t, inv, gg);
             } else if (f.pro == PRO_SILU_MUL) {
                 const float4 u = reinterpret_cast<const float4 *>(f.x)[blk * 16 + 8 + 2 * j + half];                   // up half
-                auto act = [](float a, float b) { return a / (1.0f + __expf(-a)) * b; };
-                t = make_float4(act(t.x, u.x), act(t.y, u.y), act(t.z, u.z), act(t.w, u.w));
+                t = make_float4(silu_mul(t.x, u.x), silu_mul(t.y, u.y), silu_mul(t.z, u.z), silu_mul(t.w, u.w));
             }
             v[j] = t;
         }

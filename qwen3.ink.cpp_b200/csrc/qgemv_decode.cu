@@ -24,6 +24,7 @@
 #include <cuda_fp16.h>
 
 #include "inkq_glue.h"
+#include "glue_math.cuh"
 #include "inkq_internal.h"
 #include "ptx.cuh"
 #include "qgemv_common.cuh"
@@ -75,7 +76,7 @@ __device__ __forceinline__ void cta_rmsnorm_quant(const float *x, const float *g
     __syncthreads();
     float tot = 0.0f;
     for (int w2 = 0; w2 < nwarps; w2++) tot += red[w2];
-    const float inv = 1.0f / sqrtf(tot / static_cast<float>(n) + eps);
+    const float inv = rms_inv(tot, n, eps);
     for (int blk = threadIdx.x >> 1; blk < nb; blk += blockDim.x >> 1) {
         float4 v[4];
 #pragma unroll
@@ -83,7 +84,7 @@ __device__ __forceinline__ void cta_rmsnorm_quant(const float *x, const float *g
             const int i4 = blk * 8 + 2 * j + half;
             const float4 t = single_trip ? keep[j] : __ldcg(reinterpret_cast<const float4 *>(x) + i4);
             const float4 gg = single_trip ? gkeep[j] : reinterpret_cast<const float4 *>(g)[i4];
-            v[j] = make_float4(t.x * inv * gg.x, t.y * inv * gg.y, t.z * inv * gg.z, t.w * inv * gg.w);
+            v[j] = rms_scale4(t, inv, gg);
             if (xn != nullptr) reinterpret_cast<float4 *>(xn)[i4] = v[j];
         }
         float mx = 0.0f;
@@ -188,7 +189,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_decode
     if (epi.mode == EPI_PAIR_SILUQ) {
         if (warp == 0) {
             const int blk = blockIdx.x;                           // output block = CTA index: rows come in (gate32, up32) groups
-            const float a = tot[0] / (1.0f + __expf(-tot[0])) * tot[1];
+            const float a = silu_mul(tot[0], tot[1]);
             quantize_block_lanes(a, blk, lane, epi.out);
         }
         return;

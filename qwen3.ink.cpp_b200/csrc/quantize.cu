@@ -16,6 +16,7 @@
 // bytes written per element.
 #include <cuda_fp16.h>
 
+#include "glue_math.cuh"
 #include "inkq_internal.h"
 
 namespace inkq {
@@ -30,6 +31,10 @@ __device__ __forceinline__ uint32_t pack_sat_s8x4(int a, int b, int c, int d)
     return out;
 }
 
+// SILU_MUL: x is the output of a fused gate_up projection, [M][2K] in (32 gate, 32 up) column groups, and the
+// quantized row is SiLU(gate) * up (Qwen3SiLuMul, qwen3/src/qwen/QwenOperator.cc:697-722) - the same bits as
+// k_silu_mul_rows followed by the plain quantizer, without the fp32 round trip through memory.
+template <bool SILU_MUL>
 __global__ void __launch_bounds__(256) k_quantize_q8(const float4 *__restrict__ x, int M, int K, int M_ld, int mode,
                                                      int8_t *__restrict__ q, float *__restrict__ d, float *__restrict__ s,
                                                      int32_t *__restrict__ isum)
@@ -59,10 +64,22 @@ __global__ void __launch_bounds__(256) k_quantize_q8(const float4 *__restrict__ 
     }
     // lane `half` takes the float4s 2j + half of the block: each load instruction of the warp touches
     // 16 blocks x 32 contiguous bytes (whole sectors), four loads in flight per lane
-    const float4 *src = x + (static_cast<size_t>(m) * K + static_cast<size_t>(b) * QK) / 4 + half;
     float4 v[4];
+    if (SILU_MUL) {
+        const float4 *src = x + (static_cast<size_t>(m) * 2 * K + static_cast<size_t>(b) * 2 * QK) / 4 + half;
+        float4 g[4], u[4];
 #pragma unroll
-    for (int j = 0; j < 4; j++) v[j] = src[2 * j];
+        for (int j = 0; j < 4; j++) {
+            g[j] = src[2 * j];
+            u[j] = src[2 * j + QK / 4];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) v[j] = make_float4(silu_mul(g[j].x, u[j].x), silu_mul(g[j].y, u[j].y), silu_mul(g[j].z, u[j].z), silu_mul(g[j].w, u[j].w));
+    } else {
+        const float4 *src = x + (static_cast<size_t>(m) * K + static_cast<size_t>(b) * QK) / 4 + half;
+#pragma unroll
+        for (int j = 0; j < 4; j++) v[j] = src[2 * j];
+    }
     float mx = 0.0f;
 #pragma unroll
     for (int j = 0; j < 4; j++) mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
@@ -123,11 +140,23 @@ int launch_quantize(inkq_ctx *ctx, int qmode, const float *x, int M, int K, Act 
     const int M_ld = (M + 3) & ~3;
     const long long threads = static_cast<long long>(M_ld) * (K / QK) * 2;
     const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
-    k_quantize_q8<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<const float4 *>(x), M, K, M_ld, qmode, a->q, a->d, a->s, a->isum);
+    k_quantize_q8<false><<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<const float4 *>(x), M, K, M_ld, qmode, a->q, a->d, a->s, a->isum);
     a->M = M;
     a->M_ld = M_ld;
     a->qmode = qmode;
     return after_launch(ctx, "k_quantize_q8");
+}
+
+int launch_silu_mul_quantize(inkq_ctx *ctx, int qmode, const float *gu, int M, int K, Act *a)
+{
+    const int M_ld = (M + 3) & ~3;
+    const long long threads = static_cast<long long>(M_ld) * (K / QK) * 2;
+    const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
+    k_quantize_q8<true><<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<const float4 *>(gu), M, K, M_ld, qmode, a->q, a->d, a->s, a->isum);
+    a->M = M;
+    a->M_ld = M_ld;
+    a->qmode = qmode;
+    return after_launch(ctx, "k_quantize_q8<silu_mul>");
 }
 
 }  // namespace inkq

@@ -45,6 +45,8 @@ class Qwen3Config:
     lm_head_fp16: bool = True     # fp16 lm_head (benchmark config); False: A81W41 like the reference
     decode_mode: str = "epilogue"  # decode step: "epilogue" (norm / SiLU*up / quantizer in the producers' epilogues, 5 launches per
                                    # layer), "prologue" (in the QGEMV prologues, 6 launches) or "separate" (17 launches)
+    prefill_mode: str = "fused"    # prompt: "fused" (residual add + RMSNorm + quantizer in one kernel, SiLU*up inside the quantizer:
+                                   # 10 launches per layer) or "separate" (one kernel per operator, 15 launches); same bits
 
 
 def _p(t):
@@ -134,6 +136,15 @@ class Qwen3Synthetic:
             self.arena.close()
             self.arena = None
 
+    def _gemm(self, name, w, act, T, out):
+        """The same for T > 1 rows that a fused producer has already quantized into the activation handle `act`."""
+        if self.arena is None:
+            self.ctx.gemm(act, w, out, out.shape[1])
+            return out
+        self.arena.gemm(name, w, act, w.n_begin)
+        self.arena.barrier()
+        return self.arena.view(name, T)
+
     def _linear(self, name, w, x, T, out):
         """One quantized linear over T rows: on one GPU into `out`; sharded, into region `name` of every rank's arena
         (the returned tensor is then the assembled [T][N] matrix)."""
@@ -153,6 +164,9 @@ class Qwen3Synthetic:
             self.bufs[T] = dict(x=z(T, cfg.hidden), xn=z(T, cfg.hidden), qkv=z(T, qkv_n), q=z(T, cfg.nq * cfg.head_dim),
                                 attn=z(T, cfg.nq * cfg.head_dim), proj=z(T, cfg.hidden), gu=z(T, 2 * cfg.ffn),
                                 act=z(T, cfg.ffn), logits=z(1, cfg.vocab))
+            if T > 1:   # quantized rows handed from the fused prompt kernels to the QGEMMs
+                self.bufs[T]["qh"] = self.ctx.act(T, cfg.hidden)
+                self.bufs[T]["qf"] = self.ctx.act(T, cfg.ffn)
         return self.bufs[T]
 
     def _chk(self, rc):
@@ -169,7 +183,7 @@ class Qwen3Synthetic:
         H, F = cfg.hidden, cfg.ffn
         scale = 1.0 / float(np.sqrt(cfg.head_dim))
         self._chk(L.inkq_glue_embedding(h, _p(self.embed), _p(tokens_dev), T, H, cfg.vocab, _p(b["x"])))
-        mode = cfg.decode_mode if T == 1 else "separate"
+        mode = cfg.decode_mode if T == 1 else cfg.prefill_mode
         eps = C.c_float(cfg.eps)
         Q = self.pkg.Q8_1_F16
         if mode == "epilogue":
@@ -199,6 +213,26 @@ class Qwen3Synthetic:
             self._chk(L.inkq_glue_linear_m1(h, ly["o"].h, _p(b["attn"]), 0, None, eps, _p(b["x"]), 1))
             self._chk(L.inkq_glue_linear_m1(h, ly["gate_up"].h, _p(b["x"]), 1, _p(ly["ln2"]), eps, _p(b["gu"]), 0))
             self._chk(L.inkq_glue_linear_m1(h, ly["down"].h, _p(b["gu"]), 2, None, eps, _p(b["x"]), 1))
+        pending = None     # fused prompt path: the down projection's output, added to x by the next norm kernel
+        QM = self.pkg.Q8_1_F32    # what inkq_linear uses for an A81W41 layer with M > 1
+        for ly in (self.layers if mode == "fused" else []):
+            self._chk(L.inkq_glue_add_rmsnorm_quant_rows(h, _p(b["x"]), None if pending is None else _p(pending), _p(ly["ln1"]), eps, T, H,
+                                                         b["qh"].h, QM, None))
+            qkv = self._gemm("qkv", ly["qkv"], b["qh"], T, b["qkv"])
+            for sq in range(nseq):
+                rows = slice(sq * Ts, (sq + 1) * Ts)
+                self._chk(L.inkq_glue_qknorm_rope_cache(h, _p(qkv[rows]), _p(ly["qn"]), _p(ly["kn"]), _p(self.cos), _p(self.sin), _p(self.pos), Ts,
+                                                        cfg.nq, cfg.nkv, cfg.max_pos, eps, _p(b["q"][rows]), _p(ly["k_cache"][sq]),
+                                                        _p(ly["v_cache"][sq])))
+                self._chk(L.inkq_glue_attention(h, _p(b["q"][rows]), _p(ly["k_cache"][sq]), _p(ly["v_cache"][sq]), _p(self.pos), Ts, cfg.nq, cfg.nkv,
+                                                cfg.max_pos, C.c_float(scale), _p(b["attn"][rows])))
+            proj = self._linear("proj", ly["o"], b["attn"], T, b["proj"])
+            self._chk(L.inkq_glue_add_rmsnorm_quant_rows(h, _p(b["x"]), _p(proj), _p(ly["ln2"]), eps, T, H, b["qh"].h, QM, None))
+            gu = self._gemm("gu", ly["gate_up"], b["qh"], T, b["gu"])       # fused gate_up projection, (32 gate, 32 up) column groups
+            self._chk(L.inkq_glue_silu_mul_quant_rows(h, _p(gu), T, F, b["qf"].h, QM))
+            pending = self._gemm("proj", ly["down"], b["qf"], T, b["proj"])
+        if pending is not None:
+            self._chk(L.inkq_glue_add_inplace(h, _p(b["x"]), _p(pending), C.c_longlong(T * H)))
         for ly in (self.layers if mode == "separate" else []):
             self._chk(L.inkq_glue_rmsnorm(h, _p(b["x"]), _p(ly["ln1"]), T, H, C.c_float(cfg.eps), _p(b["xn"])))
             qkv = self._linear("qkv", ly["qkv"], b["xn"], T, b["qkv"])

@@ -162,6 +162,11 @@ class PeerArena:
         cols = self.shape[name][1]
         self.ctx.linear_scatter(w, x, M, self.ps, self.off[name] + 4 * n_begin, cols)
 
+    def gemm(self, name, w, act, n_begin: int):
+        """The same for rows that are already quantized into the activation handle `act`."""
+        cols = self.shape[name][1]
+        self.ctx.gemm_scatter(act, w, self.ps, self.off[name] + 4 * n_begin, cols)
+
     def f16w(self, name, w, x, M: int, n_begin: int, precision: int = 0):
         cols = self.shape[name][1]
         self.ctx.f16w_matmul_scatter(w, x, M, self.ps, self.off[name] + 4 * n_begin, cols, precision)

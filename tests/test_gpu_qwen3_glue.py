@@ -268,3 +268,77 @@ def test_batched_prefill_equals_separate_prefills(pkg, gpu):
         one = model.prefill(prompts[i].contiguous()).clone()
         gpu.synchronize()
         assert torch.equal(batched[i:i + 1], one)
+
+
+@pytest.mark.parametrize("M,K", [(5, 256), (37, 4096), (3, 12288), (2, 16384)])
+def test_prompt_add_rmsnorm_quantizer_in_one_kernel_equals_separate_operators(pkg, gpu, M, K):
+    """inkq_glue_add_rmsnorm_quant_rows against k_add_inplace + k_rmsnorm + the stand-alone quantizer: the same
+    element arithmetic in the same order, so x, the normalized rows and every quantized byte / scale / sum are equal."""
+    import ctypes as C
+    import torch
+    L, h = gpu.L, gpu.h
+    P = lambda t: C.c_void_p(t.data_ptr())
+    g = torch.Generator(device="cuda")
+    g.manual_seed(M * 131 + K)
+    x0 = torch.randn((M, K), device="cuda", generator=g) * 3.0
+    x0[0, 32:64] = 0.0                                          # a zero block
+    delta = torch.randn((M, K), device="cuda", generator=g)
+    w = torch.rand(K, device="cuda", generator=g) + 0.5
+    for qmode in (pkg.Q8_1_F32, pkg.Q8_1_F16, pkg.Q8_0_F16):
+        for with_delta in (True, False):
+            # separate operators
+            xs = x0.clone()
+            if with_delta:
+                gpu.check(L.inkq_glue_add_inplace(h, P(xs), P(delta), C.c_longlong(M * K)))
+            xn = torch.empty_like(xs)
+            gpu.check(L.inkq_glue_rmsnorm(h, P(xs), P(w), M, K, C.c_float(1e-6), P(xn)))
+            a_ref = gpu.act(M, K)
+            gpu.quantize(a_ref, xn, M, qmode)
+            # one kernel
+            xf = x0.clone()
+            xn_f = torch.empty_like(xf)
+            a_got = gpu.act(M + 3, K)
+            gpu.check(L.inkq_glue_add_rmsnorm_quant_rows(h, P(xf), P(delta) if with_delta else None, P(w), C.c_float(1e-6), M, K, a_got.h, qmode,
+                                                         P(xn_f)))
+            gpu.synchronize()
+            assert torch.equal(xf, xs) and torch.equal(xn_f, xn)
+            for got, ref in zip(a_got.export(M), a_ref.export(M)):
+                assert np.array_equal(got, ref)
+
+
+@pytest.mark.parametrize("M,F", [(1, 64), (37, 1024), (322, 12288)])
+def test_prompt_silu_mul_inside_the_quantizer_equals_separate_operators(pkg, gpu, M, F):
+    import ctypes as C
+    import torch
+    L, h = gpu.L, gpu.h
+    P = lambda t: C.c_void_p(t.data_ptr())
+    g = torch.Generator(device="cuda")
+    g.manual_seed(M + F)
+    gu = torch.randn((M, 2 * F), device="cuda", generator=g) * 4.0
+    act = torch.empty((M, F), device="cuda")
+    gpu.check(L.inkq_glue_silu_mul_rows(h, P(gu), M, F, P(act)))
+    for qmode in (pkg.Q8_1_F32, pkg.Q8_0_F16):
+        a_ref, a_got = gpu.act(M, F), gpu.act(M, F)
+        gpu.quantize(a_ref, act, M, qmode)
+        gpu.check(L.inkq_glue_silu_mul_quant_rows(h, P(gu), M, F, a_got.h, qmode))
+        gpu.synchronize()
+        for got, ref in zip(a_got.export(M), a_ref.export(M)):
+            assert np.array_equal(got, ref)
+
+
+def test_fused_prompt_path_equals_separate_operators(pkg, gpu):
+    """The whole prompt forward with the fused kernels (10 launches per layer) gives the logits of the one-kernel-per-operator
+    path bit for bit, for one prompt and for a batch of prompts."""
+    import torch
+    toks = torch.from_numpy(pkg.synth.tokens(45, 1024, 8)).cuda()
+    out = {}
+    for mode in ("separate", "fused"):
+        model = pkg.qwen3_forward.Qwen3Synthetic(pkg, gpu, small_cfg(pkg, prefill_mode=mode), seed=4, batch=3)
+        model.reset()
+        one = model.prefill(toks).clone()
+        model.reset()
+        many = model.prefill_batch(toks[:42].reshape(3, 14).contiguous()).clone()
+        gpu.synchronize()
+        out[mode] = (one, many)
+    assert torch.equal(out["fused"][0], out["separate"][0])
+    assert torch.equal(out["fused"][1], out["separate"][1])
