@@ -66,7 +66,7 @@ int inkq_glue_rmsnorm_quant(inkq_ctx *ctx, const float *x_dev, const float *norm
 int inkq_glue_attention_quant(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev,
                               int nq, int nkv, int max_pos, float scale, inkq_act *out, int out_qmode);
 /* ---- prompt path with the element-wise operators folded into the quantizer ------------------
- * No counterpart in the reference (separate operators on host matrices, QwenDecoderLayer.cc:57-105).  Both write the
+ * No counterpart in the reference (separate operators on host matrices, QwenDecoderLayer.cc:57-105).  They write the
  * quantized rows straight into an activation handle (inkq_act_create(ctx, rows >= M, K)) that inkq_gemm then
  * consumes; the bits equal those of the separate operators followed by inkq_quantize.
  *   inkq_glue_add_rmsnorm_quant_rows: x[M][K] += delta[M][K] (skipped when delta_dev is NULL; x is updated in place),
@@ -76,6 +76,11 @@ int inkq_glue_attention_quant(inkq_ctx *ctx, const float *q_dev, const uint16_t 
 int inkq_glue_add_rmsnorm_quant_rows(inkq_ctx *ctx, float *x_dev, const float *delta_dev, const float *norm_w_dev, float eps, int M, int K,
                                      inkq_act *out, int out_qmode, float *xn_out_dev);
 int inkq_glue_silu_mul_quant_rows(inkq_ctx *ctx, const float *gu_dev, int M, int F, inkq_act *out, int out_qmode);
+/* inkq_glue_attention for T tokens of one prompt with its output quantized into rows row0 .. row0 + T - 1 of `out`
+ * (created for K = nq * 128 and at least total_rows rows; a batch of prompts calls it once per prompt with the same
+ * total_rows, and the handle is complete when every row has been written).  At most 4 query heads per kv head. */
+int inkq_glue_attention_quant_rows(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev,
+                                   int T, int nq, int nkv, int max_pos, float scale, inkq_act *out, int out_qmode, int row0, int total_rows);
 /* a += b (residual).  qwen3/src/qwen/QwenDecoderLayer.cc:73,105 */
 int inkq_glue_add_inplace(inkq_ctx *ctx, float *a_dev, const float *b_dev, long long n);
 /* Greedy sampling: *token_out = argmax(logits) (first index on ties), appended to generated

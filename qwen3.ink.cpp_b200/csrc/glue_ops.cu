@@ -319,7 +319,8 @@ __global__ void __launch_bounds__(256) k_silu_mul(const float4 *__restrict__ gat
 constexpr int ATT_QT = 8, ATT_GMAX = 4, ATT_KT = 32, ATT_KROW = HEAD_DIM + 8;   // padded key rows: conflict-free 16-byte reads
 __global__ void __launch_bounds__(256) k_attention_prefill(const float *__restrict__ q, const __half *__restrict__ k_cache,
                                                            const __half *__restrict__ v_cache, const int *__restrict__ pos0_dev, int T, int nq,
-                                                           int nkv, int max_pos, float scale, float *__restrict__ out)
+                                                           int nkv, int max_pos, float scale, float *__restrict__ out, const QuantOut qo,
+                                                           int qrow0)
 {
     __shared__ __align__(16) float qs[ATT_QT][ATT_GMAX][HEAD_DIM];
     __shared__ __align__(16) __half ks[ATT_KT][ATT_KROW];
@@ -455,9 +456,45 @@ __global__ void __launch_bounds__(256) k_attention_prefill(const float *__restri
         for (int hh = 0; hh < ATT_GMAX; hh++) {
             if (hh < G) {
                 const float inv = 1.0f / lrun[hh];
-                reinterpret_cast<float4 *>(out + (static_cast<size_t>(t) * nq + g * G + hh) * HEAD_DIM)[lane] =
-                    make_float4(acc[hh][0] * inv, acc[hh][1] * inv, acc[hh][2] * inv, acc[hh][3] * inv);
+                const float4 o = make_float4(acc[hh][0] * inv, acc[hh][1] * inv, acc[hh][2] * inv, acc[hh][3] * inv);
+                if (out != nullptr) reinterpret_cast<float4 *>(out + (static_cast<size_t>(t) * nq + g * G + hh) * HEAD_DIM)[lane] = o;
+                if (qo.q != nullptr) {
+                    // the head's 128 outputs are four quantization blocks of row qrow0 + t of the output projection's
+                    // input, eight lanes each; same arithmetic as the stand-alone quantizer
+                    float mx = fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w)));
+#pragma unroll
+                    for (int sh = 1; sh < 8; sh <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sh));
+                    const float dd = __fdiv_rn(mx, 127.0f);
+                    const float id = (mx != 0.0f) ? __fdiv_rn(127.0f, mx) : 0.0f;
+                    const int i0 = __float2int_rn(__fmul_rn(o.x, id)), i1 = __float2int_rn(__fmul_rn(o.y, id));
+                    const int i2 = __float2int_rn(__fmul_rn(o.z, id)), i3 = __float2int_rn(__fmul_rn(o.w, id));
+                    int sum = (i0 + i1) + (i2 + i3);
+#pragma unroll
+                    for (int sh = 1; sh < 8; sh <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, sh);
+                    const int row = qrow0 + t, head = g * G + hh;
+                    reinterpret_cast<uint32_t *>(qo.q)[(static_cast<size_t>(row) * nq + head) * (HEAD_DIM / 4) + lane] = pack_sat_s8x4_m1(i0, i1, i2, i3);
+                    if ((lane & 7) == 0) {
+                        const size_t pl = static_cast<size_t>(head * (HEAD_DIM / QK) + (lane >> 3)) * qo.M_ld + row;
+                        const float sv = __fmul_rn(dd, static_cast<float>(sum));
+                        if (qo.qmode == INKQ_Q8_1_F32) {
+                            qo.d[pl] = dd;
+                            qo.s[pl] = sv;
+                        } else {
+                            qo.d[pl] = __half2float(__float2half_rn(dd));
+                            qo.s[pl] = (qo.qmode == INKQ_Q8_1_F16) ? __half2float(__float2half_rn(sv)) : 0.0f;
+                        }
+                        qo.isum[pl] = sum;
+                    }
+                }
             }
+        }
+    } else if (qo.q != nullptr && qrow0 + t < qo.M_ld) {
+        // padding rows of the scale planes (only the call that holds the last rows reaches them) read as zero
+        for (int b = lane; b < G * (HEAD_DIM / QK); b += 32) {
+            const size_t pl = static_cast<size_t>(g * G * (HEAD_DIM / QK) + b) * qo.M_ld + qrow0 + t;
+            qo.d[pl] = 0.0f;
+            qo.s[pl] = 0.0f;
+            qo.isum[pl] = 0;
         }
     }
 }
@@ -595,7 +632,7 @@ int inkq_glue_qknorm_rope_cache(inkq_ctx *ctx, const float *qkv_dev, const float
 }
 
 static int attention_impl(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev, int T,
-                          int nq, int nkv, int max_pos, float scale, float *out_dev, const QuantOut &qo);
+                          int nq, int nkv, int max_pos, float scale, float *out_dev, const QuantOut &qo, int qrow0 = 0);
 
 int inkq_glue_attention(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev, int T,
                         int nq, int nkv, int max_pos, float scale, float *out_dev)
@@ -616,16 +653,41 @@ int inkq_glue_attention_quant(inkq_ctx *ctx, const float *q_dev, const uint16_t 
     return attention_impl(ctx, q_dev, k_cache_dev, v_cache_dev, pos0_dev, 1, nq, nkv, max_pos, scale, nullptr, quant_out_of(out, nq * HEAD_DIM, out_qmode));
 }
 
+int inkq_glue_attention_quant_rows(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev,
+                                   int T, int nq, int nkv, int max_pos, float scale, inkq_act *out, int out_qmode, int row0, int total_rows)
+{
+    int rc = glue_use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, out != nullptr && out->K == nq * HEAD_DIM, "the output activation handle must have been created for K = nq * 128");
+    INKQ_REQUIRE(ctx, out_qmode == INKQ_Q8_1_F16 || out_qmode == INKQ_Q8_0_F16 || out_qmode == INKQ_Q8_1_F32, "bad output quantization mode");
+    INKQ_REQUIRE(ctx, T >= 1 && row0 >= 0 && row0 + T <= total_rows && total_rows <= out->max_rows, "rows outside the activation handle");
+    QuantOut qo;
+    qo.q = out->q;
+    qo.d = out->d;
+    qo.s = out->s;
+    qo.isum = out->isum;
+    qo.M_ld = (total_rows + 3) & ~3;
+    qo.qmode = out_qmode;
+    out->M = total_rows;
+    out->M_ld = qo.M_ld;
+    out->qmode = out_qmode;
+    // a one-row handle keeps the layout of the decode-step kernel; everything else goes through the prompt kernel
+    if (total_rows == 1) return attention_impl(ctx, q_dev, k_cache_dev, v_cache_dev, pos0_dev, 1, nq, nkv, max_pos, scale, nullptr, qo);
+    return attention_impl(ctx, q_dev, k_cache_dev, v_cache_dev, pos0_dev, T, nq, nkv, max_pos, scale, nullptr, qo, row0);
+}
+
 static int attention_impl(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev, int T,
-                          int nq, int nkv, int max_pos, float scale, float *out_dev, const QuantOut &qo)
+                          int nq, int nkv, int max_pos, float scale, float *out_dev, const QuantOut &qo, int qrow0)
 {
     int rc = INKQ_OK;
     INKQ_REQUIRE(ctx, q_dev && k_cache_dev && v_cache_dev && pos0_dev, "null argument");
     INKQ_REQUIRE(ctx, T >= 1 && nq % nkv == 0 && max_pos >= 1, "bad head configuration");
-    if (T >= 16 && nq / nkv <= ATT_GMAX) {   // a prompt: key/value tiles shared by 8 tokens x the heads of a kv group
+    const bool quant_rows = qo.q != nullptr && (T > 1 || qrow0 > 0 || qo.M_ld > 4);
+    INKQ_REQUIRE(ctx, !quant_rows || nq / nkv <= ATT_GMAX, "the quantizing prompt attention serves at most 4 query heads per kv head");
+    if ((T >= 16 || quant_rows) && nq / nkv <= ATT_GMAX) {   // a prompt: key/value tiles shared by 8 tokens x the heads of a kv group
         k_attention_prefill<<<dim3((T + ATT_QT - 1) / ATT_QT, nkv), 256, 0, ctx->stream>>>(
             q_dev, reinterpret_cast<const __half *>(k_cache_dev), reinterpret_cast<const __half *>(v_cache_dev), pos0_dev, T, nq, nkv, max_pos,
-            scale, out_dev);
+            scale, out_dev, qo, qrow0);
         return after_launch(ctx, "k_attention_prefill");
     }
     // few (token, head) items (a decode step): 16 warps per item so that the item's keys are spread over more

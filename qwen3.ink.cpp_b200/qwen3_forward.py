@@ -45,8 +45,9 @@ class Qwen3Config:
     lm_head_fp16: bool = True     # fp16 lm_head (benchmark config); False: A81W41 like the reference
     decode_mode: str = "epilogue"  # decode step: "epilogue" (norm / SiLU*up / quantizer in the producers' epilogues, 5 launches per
                                    # layer), "prologue" (in the QGEMV prologues, 6 launches) or "separate" (17 launches)
-    prefill_mode: str = "fused"    # prompt: "fused" (residual add + RMSNorm + quantizer in one kernel, SiLU*up inside the quantizer:
-                                   # 10 launches per layer) or "separate" (one kernel per operator, 15 launches); same bits
+    prefill_mode: str = "fused"    # prompt: "fused" (residual add + RMSNorm + quantizer in one kernel, SiLU*up inside the quantizer,
+                                   # attention quantizes its own output: 9 launches per layer) or "separate" (one kernel per
+                                   # operator, 15 launches); same bits
 
 
 def _p(t):
@@ -167,6 +168,7 @@ class Qwen3Synthetic:
             if T > 1:   # quantized rows handed from the fused prompt kernels to the QGEMMs
                 self.bufs[T]["qh"] = self.ctx.act(T, cfg.hidden)
                 self.bufs[T]["qf"] = self.ctx.act(T, cfg.ffn)
+                self.bufs[T]["qa"] = self.ctx.act(T, cfg.nq * cfg.head_dim)
         return self.bufs[T]
 
     def _chk(self, rc):
@@ -224,9 +226,9 @@ class Qwen3Synthetic:
                 self._chk(L.inkq_glue_qknorm_rope_cache(h, _p(qkv[rows]), _p(ly["qn"]), _p(ly["kn"]), _p(self.cos), _p(self.sin), _p(self.pos), Ts,
                                                         cfg.nq, cfg.nkv, cfg.max_pos, eps, _p(b["q"][rows]), _p(ly["k_cache"][sq]),
                                                         _p(ly["v_cache"][sq])))
-                self._chk(L.inkq_glue_attention(h, _p(b["q"][rows]), _p(ly["k_cache"][sq]), _p(ly["v_cache"][sq]), _p(self.pos), Ts, cfg.nq, cfg.nkv,
-                                                cfg.max_pos, C.c_float(scale), _p(b["attn"][rows])))
-            proj = self._linear("proj", ly["o"], b["attn"], T, b["proj"])
+                self._chk(L.inkq_glue_attention_quant_rows(h, _p(b["q"][rows]), _p(ly["k_cache"][sq]), _p(ly["v_cache"][sq]), _p(self.pos), Ts, cfg.nq,
+                                                           cfg.nkv, cfg.max_pos, C.c_float(scale), b["qa"].h, QM, sq * Ts, T))
+            proj = self._gemm("proj", ly["o"], b["qa"], T, b["proj"])
             self._chk(L.inkq_glue_add_rmsnorm_quant_rows(h, _p(b["x"]), _p(proj), _p(ly["ln2"]), eps, T, H, b["qh"].h, QM, None))
             gu = self._gemm("gu", ly["gate_up"], b["qh"], T, b["gu"])       # fused gate_up projection, (32 gate, 32 up) column groups
             self._chk(L.inkq_glue_silu_mul_quant_rows(h, _p(gu), T, F, b["qf"].h, QM))

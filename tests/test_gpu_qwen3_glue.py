@@ -327,18 +327,54 @@ def test_prompt_silu_mul_inside_the_quantizer_equals_separate_operators(pkg, gpu
 
 
 def test_fused_prompt_path_equals_separate_operators(pkg, gpu):
-    """The whole prompt forward with the fused kernels (10 launches per layer) gives the logits of the one-kernel-per-operator
+    """The whole prompt forward with the fused kernels (9 launches per layer) gives the logits of the one-kernel-per-operator
     path bit for bit, for one prompt and for a batch of prompts."""
     import torch
-    toks = torch.from_numpy(pkg.synth.tokens(45, 1024, 8)).cuda()
+    toks = torch.from_numpy(pkg.synth.tokens(48, 1024, 8)).cuda()
     out = {}
     for mode in ("separate", "fused"):
         model = pkg.qwen3_forward.Qwen3Synthetic(pkg, gpu, small_cfg(pkg, prefill_mode=mode), seed=4, batch=3)
         model.reset()
-        one = model.prefill(toks).clone()
+        one = model.prefill(toks[:45]).clone()
         model.reset()
-        many = model.prefill_batch(toks[:42].reshape(3, 14).contiguous()).clone()
+        # (prompts of at least 16 tokens: below that the stand-alone attention call takes its per-(token, head) kernel,
+        # whose summation order differs from the prompt kernel's)
+        many = model.prefill_batch(toks.reshape(3, 16).contiguous()).clone()
         gpu.synchronize()
         out[mode] = (one, many)
     assert torch.equal(out["fused"][0], out["separate"][0])
     assert torch.equal(out["fused"][1], out["separate"][1])
+
+
+@pytest.mark.parametrize("T,prompts", [(45, 1), (14, 3), (2, 1)])
+def test_prompt_attention_quantizing_its_output_equals_attention_then_quantizer(pkg, gpu, T, prompts):
+    import ctypes as C
+    import torch
+    L, h = gpu.L, gpu.h
+    P = lambda t: C.c_void_p(t.data_ptr())
+    nq, nkv, max_pos, hd = 8, 2, 64, 128
+    g = torch.Generator(device="cuda")
+    g.manual_seed(T)
+    rows = T * prompts
+    q = torch.randn((rows, nq * hd), device="cuda", generator=g)
+    kc = torch.randn((prompts, nkv, max_pos, hd), device="cuda", generator=g).half()
+    vc = torch.randn((prompts, nkv, max_pos, hd), device="cuda", generator=g).half()
+    pos = torch.tensor([3], dtype=torch.int32, device="cuda")
+    scale = C.c_float(1.0 / np.sqrt(hd))
+    for qmode in (pkg.Q8_1_F32, pkg.Q8_0_F16):
+        out = torch.empty((rows, nq * hd), device="cuda")
+        a_ref, a_got = gpu.act(rows, nq * hd), gpu.act(rows + 2, nq * hd)
+        for p in range(prompts):
+            r = slice(p * T, (p + 1) * T)
+            gpu.check(L.inkq_glue_attention(h, P(q[r]), P(kc[p]), P(vc[p]), P(pos), T, nq, nkv, max_pos, scale, P(out[r])))
+            gpu.check(L.inkq_glue_attention_quant_rows(h, P(q[r]), P(kc[p]), P(vc[p]), P(pos), T, nq, nkv, max_pos, scale, a_got.h, qmode, p * T, rows))
+        gpu.quantize(a_ref, out, rows, qmode)
+        gpu.synchronize()
+        if T < 16:   # the stand-alone call takes the per-(token, head) kernel there: other summation order, compare the values
+            qv, d, _, _ = a_got.export(rows)
+            deq = (qv.reshape(rows, -1, 32).astype(np.float32) * d[:, :, None]).reshape(rows, -1)
+            ref = out.cpu().numpy()
+            assert np.abs(deq - ref).max() <= np.abs(ref).max() / 127 * 0.51 + 1e-5
+        else:
+            for got, ref in zip(a_got.export(rows), a_ref.export(rows)):
+                assert np.array_equal(got, ref)
