@@ -302,6 +302,148 @@ __global__ void __launch_bounds__(NT) k_attention(const float *__restrict__ q, c
     }
 }
 
+// Decode-step attention split over the keys: ATT_S CTAs per query head, each takes a contiguous share of the
+// keys 0 .. pos0 (so a head's 2 x 256 bytes per key come in through ATT_S times as many loads in flight; a decode
+// step has one query token and would otherwise run on nq of the SMs).  A CTA leaves an unnormalized partial
+// (running max, sum of exponentials, 128 weighted value sums); the CTA of a head that finishes last (ticket counter,
+// nobody waits) merges the partials in ascending split order - the result does not depend on which CTA merges - and
+// writes and/or quantizes the head's output.  Scores: four threads per key (32 dimensions each, xor-shuffle);
+// values: warp w takes keys w, w + 16, ... of the share, lane = 4 output dimensions.
+#ifndef INKQ_ATT_S
+#define INKQ_ATT_S 4   // tuning knob: shares per head
+#endif
+constexpr int ATT_S = INKQ_ATT_S, ATT_SPLIT_NT = 512, ATT_SPLIT_NW = ATT_SPLIT_NT / 32;
+static_assert(ATT_S >= 1 && ATT_S <= ATT_MAX_SPLITS, "more shares than the scratch holds");
+__global__ void __launch_bounds__(ATT_SPLIT_NT) k_attention_split(const float *__restrict__ q, const __half *__restrict__ k_cache,
+                                                                  const __half *__restrict__ v_cache, const int *__restrict__ pos0_dev, int nq,
+                                                                  int nkv, int max_pos, float scale, float *__restrict__ out, const QuantOut qo,
+                                                                  float *__restrict__ partials, unsigned *__restrict__ counters)
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    extern __shared__ float sm[];
+    float *qs = sm;                               // 128
+    float *part = sm + HEAD_DIM;                  // NW * 128
+    float *red = part + ATT_SPLIT_NW * HEAD_DIM;  // 2 * NW
+    float *sc = red + 2 * ATT_SPLIT_NW;           // scores of the share
+    __shared__ unsigned ticket_s;
+    const int h = blockIdx.x / ATT_S, sp = blockIdx.x % ATT_S;
+    const int kvh = h / (nq / nkv);
+    const int nkeys = min(*pos0_dev + 1, max_pos);
+    const int share = (nkeys + ATT_S - 1) / ATT_S;
+    const int k0 = min(sp * share, nkeys), n = min(nkeys - k0, share);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < HEAD_DIM) qs[tid] = q[static_cast<size_t>(h) * HEAD_DIM + tid];
+    __syncthreads();
+    const __half *kb = k_cache + (static_cast<size_t>(kvh) * max_pos + k0) * HEAD_DIM;
+    const __half *vb = v_cache + (static_cast<size_t>(kvh) * max_pos + k0) * HEAD_DIM;
+    const int sub = tid & 3;
+    float lmax = -INFINITY;
+    for (int jb = 0; jb < n; jb += ATT_SPLIT_NT / 4) {
+        const int j = jb + (tid >> 2);
+        float acc = 0.0f;
+        if (j < n) {
+            const uint4 *kr = reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(j) * HEAD_DIM) + sub * 4;
+            uint4 pk[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) pk[u] = kr[u];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const uint32_t wd[4] = {pk[u].x, pk[u].y, pk[u].z, pk[u].w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&wd[i]));
+                    acc = fmaf(qs[sub * 32 + u * 8 + 2 * i], f.x, acc);
+                    acc = fmaf(qs[sub * 32 + u * 8 + 2 * i + 1], f.y, acc);
+                }
+            }
+        }
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        if (j < n) {
+            acc *= scale;
+            if (sub == 0) sc[j] = acc;
+            lmax = fmaxf(lmax, acc);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
+    if (lane == 0) red[warp] = lmax;
+    __syncthreads();
+    float gmax = red[0];
+#pragma unroll
+    for (int i = 1; i < ATT_SPLIT_NW; i++) gmax = fmaxf(gmax, red[i]);
+    float lsum = 0.0f;
+    for (int j = tid; j < n; j += ATT_SPLIT_NT) {
+        const float e = __expf(sc[j] - gmax);
+        sc[j] = e;
+        lsum += e;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+    if (lane == 0) red[ATT_SPLIT_NW + warp] = lsum;
+    __syncthreads();
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+    for (int j = warp; j < n; j += ATT_SPLIT_NW) {
+        const float pj = sc[j];
+        const uint2 pk = reinterpret_cast<const uint2 *>(vb + static_cast<size_t>(j) * HEAD_DIM)[lane];
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.x));
+        const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.y));
+        a[0] = fmaf(pj, f0.x, a[0]);
+        a[1] = fmaf(pj, f0.y, a[1]);
+        a[2] = fmaf(pj, f1.x, a[2]);
+        a[3] = fmaf(pj, f1.y, a[3]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) part[warp * HEAD_DIM + lane * 4 + i] = a[i];
+    __syncthreads();
+    float *mine = partials + (static_cast<size_t>(h) * ATT_MAX_SPLITS + sp) * ATT_PART_WORDS;
+    if (tid < HEAD_DIM) {
+        float o = 0.0f;
+#pragma unroll
+        for (int i = 0; i < ATT_SPLIT_NW; i++) o += part[i * HEAD_DIM + tid];
+        mine[tid] = o;
+        if (tid == 0) {
+            float den = 0.0f;
+#pragma unroll
+            for (int i = 0; i < ATT_SPLIT_NW; i++) den += red[ATT_SPLIT_NW + i];
+            mine[HEAD_DIM] = (n > 0) ? gmax : -INFINITY;
+            mine[HEAD_DIM + 1] = den;
+        }
+        __threadfence();   // every storing thread: its partial before the ticket
+    }
+    __syncthreads();
+    if (tid == 0) ticket_s = atomicAdd(counters + h, 1u);
+    __syncthreads();
+    if (ticket_s != ATT_S - 1) return;
+    __threadfence();       // the other shares' partials before the reads below
+    if (tid < HEAD_DIM) {
+        const float *ph = partials + static_cast<size_t>(h) * ATT_MAX_SPLITS * ATT_PART_WORDS;
+        float m[ATT_S], l[ATT_S], o[ATT_S];
+#pragma unroll
+        for (int s2 = 0; s2 < ATT_S; s2++) {
+            m[s2] = __ldcg(ph + s2 * ATT_PART_WORDS + HEAD_DIM);
+            l[s2] = __ldcg(ph + s2 * ATT_PART_WORDS + HEAD_DIM + 1);
+            o[s2] = __ldcg(ph + s2 * ATT_PART_WORDS + tid);
+        }
+        float mm = m[0];   // share 0 always holds key 0
+#pragma unroll
+        for (int s2 = 1; s2 < ATT_S; s2++) mm = fmaxf(mm, m[s2]);
+        float den = 0.0f, num = 0.0f;
+#pragma unroll
+        for (int s2 = 0; s2 < ATT_S; s2++) {
+            const float w = __expf(m[s2] - mm);   // 0 for an empty share
+            den = fmaf(l[s2], w, den);
+            num = fmaf(o[s2], w, num);
+        }
+        const float res = num / den;
+        if (out != nullptr) out[static_cast<size_t>(h) * HEAD_DIM + tid] = res;
+        if (qo.q != nullptr) quantize_block_lanes(res, h * (HEAD_DIM / QK) + warp, lane, qo);
+    }
+    if (tid == 0) counters[h] = 0u;   // ready for the next launch
+}
+
 __global__ void __launch_bounds__(256) k_silu_mul(const float4 *__restrict__ gate, const float4 *__restrict__ up, long long n4,
                                                   float4 *__restrict__ out)
 {
@@ -671,6 +813,7 @@ int inkq_glue_attention_quant_rows(inkq_ctx *ctx, const float *q_dev, const uint
     out->M = total_rows;
     out->M_ld = qo.M_ld;
     out->qmode = out_qmode;
+    out->ssq_parts = 0;
     // a one-row handle keeps the layout of the decode-step kernel; everything else goes through the prompt kernel
     if (total_rows == 1) return attention_impl(ctx, q_dev, k_cache_dev, v_cache_dev, pos0_dev, 1, nq, nkv, max_pos, scale, nullptr, qo);
     return attention_impl(ctx, q_dev, k_cache_dev, v_cache_dev, pos0_dev, T, nq, nkv, max_pos, scale, nullptr, qo, row0);
@@ -689,6 +832,18 @@ static int attention_impl(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_c
             q_dev, reinterpret_cast<const __half *>(k_cache_dev), reinterpret_cast<const __half *>(v_cache_dev), pos0_dev, T, nq, nkv, max_pos,
             scale, out_dev, qo, qrow0);
         return after_launch(ctx, "k_attention_prefill");
+    }
+    if (T == 1 && nq <= ATT_MAX_HEADS && nq * ATT_S <= 2 * ctx->num_sms && !quant_rows) {
+        // a decode step: the keys of each head split over ATT_S CTAs, merged by the one that finishes last
+        const int share_max = (max_pos + ATT_S - 1) / ATT_S;
+        const size_t smem_s = sizeof(float) * (HEAD_DIM + ATT_SPLIT_NW * HEAD_DIM + 2 * ATT_SPLIT_NW + static_cast<size_t>(share_max));
+        INKQ_REQUIRE(ctx, smem_s <= 200 * 1024, "context too long for the decode attention kernel");
+        if (smem_s > 48 * 1024) cudaFuncSetAttribute(k_attention_split, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_s));
+        unsigned *counters = reinterpret_cast<unsigned *>(ctx->dev_flag) + 4;
+        float *partials = reinterpret_cast<float *>(ctx->dev_flag) + 4 + ATT_MAX_HEADS;
+        launch_pdl(k_attention_split, dim3(nq * ATT_S), dim3(ATT_SPLIT_NT), smem_s, ctx->stream, q_dev, reinterpret_cast<const __half *>(k_cache_dev),
+                   reinterpret_cast<const __half *>(v_cache_dev), pos0_dev, nq, nkv, max_pos, scale, out_dev, qo, partials, counters);
+        return after_launch(ctx, "k_attention_split");
     }
     // few (token, head) items (a decode step): 16 warps per item so that the item's keys are spread over more
     // loads in flight; many items (a prompt): 4 warps per item, the grid fills the machine
@@ -768,6 +923,7 @@ int inkq_glue_add_rmsnorm_quant_rows(inkq_ctx *ctx, float *x_dev, const float *d
     out->M = M;
     out->M_ld = M_ld;
     out->qmode = out_qmode;
+    out->ssq_parts = 0;
     return after_launch(ctx, "k_add_rmsnorm_quant_rows");
 }
 

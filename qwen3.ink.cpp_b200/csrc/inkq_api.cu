@@ -70,6 +70,7 @@ static void free_act(Act *a)
     cudaFree(a->d);
     cudaFree(a->s);
     cudaFree(a->isum);
+    cudaFree(a->ssq);
 }
 
 static int check_weight_args(inkq_ctx *ctx, int scheme, int scale_mode, int N, int K, const void *nib, const void *d, const void *m,
@@ -169,8 +170,8 @@ int inkq_ctx_create(int device, void *stream, inkq_ctx **out)
     }
     ctx->num_sms = prop.multiProcessorCount;
     // word 0: set by a kernel whose bounded wait ran out; word 1: ticket counter of the decode GEMV's last-CTA epilogue
-    if ((e = cudaMalloc(reinterpret_cast<void **>(&ctx->dev_flag), 4 * sizeof(int))) != cudaSuccess ||
-        (e = cudaMemset(ctx->dev_flag, 0, 4 * sizeof(int))) != cudaSuccess) {
+    if ((e = cudaMalloc(reinterpret_cast<void **>(&ctx->dev_flag), CTX_FLAG_WORDS * sizeof(int))) != cudaSuccess ||
+        (e = cudaMemset(ctx->dev_flag, 0, CTX_FLAG_WORDS * sizeof(int))) != cudaSuccess) {
         delete ctx;
         return fail(nullptr, INKQ_ERR_ALLOC, std::string("context allocation: ") + cudaGetErrorString(e));
     }
@@ -356,6 +357,7 @@ int inkq_act_create(inkq_ctx *ctx, int max_rows, int K, inkq_act **out)
     if (!rc) rc = dev_alloc(ctx, &a->d, ld * nb);
     if (!rc) rc = dev_alloc(ctx, &a->s, ld * nb);
     if (!rc) rc = dev_alloc(ctx, &a->isum, ld * nb);
+    if (!rc) rc = dev_alloc(ctx, &a->ssq, static_cast<size_t>(ACT_SSQ_CAP));
     if (rc) {
         free_act(a);
         delete a;
@@ -470,6 +472,7 @@ int inkq_act_import(inkq_ctx *ctx, inkq_act *act, int qmode, int M, const int8_t
     act->M = M;
     act->M_ld = static_cast<int>(ld);
     act->qmode = qmode;
+    act->ssq_parts = 0;
     return INKQ_OK;
 }
 
@@ -478,6 +481,7 @@ static int check_mm(inkq_ctx *ctx, const inkq_act *act, const inkq_weight *w, co
 {
     INKQ_REQUIRE(ctx, act != nullptr && w != nullptr && C != nullptr, "null handle or output");
     INKQ_REQUIRE(ctx, act->M > 0, "activation handle holds no quantized data");
+    INKQ_REQUIRE(ctx, act->ssq_parts == 0, "the handle holds a row whose RMS scale is pending: only inkq_glue_decode_gemv consumes it");
     INKQ_REQUIRE(ctx, act->K == w->K, "activation and weight K differ");
     INKQ_REQUIRE(ctx, w->scheme != INKQ_W41, "a weight-only layer takes fp16 activations: use inkq_gemm_w41_f16act");
     const bool want_q81 = (w->scheme == INKQ_A81W41);

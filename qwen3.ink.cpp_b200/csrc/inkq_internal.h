@@ -59,7 +59,15 @@ struct Act {
     int8_t *q;
     float *d, *s;
     int32_t *isum;
+    // Pending RMS scale (decode step only, inkq_glue_decode_gemv epilogue 4): the row was quantized as x * g WITHOUT
+    // the factor 1 / sqrt(mean(x^2) + eps), and ssq[0 .. ssq_parts) holds the sums of squares of its 32-element groups;
+    // the consuming matrix-vector product derives the factor from them and applies it to the block scales.
+    // ssq_parts == 0: nothing pending (every other producer resets it).
+    float *ssq = nullptr;
+    int ssq_parts = 0, norm_n = 0;
+    float norm_eps = 0.0f;
 };
+constexpr int ACT_SSQ_CAP = 512;   // groups of 32: rows of up to 16384 values
 
 // Further destinations of an output matrix: the same element offset is stored through every pointer
 // (other GPUs' mapped buffers of a column-sharded layer, or other local buffers).
@@ -92,7 +100,7 @@ struct inkq_ctx {
     std::string err;
     uint64_t launches;
     int num_sms;
-    int *dev_flag;        // device word set by a kernel whose bounded wait ran out
+    int *dev_flag;        // device word set by a kernel whose bounded wait ran out (word 0), ticket counters and the split attention's scratch behind it
     inkq::Act *scratch_act;  // activation scratch of inkq_linear (grown on demand)
     size_t scratch_elems;    // its capacity in activation elements (M * K)
     size_t scratch_planes;   // capacity of each of its per-block planes, in entries
@@ -108,6 +116,13 @@ struct inkq_ctx {
     cudaStream_t copy_stream;   // inkq_linear_host: device-to-host copies of finished column chunks (created on first use)
     cudaEvent_t chunk_ev[4];
 };
+// Layout of the block dev_flag points to, in 4-byte words: [0] time-out flag, [1] ticket counter of the decode GEMV's last-CTA
+// epilogue, [4 .. 4 + ATT_MAX_HEADS) per-head ticket counters of the split decode attention, then its partial results
+// [ATT_MAX_HEADS][ATT_MAX_SPLITS][ATT_PART_WORDS] floats.
+namespace inkq {
+constexpr int ATT_MAX_HEADS = 128, ATT_MAX_SPLITS = 8, ATT_PART_WORDS = 132;
+constexpr size_t CTX_FLAG_WORDS = 4 + ATT_MAX_HEADS + static_cast<size_t>(ATT_MAX_HEADS) * ATT_MAX_SPLITS * ATT_PART_WORDS;
+}
 struct inkq_weight : inkq::Weight {};
 struct inkq_act : inkq::Act {};
 struct inkq_f16w : inkq::F16W {};

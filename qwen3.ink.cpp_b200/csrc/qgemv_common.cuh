@@ -136,6 +136,7 @@ inline QuantOut quant_out_of(Act *a, int K, int qmode)
     a->M = 1;
     a->M_ld = 4;
     a->qmode = qmode;
+    a->ssq_parts = 0;
     return o;
 }
 

@@ -12,6 +12,13 @@
 //   EPI_PAIR_SILUQ  the weight's rows come in (32 gate rows, 32 up rows) groups (an interleaved fused
 //                   gate_up projection); a CTA computes both groups, SiLU(gate)*up of its 32 results is
 //                   exactly one quantization block, quantized into `out`: input of down_proj
+//   EPI_ACC_QUANT_PENDING  C[n] += y[n]; the CTA's 32 results times the norm weights are one quantization block,
+//                   quantized on the spot WITHOUT the row's RMS factor, and the CTA leaves the sum of squares of its
+//                   32 results; the factor 1 / sqrt(mean(C^2) + eps) is a scalar of the whole row, so the consuming
+//                   product applies it to the block scales (W (f v) = f (W v)): no CTA has to see the whole row and
+//                   the serial last-CTA pass of EPI_ACC_NORMQ disappears.  The quantized values differ from
+//                   EPI_ACC_NORMQ's in the last bit at most (x * g against (x * f) * g before rounding to int8); the
+//                   block scales stay fp32 (an fp16 scale of an un-normalized row could overflow).
 // The matrix-vector arithmetic and its fixed reduction order are those of k_qgemv_a8w4 (per K-slice the
 // reference's per-pair order, qwen3/src/qwen/quantized_gemx_kernels.cc:171-188; slice partials ascending);
 // the quantization arithmetic is k_quantize_q8's (quantized_gemx_kernels.cc:693-801), operation for
@@ -31,7 +38,7 @@
 
 namespace inkq {
 
-enum { EPI_STORE = 0, EPI_ACC = 1, EPI_ACC_NORMQ = 2, EPI_PAIR_SILUQ = 3 };
+enum { EPI_STORE = 0, EPI_ACC = 1, EPI_ACC_NORMQ = 2, EPI_PAIR_SILUQ = 3, EPI_ACC_QUANT_PENDING = 4 };
 
 struct DecodeEpi {
     int mode;
@@ -39,7 +46,15 @@ struct DecodeEpi {
     float eps;
     float *xn;           // EPI_ACC_NORMQ: optional fp32 copy of the normalized row
     unsigned *counter;   // EPI_ACC_NORMQ: ticket counter (zero between launches)
+    float *ssq_out;      // EPI_ACC_QUANT_PENDING: sums of squares, one per 32-row group
     QuantOut out;
+};
+
+// RMS factor still to be applied to the input row (the producer ran EPI_ACC_QUANT_PENDING); parts == 0: none
+struct PendingNorm {
+    const float *ssq;
+    int parts, n;
+    float eps;
 };
 
 // RMSNorm of the fp32 row x[0..n) (read through L2) by the whole CTA, then quantization, two lanes per block.
@@ -125,7 +140,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_decode
                                                                  const uchar2 *__restrict__ zpT, const int8_t *__restrict__ q,
                                                                  const float *__restrict__ d, const float *__restrict__ s,
                                                                  const int32_t *__restrict__ isum, int M_ld, float *C, int rows, int K,
-                                                                 int pairs, const DecodeEpi epi)
+                                                                 int pairs, const DecodeEpi epi, const PendingNorm pend)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int nb = K / QK;
@@ -151,9 +166,18 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_decode
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     for (int i = threadIdx.x; i < K / 16; i += blockDim.x) reinterpret_cast<uint4 *>(qa)[i] = reinterpret_cast<const uint4 *>(q)[i];
+    float in_scale = 1.0f;
+    if (pend.parts > 0) {
+        // every warp of every CTA adds the group sums in the same order (lane-strided, then an xor tree): one value for all
+        float ss = 0.0f;
+        for (int i = lane; i < pend.parts; i += 32) ss = __fadd_rn(ss, __ldcg(pend.ssq + i));
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, off));
+        in_scale = rms_inv(ss, pend.n, pend.eps);
+    }
     for (int b = threadIdx.x; b < nb; b += blockDim.x) {
-        da[b] = d[static_cast<size_t>(b) * M_ld];
-        if (HAS_MIN) sa[b] = s[static_cast<size_t>(b) * M_ld];
+        da[b] = __fmul_rn(d[static_cast<size_t>(b) * M_ld], in_scale);
+        if (HAS_MIN) sa[b] = __fmul_rn(s[static_cast<size_t>(b) * M_ld], in_scale);
         else reinterpret_cast<int32_t *>(sa)[b] = isum[static_cast<size_t>(b) * M_ld];
     }
     __syncthreads();
@@ -195,6 +219,18 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_decode
         return;
     }
     const int n = t * TILE_N + (g0 << 5) + lane;
+    if (epi.mode == EPI_ACC_QUANT_PENDING) {
+        if (warp == 0) {   // rows is a multiple of 32 here: the whole warp holds results
+            const float y = __fadd_rn(C[n], tot[0]);
+            C[n] = y;
+            float ss = __fmul_rn(y, y);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, off));
+            if (lane == 0) epi.ssq_out[n >> 5] = ss;
+            quantize_block_lanes(__fmul_rn(y, epi.g[n]), n >> 5, lane, epi.out);
+        }
+        return;
+    }
     if (warp == 0 && n < rows) {
         float y = tot[0];
         if (epi.mode != EPI_STORE) y = __fadd_rn(C[n], y);
@@ -223,7 +259,7 @@ __global__ void __launch_bounds__(512) k_rmsnorm_quant_row(const float *x, const
 }
 
 template <bool HAS_MIN, int WARPS>
-static void launch_decode_variant(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, const DecodeEpi &epi)
+static void launch_decode_variant(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, const DecodeEpi &epi, const PendingNorm &pend)
 {
     const size_t smem = static_cast<size_t>(w->K) + 2 * sizeof(float) * (w->K / QK) + sizeof(float) * WARPS * 32;
     if (smem > 48 * 1024) cudaFuncSetAttribute(k_qgemv_decode<HAS_MIN, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -239,7 +275,7 @@ static void launch_decode_variant(inkq_ctx *ctx, const Act *a, const Weight *w, 
     cfg.numAttrs = 1;
     cudaLaunchKernelEx(&cfg, k_qgemv_decode<HAS_MIN, WARPS>, static_cast<const uint8_t *>(w->nibT), static_cast<const uint2 *>(w->sc16),
                        static_cast<const uchar2 *>(w->zpT), static_cast<const int8_t *>(a->q), static_cast<const float *>(a->d),
-                       static_cast<const float *>(a->s), static_cast<const int32_t *>(a->isum), a->M_ld, C, w->rows, w->K, w->pairs, epi);
+                       static_cast<const float *>(a->s), static_cast<const int32_t *>(a->isum), a->M_ld, C, w->rows, w->K, w->pairs, epi, pend);
 }
 
 }  // namespace inkq
@@ -261,14 +297,33 @@ int inkq_glue_decode_gemv(inkq_ctx *ctx, const inkq_weight *w, const inkq_act *i
     int rc = decode_use(ctx);
     if (rc) return rc;
     INKQ_REQUIRE(ctx, w != nullptr && in != nullptr, "null weight or activation handle");
-    INKQ_REQUIRE(ctx, epilogue >= EPI_STORE && epilogue <= EPI_PAIR_SILUQ, "epilogue must be 0..3");
+    INKQ_REQUIRE(ctx, epilogue >= EPI_STORE && epilogue <= EPI_ACC_QUANT_PENDING, "epilogue must be 0..4");
     INKQ_REQUIRE(ctx, w->scheme != INKQ_W41, "a weight-only layer takes fp16 activations");
     INKQ_REQUIRE(ctx, in->M == 1 && in->K == w->K, "the input must be one quantized row of the layer's K");
     const int expect = (w->scheme == INKQ_A81W41) ? INKQ_Q8_1_F16 : INKQ_Q8_0_F16;
-    INKQ_REQUIRE(ctx, in->qmode == expect, "the input row was quantized in another mode than this layer's M == 1 path uses");
+    // (a row whose RMS factor is pending carries fp32 block scales and sums whatever the scheme)
+    INKQ_REQUIRE(ctx, in->qmode == expect || in->ssq_parts > 0, "the input row was quantized in another mode than this layer's M == 1 path uses");
+    PendingNorm pend = {};
+    if (in->ssq_parts > 0) {
+        pend.ssq = in->ssq;
+        pend.parts = in->ssq_parts;
+        pend.n = in->norm_n;
+        pend.eps = in->norm_eps;
+    }
     INKQ_REQUIRE(ctx, epilogue == EPI_PAIR_SILUQ || C_dev != nullptr, "null output");
     DecodeEpi epi = {};
     epi.mode = epilogue;
+    if (epilogue == EPI_ACC_QUANT_PENDING) {
+        INKQ_REQUIRE(ctx, out != nullptr && out != in && out->K == w->rows, "out must be another handle created for K = the layer's row count");
+        INKQ_REQUIRE(ctx, norm_w_dev != nullptr && w->rows % 128 == 0 && w->rows / 32 <= ACT_SSQ_CAP && out->ssq != nullptr,
+                     "the pending-norm epilogue needs the norm weights and a row count that is a multiple of 128, at most 16384");
+        epi.g = norm_w_dev;
+        epi.ssq_out = out->ssq;
+        epi.out = quant_out_of(out, w->rows, INKQ_Q8_1_F32);
+        out->ssq_parts = w->rows / 32;
+        out->norm_n = w->rows;
+        out->norm_eps = eps;
+    }
     if (epilogue == EPI_ACC_NORMQ || epilogue == EPI_PAIR_SILUQ) {
         INKQ_REQUIRE(ctx, out != nullptr, "this epilogue writes a quantized row: out is required");
         INKQ_REQUIRE(ctx, out_qmode == INKQ_Q8_1_F16 || out_qmode == INKQ_Q8_0_F16 || out_qmode == INKQ_Q8_1_F32, "bad output quantization mode");
@@ -289,11 +344,11 @@ int inkq_glue_decode_gemv(inkq_ctx *ctx, const inkq_weight *w, const inkq_act *i
     }
     const bool wide_cta = (w->tiles * 4 <= 2 * ctx->num_sms) || (w->pairs >= 128);
     if (w->scheme == INKQ_A81W41) {
-        if (wide_cta) launch_decode_variant<true, 16>(ctx, in, w, C_dev, epi);
-        else launch_decode_variant<true, 8>(ctx, in, w, C_dev, epi);
+        if (wide_cta) launch_decode_variant<true, 16>(ctx, in, w, C_dev, epi, pend);
+        else launch_decode_variant<true, 8>(ctx, in, w, C_dev, epi, pend);
     } else {
-        if (wide_cta) launch_decode_variant<false, 16>(ctx, in, w, C_dev, epi);
-        else launch_decode_variant<false, 8>(ctx, in, w, C_dev, epi);
+        if (wide_cta) launch_decode_variant<false, 16>(ctx, in, w, C_dev, epi, pend);
+        else launch_decode_variant<false, 8>(ctx, in, w, C_dev, epi, pend);
     }
     return after_launch(ctx, "k_qgemv_decode");
 }

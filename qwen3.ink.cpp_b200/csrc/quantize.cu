@@ -144,6 +144,7 @@ int launch_quantize(inkq_ctx *ctx, int qmode, const float *x, int M, int K, Act 
     a->M = M;
     a->M_ld = M_ld;
     a->qmode = qmode;
+    a->ssq_parts = 0;
     return after_launch(ctx, "k_quantize_q8");
 }
 
@@ -156,6 +157,7 @@ int launch_silu_mul_quantize(inkq_ctx *ctx, int qmode, const float *gu, int M, i
     a->M = M;
     a->M_ld = M_ld;
     a->qmode = qmode;
+    a->ssq_parts = 0;
     return after_launch(ctx, "k_quantize_q8<silu_mul>");
 }
 

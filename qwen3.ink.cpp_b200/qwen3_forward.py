@@ -45,6 +45,8 @@ class Qwen3Config:
     lm_head_fp16: bool = True     # fp16 lm_head (benchmark config); False: A81W41 like the reference
     decode_mode: str = "epilogue"  # decode step: "epilogue" (norm / SiLU*up / quantizer in the producers' epilogues, 5 launches per
                                    # layer), "prologue" (in the QGEMV prologues, 6 launches) or "separate" (17 launches)
+    decode_norm: str = "pending"   # "epilogue" decode mode: "pending" (each CTA quantizes its own 32 results, the row's RMS factor is applied
+                                   # by the consumer: no whole-row pass) or "last_cta" (RMSNorm + quantizer by the CTA that finishes last)
     prefill_mode: str = "fused"    # prompt: "fused" (residual add + RMSNorm + quantizer in one kernel, SiLU*up inside the quantizer,
                                    # attention quantizes its own output: 9 launches per layer) or "separate" (one kernel per
                                    # operator, 15 launches); same bits
@@ -198,11 +200,12 @@ class Qwen3Synthetic:
                                                         cfg.nq, cfg.nkv, cfg.max_pos, eps, _p(b["q"]), _p(ly["k_cache"][0]), _p(ly["v_cache"][0])))
                 self._chk(L.inkq_glue_attention_quant(h, _p(b["q"]), _p(ly["k_cache"][0]), _p(ly["v_cache"][0]), _p(self.pos), cfg.nq, cfg.nkv,
                                                       cfg.max_pos, C.c_float(scale), self.act_attn.h, Q))
-                self._chk(L.inkq_glue_decode_gemv(h, ly["o"].h, self.act_attn.h, _p(b["x"]), 2, _p(ly["ln2"]), eps, self.act_h.h, Q, None))
+                tail = 4 if cfg.decode_norm == "pending" else 2
+                self._chk(L.inkq_glue_decode_gemv(h, ly["o"].h, self.act_attn.h, _p(b["x"]), tail, _p(ly["ln2"]), eps, self.act_h.h, Q, None))
                 self._chk(L.inkq_glue_decode_gemv(h, ly["gate_up"].h, self.act_h.h, None, 3, None, eps, self.act_f.h, Q, None))
-                last = (i == nl - 1)
+                last = (i == nl - 1)    # the last layer's row goes to the lm_head as fp32: normalized by the last CTA
                 nxt = self.final_norm if last else self.layers[i + 1]["ln1"]
-                self._chk(L.inkq_glue_decode_gemv(h, ly["down"].h, self.act_f.h, _p(b["x"]), 2, _p(nxt), eps, self.act_h.h, Q,
+                self._chk(L.inkq_glue_decode_gemv(h, ly["down"].h, self.act_f.h, _p(b["x"]), 2 if last else tail, _p(nxt), eps, self.act_h.h, Q,
                                                   _p(b["xn"]) if last else None))
         for ly in (self.layers if mode == "prologue" else []):
             # one launch per linear: norm / SiLU*up and the activation quantizer run in the QGEMV's prologue,

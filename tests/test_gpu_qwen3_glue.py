@@ -378,3 +378,59 @@ def test_prompt_attention_quantizing_its_output_equals_attention_then_quantizer(
         else:
             for got, ref in zip(a_got.export(rows), a_ref.export(rows)):
                 assert np.array_equal(got, ref)
+
+
+def test_decode_gemv_pending_norm_epilogue(pkg, gpu):
+    """Epilogue 4 of inkq_glue_decode_gemv (each CTA quantizes its own 32 results times the norm weights, the row's RMS factor
+    is left to the consumer) against epilogue 2 (RMSNorm + quantizer over the whole row by the last CTA): the residual row is
+    the same bit for bit, the raw quantized row is x * g within half a quantization step, and the product that consumes it
+    agrees with the one consuming the normalized row to 2e-3 of its largest value (two int8 roundings of slightly different
+    fp32 values, and fp32 instead of fp16 block scales)."""
+    import ctypes as C
+    import torch
+    L, h = gpu.L, gpu.h
+    P = lambda t: C.c_void_p(t.data_ptr())
+    K, N, N2 = 512, 384, 256
+    for scheme, qm in ((pkg.A81W41, pkg.Q8_1_F16), (pkg.A80W40, pkg.Q8_0_F16)):
+        w = pkg.synth.weights(N, K, 41)
+        w2 = pkg.synth.weights(N2, N, 42)
+        mm = lambda ww: ww["m"] if scheme == pkg.A81W41 else None
+        wh = gpu.weight(scheme, pkg.SCALES_F16, w["nib"], w["d"], mm(w))
+        wh2 = gpu.weight(scheme, pkg.SCALES_F16, w2["nib"], w2["d"], mm(w2))
+        x = torch.randn((1, K), device="cuda")
+        a_in = gpu.act(1, K)
+        gpu.quantize(a_in, x, 1, qm)
+        g = torch.rand(N, device="cuda") + 0.5
+        base = torch.randn((1, N), device="cuda") * 30.0            # an un-normalized residual row
+        res_a, res_b = base.clone(), base.clone()
+        out_a, out_b = gpu.act(1, N), gpu.act(1, N)
+        gpu.check(L.inkq_glue_decode_gemv(h, wh.h, a_in.h, P(res_a), 2, P(g), C.c_float(1e-6), out_a.h, qm, None))
+        gpu.check(L.inkq_glue_decode_gemv(h, wh.h, a_in.h, P(res_b), 4, P(g), C.c_float(1e-6), out_b.h, qm, None))
+        y_a, y_b = torch.empty((1, N2), device="cuda"), torch.empty((1, N2), device="cuda")
+        gpu.check(L.inkq_glue_decode_gemv(h, wh2.h, out_a.h, P(y_a), 0, None, C.c_float(0), None, qm, None))
+        gpu.check(L.inkq_glue_decode_gemv(h, wh2.h, out_b.h, P(y_b), 0, None, C.c_float(0), None, qm, None))
+        gpu.synchronize()
+        assert torch.equal(res_a, res_b)
+        qv, d, _, _ = out_b.export(1)
+        raw = (qv.reshape(1, -1, 32).astype(np.float32) * d[:, :, None]).reshape(1, -1)
+        want = (res_b * g).cpu().numpy()
+        assert (np.abs(raw - want) <= 0.51 * np.repeat(d, 32, axis=1) + 1e-6).all()
+        assert (y_a - y_b).abs().max().item() <= 2e-3 * y_a.abs().max().item()
+        # a pending row is not an input of the plain matmuls
+        with pytest.raises(pkg.InkqError):
+            gpu.gemv(out_b, wh2, y_b)
+
+
+def test_decode_with_pending_norm_agrees_with_last_cta_norm(pkg, gpu):
+    import torch
+    toks = torch.from_numpy(pkg.synth.tokens(9, 1024, 6)).cuda()
+    logits = []
+    for norm in ("last_cta", "pending"):
+        model = pkg.qwen3_forward.Qwen3Synthetic(pkg, gpu, small_cfg(pkg, decode_norm=norm), seed=2)
+        model.reset()
+        model.prefill(toks[:8])
+        model.token.copy_(toks[8:9])
+        logits.append(model.decode_step().clone())
+        gpu.synchronize()
+    rel = (logits[0] - logits[1]).abs().max().item() / logits[0].abs().max().item()
+    assert rel < 2e-2, rel
