@@ -132,8 +132,8 @@ __device__ __forceinline__ void fused_prologue(const FusedM1 &f, int K, uint32_t
 // the grid alone cannot fill the machine).  The register budget keeps 3 (resp. 2) CTAs per SM resident so
 // that every Qwen3-8B shape runs as a single wave.  FUSED: the activation row is built from fp32 input in
 // the prologue (FusedM1) instead of being read from a quantizer's output.
-template <bool HAS_MIN, int WARPS, bool FUSED>
-__global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_a8w4(const uint8_t *__restrict__ nibT, const uint2 *__restrict__ sc16,
+template <bool HAS_MIN, int WARPS, bool FUSED, bool DEEP>
+__global__ void __launch_bounds__(WARPS * 32, GemvShape<WARPS, DEEP>::CTAS_PER_SM) k_qgemv_a8w4(const uint8_t *__restrict__ nibT, const uint2 *__restrict__ sc16,
                                                                const uchar2 *__restrict__ zpT, const int8_t *__restrict__ q,
                                                                const float *__restrict__ d, const float *__restrict__ s,
                                                                const int32_t *__restrict__ isum, int M_ld, float *__restrict__ C,
@@ -155,9 +155,8 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_a8w4(c
 
     // The weight stream does not depend on the activations: put the first two batches in flight
     // before anything else, so the staging of the activation row hides behind their latency.
-    PairBatch b0, b1;
-    if (p_begin < p_end) load_batch<HAS_MIN>(b0, nibT, sc16, zpT, slab, r, p_begin, p_end);
-    if (p_begin + GEMV_UNROLL < p_end) load_batch<HAS_MIN>(b1, nibT, sc16, zpT, slab, r, p_begin + GEMV_UNROLL, p_end);
+    RowStream<HAS_MIN, GemvShape<WARPS, DEEP>::DEPTH> rs;
+    rs.prime(nibT, sc16, zpT, slab, r, p_begin, p_end);
     // Programmatic dependent launch: this grid may have started while its predecessor in the stream
     // (normally the quantizer that produces q, d, s) was still running.  The weights above are
     // independent of it; everything below is not, so wait for the predecessor to complete here, and
@@ -178,16 +177,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_a8w4(c
     }
     __syncthreads();
 
-    // two batches per trip: while one is consumed the other (and its successor) are in flight
-    float acc = 0.0f;
-    for (int p0 = p_begin; p0 < p_end; p0 += 2 * GEMV_UNROLL) {
-        acc = consume_batch<HAS_MIN>(b0, acc, swz, qa, da, sa, p0, p_end);
-        if (p0 + 2 * GEMV_UNROLL < p_end) load_batch<HAS_MIN>(b0, nibT, sc16, zpT, slab, r, p0 + 2 * GEMV_UNROLL, p_end);
-        if (p0 + GEMV_UNROLL < p_end) {
-            acc = consume_batch<HAS_MIN>(b1, acc, swz, qa, da, sa, p0 + GEMV_UNROLL, p_end);
-            if (p0 + 3 * GEMV_UNROLL < p_end) load_batch<HAS_MIN>(b1, nibT, sc16, zpT, slab, r, p0 + 3 * GEMV_UNROLL, p_end);
-        }
-    }
+    const float acc = rs.run(0.0f, swz, qa, da, sa, nibT, sc16, zpT, slab, r, p_begin, p_end);
     part[warp * 32 + lane] = acc;
     __syncthreads();
     if (warp == 0) {
@@ -205,12 +195,12 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_a8w4(c
     }
 }
 
-template <bool HAS_MIN, int WARPS, bool FUSED>
+template <bool HAS_MIN, int WARPS, bool FUSED, bool DEEP = false>
 static void launch_gemv_variant(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, const ExtraDst &extra, const FusedM1 &fused)
 {
     const size_t smem = static_cast<size_t>(w->K) + 2 * sizeof(float) * (w->K / QK) + sizeof(float) * WARPS * 32;
     if (smem > 48 * 1024)
-        cudaFuncSetAttribute(k_qgemv_a8w4<HAS_MIN, WARPS, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        cudaFuncSetAttribute(k_qgemv_a8w4<HAS_MIN, WARPS, FUSED, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     // launched with programmatic stream serialization: the grid may begin (and prefetch weights) before the
     // previous kernel in the stream has finished; it waits for that kernel inside (griddepcontrol.wait)
     cudaLaunchConfig_t cfg = {};
@@ -223,7 +213,7 @@ static void launch_gemv_variant(inkq_ctx *ctx, const Act *a, const Weight *w, fl
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaLaunchKernelEx(&cfg, k_qgemv_a8w4<HAS_MIN, WARPS, FUSED>, static_cast<const uint8_t *>(w->nibT), static_cast<const uint2 *>(w->sc16),
+    cudaLaunchKernelEx(&cfg, k_qgemv_a8w4<HAS_MIN, WARPS, FUSED, DEEP>, static_cast<const uint8_t *>(w->nibT), static_cast<const uint2 *>(w->sc16),
                        static_cast<const uchar2 *>(w->zpT), static_cast<const int8_t *>(a ? a->q : nullptr),
                        static_cast<const float *>(a ? a->d : nullptr), static_cast<const float *>(a ? a->s : nullptr),
                        static_cast<const int32_t *>(a ? a->isum : nullptr), a ? a->M_ld : 0, C, w->rows, w->K, w->pairs, extra, fused);
@@ -234,11 +224,15 @@ static void launch_gemv_any(inkq_ctx *ctx, const Act *a, const Weight *w, float 
 {
     // narrow layers (few CTAs) or long rows: 16 K-slices per CTA
     const bool wide_cta = (w->tiles * 4 <= 2 * ctx->num_sms) || (w->pairs >= 128);
+    // no more CTAs than SMs and long rows: one CTA per SM with four batches in flight per lane (same accumulation order)
+    const bool deep = wide_cta && gemv_deep(w->tiles * 4, w->pairs, 16, ctx->num_sms);
     if (w->scheme == INKQ_A81W41) {
-        if (wide_cta) launch_gemv_variant<true, 16, FUSED>(ctx, a, w, C, extra, fused);
+        if (deep) launch_gemv_variant<true, 16, FUSED, true>(ctx, a, w, C, extra, fused);
+        else if (wide_cta) launch_gemv_variant<true, 16, FUSED>(ctx, a, w, C, extra, fused);
         else launch_gemv_variant<true, 8, FUSED>(ctx, a, w, C, extra, fused);
     } else {
-        if (wide_cta) launch_gemv_variant<false, 16, FUSED>(ctx, a, w, C, extra, fused);
+        if (deep) launch_gemv_variant<false, 16, FUSED, true>(ctx, a, w, C, extra, fused);
+        else if (wide_cta) launch_gemv_variant<false, 16, FUSED>(ctx, a, w, C, extra, fused);
         else launch_gemv_variant<false, 8, FUSED>(ctx, a, w, C, extra, fused);
     }
 }

@@ -77,6 +77,46 @@ __device__ __forceinline__ float consume_batch(const PairBatch &b, float acc, bo
     return acc;
 }
 
+// A lane's walk over its K-slice [p_begin, p_end) of one weight row with DEPTH batches in flight: prime() issues the
+// first DEPTH batches (they do not depend on the activations), run() consumes the pairs in ascending order - the
+// accumulation order never depends on DEPTH - and refills each batch as soon as it is consumed.
+template <bool HAS_MIN, int DEPTH>
+struct RowStream {
+    PairBatch b[DEPTH];
+    __device__ __forceinline__ void prime(const uint8_t *__restrict__ nibT, const uint2 *__restrict__ sc16, const uchar2 *__restrict__ zpT, size_t slab,
+                                          int r, int p_begin, int p_end)
+    {
+#pragma unroll
+        for (int i = 0; i < DEPTH; i++)
+            if (p_begin + i * GEMV_UNROLL < p_end) load_batch<HAS_MIN>(b[i], nibT, sc16, zpT, slab, r, p_begin + i * GEMV_UNROLL, p_end);
+    }
+    __device__ __forceinline__ float run(float acc, bool swz, const uint32_t *__restrict__ qa, const float *__restrict__ da, const float *__restrict__ sa,
+                                         const uint8_t *__restrict__ nibT, const uint2 *__restrict__ sc16, const uchar2 *__restrict__ zpT, size_t slab,
+                                         int r, int p_begin, int p_end)
+    {
+        for (int p0 = p_begin; p0 < p_end; p0 += DEPTH * GEMV_UNROLL) {
+#pragma unroll
+            for (int i = 0; i < DEPTH; i++) {
+                const int pi = p0 + i * GEMV_UNROLL;
+                if (pi < p_end) {
+                    acc = consume_batch<HAS_MIN>(b[i], acc, swz, qa, da, sa, pi, p_end);
+                    if (pi + DEPTH * GEMV_UNROLL < p_end) load_batch<HAS_MIN>(b[i], nibT, sc16, zpT, slab, r, pi + DEPTH * GEMV_UNROLL, p_end);
+                }
+            }
+        }
+        return acc;
+    }
+};
+
+// Batches in flight per lane and CTAs per SM of a kernel variant: 8 warps x 3 CTAs and 16 warps x 2 CTAs keep two
+// batches in flight; DEEP (16 warps, one CTA per SM: layers with no more 32-row groups than SMs and long rows) four.
+template <int WARPS, bool DEEP> struct GemvShape {
+    static constexpr int DEPTH = DEEP ? 4 : 2;
+    static constexpr int CTAS_PER_SM = DEEP ? 1 : (WARPS == 8 ? 3 : 2);
+};
+// the rule both matrix-vector kernels use (so that they stay bit-identical): few CTAs and at least three batches per lane
+inline bool gemv_deep(int ctas, int pairs, int warps, int num_sms) { return ctas <= num_sms && pairs / warps >= 3 * GEMV_UNROLL; }
+
 // Saturating pack of four s32 to s8 (a in the low byte): two cvt.pack instructions.
 __device__ __forceinline__ uint32_t pack_sat_s8x4_m1(int a, int b, int c, int d)
 {

@@ -135,8 +135,8 @@ __device__ __forceinline__ void cta_rmsnorm_quant(const float *x, const float *g
     }
 }
 
-template <bool HAS_MIN, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_decode(const uint8_t *__restrict__ nibT, const uint2 *__restrict__ sc16,
+template <bool HAS_MIN, int WARPS, bool DEEP>
+__global__ void __launch_bounds__(WARPS * 32, GemvShape<WARPS, DEEP>::CTAS_PER_SM) k_qgemv_decode(const uint8_t *__restrict__ nibT, const uint2 *__restrict__ sc16,
                                                                  const uchar2 *__restrict__ zpT, const int8_t *__restrict__ q,
                                                                  const float *__restrict__ d, const float *__restrict__ s,
                                                                  const int32_t *__restrict__ isum, int M_ld, float *C, int rows, int K,
@@ -159,9 +159,8 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_decode
     const size_t slab = static_cast<size_t>(t) * pairs;
 
     int r = (g0 << 5) + lane;
-    PairBatch b0, b1;
-    if (p_begin < p_end) load_batch<HAS_MIN>(b0, nibT, sc16, zpT, slab, r, p_begin, p_end);
-    if (p_begin + GEMV_UNROLL < p_end) load_batch<HAS_MIN>(b1, nibT, sc16, zpT, slab, r, p_begin + GEMV_UNROLL, p_end);
+    RowStream<HAS_MIN, GemvShape<WARPS, DEEP>::DEPTH> rs;
+    rs.prime(nibT, sc16, zpT, slab, r, p_begin, p_end);
     // the weights do not depend on the predecessor in the stream; everything below does
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -185,19 +184,10 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_qgemv_decode
     float tot[2] = {0.0f, 0.0f};
     for (int gi = 0; gi < groups; gi++) {
         const bool swz = ((r >> 2) & 1) != 0;
-        float acc = 0.0f;
-        for (int p0 = p_begin; p0 < p_end; p0 += 2 * GEMV_UNROLL) {
-            acc = consume_batch<HAS_MIN>(b0, acc, swz, qa, da, sa, p0, p_end);
-            if (p0 + 2 * GEMV_UNROLL < p_end) load_batch<HAS_MIN>(b0, nibT, sc16, zpT, slab, r, p0 + 2 * GEMV_UNROLL, p_end);
-            if (p0 + GEMV_UNROLL < p_end) {
-                acc = consume_batch<HAS_MIN>(b1, acc, swz, qa, da, sa, p0 + GEMV_UNROLL, p_end);
-                if (p0 + 3 * GEMV_UNROLL < p_end) load_batch<HAS_MIN>(b1, nibT, sc16, zpT, slab, r, p0 + 3 * GEMV_UNROLL, p_end);
-            }
-        }
+        const float acc = rs.run(0.0f, swz, qa, da, sa, nibT, sc16, zpT, slab, r, p_begin, p_end);
         if (gi + 1 < groups) {   // the second group's first batches fly while the first group is reduced
             r += 32;
-            if (p_begin < p_end) load_batch<HAS_MIN>(b0, nibT, sc16, zpT, slab, r, p_begin, p_end);
-            if (p_begin + GEMV_UNROLL < p_end) load_batch<HAS_MIN>(b1, nibT, sc16, zpT, slab, r, p_begin + GEMV_UNROLL, p_end);
+            rs.prime(nibT, sc16, zpT, slab, r, p_begin, p_end);
         }
         part[warp * 32 + lane] = acc;
         __syncthreads();
@@ -258,11 +248,11 @@ __global__ void __launch_bounds__(512) k_rmsnorm_quant_row(const float *x, const
     cta_rmsnorm_quant(x, g, eps, n, xn, o, red);
 }
 
-template <bool HAS_MIN, int WARPS>
+template <bool HAS_MIN, int WARPS, bool DEEP = false>
 static void launch_decode_variant(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, const DecodeEpi &epi, const PendingNorm &pend)
 {
     const size_t smem = static_cast<size_t>(w->K) + 2 * sizeof(float) * (w->K / QK) + sizeof(float) * WARPS * 32;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(k_qgemv_decode<HAS_MIN, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k_qgemv_decode<HAS_MIN, WARPS, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(w->tiles) * (epi.mode == EPI_PAIR_SILUQ ? 2 : 4));
     cfg.blockDim = dim3(WARPS * 32);
@@ -273,7 +263,7 @@ static void launch_decode_variant(inkq_ctx *ctx, const Act *a, const Weight *w, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaLaunchKernelEx(&cfg, k_qgemv_decode<HAS_MIN, WARPS>, static_cast<const uint8_t *>(w->nibT), static_cast<const uint2 *>(w->sc16),
+    cudaLaunchKernelEx(&cfg, k_qgemv_decode<HAS_MIN, WARPS, DEEP>, static_cast<const uint8_t *>(w->nibT), static_cast<const uint2 *>(w->sc16),
                        static_cast<const uchar2 *>(w->zpT), static_cast<const int8_t *>(a->q), static_cast<const float *>(a->d),
                        static_cast<const float *>(a->s), static_cast<const int32_t *>(a->isum), a->M_ld, C, w->rows, w->K, w->pairs, epi, pend);
 }
@@ -343,11 +333,15 @@ int inkq_glue_decode_gemv(inkq_ctx *ctx, const inkq_weight *w, const inkq_act *i
         epi.counter = reinterpret_cast<unsigned *>(ctx->dev_flag) + 1;
     }
     const bool wide_cta = (w->tiles * 4 <= 2 * ctx->num_sms) || (w->pairs >= 128);
+    const int ctas = w->tiles * (epilogue == EPI_PAIR_SILUQ ? 2 : 4);
+    const bool deep = wide_cta && gemv_deep(ctas, w->pairs, 16, ctx->num_sms);
     if (w->scheme == INKQ_A81W41) {
-        if (wide_cta) launch_decode_variant<true, 16>(ctx, in, w, C_dev, epi, pend);
+        if (deep) launch_decode_variant<true, 16, true>(ctx, in, w, C_dev, epi, pend);
+        else if (wide_cta) launch_decode_variant<true, 16>(ctx, in, w, C_dev, epi, pend);
         else launch_decode_variant<true, 8>(ctx, in, w, C_dev, epi, pend);
     } else {
-        if (wide_cta) launch_decode_variant<false, 16>(ctx, in, w, C_dev, epi, pend);
+        if (deep) launch_decode_variant<false, 16, true>(ctx, in, w, C_dev, epi, pend);
+        else if (wide_cta) launch_decode_variant<false, 16>(ctx, in, w, C_dev, epi, pend);
         else launch_decode_variant<false, 8>(ctx, in, w, C_dev, epi, pend);
     }
     return after_launch(ctx, "k_qgemv_decode");
