@@ -96,3 +96,58 @@ def test_scatter_argument_checks(pkg, gpu):
     ps.close()
     with pytest.raises(pkg.InkqError):
         gpu.peerset_from_tensors(3, bufs)                        # rank outside the world
+
+
+@pytest.mark.parametrize("M", [1, 322])
+def test_one_process_driving_two_devices(pkg, gpu, M):
+    """The mode inkq_peerset_from_pointers documents for a single process that owns every GPU: one context per device,
+    every rank's buffer addressed directly (peer access enabled), the two barrier kernels meeting across NVLink.  Also
+    the first launch of the tensor-core kernels on a second device of the process (their shared-memory opt-in is per
+    device).  Needs two visible GPUs."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two visible GPUs")
+    if not (torch.cuda.can_device_access_peer(0, 1) and torch.cuda.can_device_access_peer(1, 0)):
+        pytest.skip("the two GPUs cannot address each other")
+    N, K, world = 1024, 512, 2
+    x_host = pkg.synth.activations(M, K, 23)
+    w = pkg.synth.weights(N, K, 23)
+    whole = gpu.weight(pkg.A81W41, pkg.SCALES_F16, w["nib"], w["d"], w["m"])
+    x0 = torch.from_numpy(x_host).cuda(0)
+    ref = torch.empty((M, N), device="cuda:0")
+    gpu.linear(whole, x0, M, ref, N)
+    gpu.synchronize()
+    nbytes = pkg.PEER_RESERVED_BYTES + 4 * M * N
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=f"cuda:{d}") for d in range(world)]
+    # a copy in each direction makes torch enable peer access between the two devices
+    bufs[0][:16].to("cuda:1")
+    bufs[1][:16].to("cuda:0")
+    torch.cuda.synchronize(0)
+    torch.cuda.synchronize(1)
+    ctxs, sets, keep = [], [], []
+    try:
+        for rank in range(world):
+            with torch.cuda.device(rank):
+                ctx = gpu if rank == 0 else pkg.Context(rank, torch.cuda.current_stream(rank).cuda_stream)
+                ctxs.append(ctx)
+                n0, n1 = pkg.tp.shard_range(N, world, rank)
+                shard = ctx.weight(pkg.A81W41, pkg.SCALES_F16, w["nib"], w["d"], w["m"], None, n0, n1)
+                xr = x0 if rank == 0 else torch.from_numpy(x_host).cuda(rank)
+                ps = ctx.peerset_from_tensors(rank, bufs)
+                sets.append(ps)
+                keep += [shard, xr]
+                ctx.linear_scatter(shard, xr, M, ps, pkg.tp.scatter_offset(0, M, N, n0), N)
+        for rank in range(world):                         # asynchronous launches: rank 0's barrier kernel waits on its GPU
+            with torch.cuda.device(rank):                 # for the arrival that rank 1's kernel sends from the other one
+                ctxs[rank].peer_barrier(sets[rank], timeout_ms=5000)
+        for ctx in ctxs:
+            ctx.synchronize()
+        for d, b in enumerate(bufs):
+            got = b[pkg.PEER_RESERVED_BYTES:].view(torch.float32).view(M, N)
+            assert torch.equal(got.to("cuda:0"), ref), f"buffer of device {d}"
+    finally:
+        for ps in sets:
+            ps.close()
+        for ctx in ctxs[1:]:
+            ctx.close()
+        torch.cuda.set_device(0)
