@@ -877,7 +877,7 @@ def run_ours(args, rank, world, local_rank):
             ctx.linear_host(ws[i % sets], xh, M, ch, N)
         dt = (time.perf_counter() - t0) / it
         e2e = {"value": ops / dt / 1e12, "unit": "TOPS", "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * 4, "ms_per_step": dt * 1e3,
-               "path": "inkq_linear_host (four launches over quarters of the weight tiles, finished columns copied back meanwhile)"}
+               "path": "inkq_linear_host (windows of rows: activations in, quantizer + QGEMM, finished rows out, on three streams)"}
     elif scatter is not None:
         xh = torch.from_numpy(x_host).pin_memory()
         ch = torch.empty((M, N), dtype=torch.float32).pin_memory() if rank == 0 else None

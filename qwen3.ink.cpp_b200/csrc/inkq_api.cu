@@ -157,7 +157,9 @@ int inkq_ctx_create(int device, void *stream, inkq_ctx **out)
     ctx->dev_flag = nullptr;
     ctx->encode_tiled = nullptr;
     ctx->copy_stream = nullptr;
-    for (int i = 0; i < 4; i++) ctx->chunk_ev[i] = nullptr;
+    ctx->h2d_stream = nullptr;
+    ctx->start_ev = nullptr;
+    for (int i = 0; i < 8; i++) ctx->chunk_ev[i] = ctx->h2d_ev[i] = nullptr;
     cudaDeviceProp prop;
     if ((e = cudaSetDevice(device)) != cudaSuccess || (e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) {
         delete ctx;
@@ -200,8 +202,12 @@ int inkq_ctx_destroy(inkq_ctx *ctx)
     cudaFree(ctx->lin_c);
     cudaFree(ctx->dev_flag);
     if (ctx->copy_stream != nullptr) cudaStreamDestroy(ctx->copy_stream);
-    for (int i = 0; i < 4; i++)
+    if (ctx->h2d_stream != nullptr) cudaStreamDestroy(ctx->h2d_stream);
+    if (ctx->start_ev != nullptr) cudaEventDestroy(ctx->start_ev);
+    for (int i = 0; i < 8; i++) {
         if (ctx->chunk_ev[i] != nullptr) cudaEventDestroy(ctx->chunk_ev[i]);
+        if (ctx->h2d_ev[i] != nullptr) cudaEventDestroy(ctx->h2d_ev[i]);
+    }
     delete ctx;
     return INKQ_OK;
 }
@@ -645,34 +651,64 @@ int inkq_linear_host(inkq_ctx *ctx, const inkq_weight *w, const float *x_host, i
     INKQ_REQUIRE(ctx, ldc >= w->rows, "ldc is smaller than the number of weight rows");
     const size_t xn = static_cast<size_t>(M) * w->K, cn = static_cast<size_t>(M) * w->rows;
     if ((rc = ensure_staging(ctx, xn, cn))) return rc;
-    INKQ_CUDA(ctx, cudaMemcpyAsync(ctx->lin_x, x_host, xn * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
-    constexpr int CHUNKS = 4;
-    if (M > 1 && w->scheme != INKQ_W41 && w->tiles >= 2 * CHUNKS) {
-        // The result (M*N*4 bytes over PCIe) takes longer to copy back than to compute: the QGEMM runs in four
-        // launches over quarters of the weight tiles, and the columns of a finished quarter travel to the host on a
-        // second stream while the next quarter is computed.
+    if (M >= 96 && w->scheme != INKQ_W41) {
+        // Both copies (M*K*4 bytes in, M*N*4 bytes out over PCIe) take longer than the arithmetic, so the call works on
+        // windows of rows: window i's activations travel to the device on one stream while window i-1 is quantized and
+        // multiplied on the context's stream and window i-2's finished rows (contiguous in the result) travel back on
+        // a third.  The first windows are small, so that the device-to-host link, which carries the most bytes, starts
+        // early and then never waits: a window's product is ready before its predecessor's rows have left.
+        constexpr int MAXC = 8;
+        int m0[MAXC + 1], nch = 0, at = 0;
+        const int lead[3] = {48, 80, 96};
+        m0[0] = 0;
+        while (nch < 3 && M - at >= lead[nch] + 32) {
+            at += lead[nch];
+            m0[++nch] = at;
+        }
+        if (at < M) {
+            const int left = M - at, parts = (left + 127) / 128 < MAXC - nch ? (left + 127) / 128 : MAXC - nch;
+            const int step = ((left + parts - 1) / parts + 15) & ~15;
+            while (at < M) {
+                at = (at + step < M) ? at + step : M;
+                m0[++nch] = at;
+            }
+        }
         if (ctx->copy_stream == nullptr) {
             INKQ_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
-            for (int i = 0; i < CHUNKS; i++) INKQ_CUDA(ctx, cudaEventCreateWithFlags(&ctx->chunk_ev[i], cudaEventDisableTiming));
+            INKQ_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->h2d_stream, cudaStreamNonBlocking));
+            INKQ_CUDA(ctx, cudaEventCreateWithFlags(&ctx->start_ev, cudaEventDisableTiming));
+            for (int i = 0; i < MAXC; i++) {
+                INKQ_CUDA(ctx, cudaEventCreateWithFlags(&ctx->chunk_ev[i], cudaEventDisableTiming));
+                INKQ_CUDA(ctx, cudaEventCreateWithFlags(&ctx->h2d_ev[i], cudaEventDisableTiming));
+            }
         }
         if ((rc = ensure_scratch_act(ctx, M, w->K))) return rc;
         inkq_act *act = static_cast<inkq_act *>(ctx->scratch_act);
         const int qmode = (w->scheme == INKQ_A81W41) ? INKQ_Q8_1_F32 : INKQ_Q8_0_F16;
-        if ((rc = inkq_quantize(ctx, qmode, ctx->lin_x, M, w->K, act))) return rc;
-        for (int c = 0; c < CHUNKS; c++) {
-            const int t0 = static_cast<int>(static_cast<long long>(w->tiles) * c / CHUNKS);
-            const int t1 = static_cast<int>(static_cast<long long>(w->tiles) * (c + 1) / CHUNKS);
-            if ((rc = launch_gemm_tc(ctx, act, w, ctx->lin_c, w->rows, nullptr, nullptr, t0, t1 - t0))) return rc;
+        // whatever the context's stream still does with the staging buffers finishes before they are overwritten
+        INKQ_CUDA(ctx, cudaEventRecord(ctx->start_ev, ctx->stream));
+        INKQ_CUDA(ctx, cudaStreamWaitEvent(ctx->h2d_stream, ctx->start_ev, 0));
+        INKQ_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->start_ev, 0));
+        for (int c = 0; c < nch; c++) {
+            const size_t off = static_cast<size_t>(m0[c]) * w->K, cnt = static_cast<size_t>(m0[c + 1] - m0[c]) * w->K;
+            INKQ_CUDA(ctx, cudaMemcpyAsync(ctx->lin_x + off, x_host + off, cnt * sizeof(float), cudaMemcpyHostToDevice, ctx->h2d_stream));
+            INKQ_CUDA(ctx, cudaEventRecord(ctx->h2d_ev[c], ctx->h2d_stream));
+        }
+        for (int c = 0; c < nch; c++) {
+            const int rows = m0[c + 1] - m0[c];
+            INKQ_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->h2d_ev[c], 0));
+            if ((rc = launch_quantize_rows(ctx, qmode, ctx->lin_x + static_cast<size_t>(m0[c]) * w->K, m0[c], rows, M, w->K, act))) return rc;
+            if ((rc = launch_gemm_tc(ctx, act, w, ctx->lin_c, w->rows, nullptr, nullptr, 0, -1, m0[c], rows))) return rc;
             INKQ_CUDA(ctx, cudaEventRecord(ctx->chunk_ev[c], ctx->stream));
             INKQ_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->chunk_ev[c], 0));
-            const int n0 = t0 * TILE_N, n1 = (t1 * TILE_N < w->rows) ? t1 * TILE_N : w->rows;
-            INKQ_CUDA(ctx, cudaMemcpy2DAsync(C_host + n0, static_cast<size_t>(ldc) * sizeof(float), ctx->lin_c + n0,
-                                             static_cast<size_t>(w->rows) * sizeof(float), static_cast<size_t>(n1 - n0) * sizeof(float), M,
-                                             cudaMemcpyDeviceToHost, ctx->copy_stream));
+            INKQ_CUDA(ctx, cudaMemcpy2DAsync(C_host + static_cast<size_t>(m0[c]) * ldc, static_cast<size_t>(ldc) * sizeof(float),
+                                             ctx->lin_c + static_cast<size_t>(m0[c]) * w->rows, static_cast<size_t>(w->rows) * sizeof(float),
+                                             static_cast<size_t>(w->rows) * sizeof(float), rows, cudaMemcpyDeviceToHost, ctx->copy_stream));
         }
         INKQ_CUDA(ctx, cudaStreamSynchronize(ctx->copy_stream));
         return inkq_ctx_synchronize(ctx);
     }
+    INKQ_CUDA(ctx, cudaMemcpyAsync(ctx->lin_x, x_host, xn * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
     if ((rc = inkq_linear(ctx, w, ctx->lin_x, M, ctx->lin_c, w->rows))) return rc;
     INKQ_CUDA(ctx, cudaMemcpy2DAsync(C_host, static_cast<size_t>(ldc) * sizeof(float), ctx->lin_c, static_cast<size_t>(w->rows) * sizeof(float),
                                      static_cast<size_t>(w->rows) * sizeof(float), M, cudaMemcpyDeviceToHost, ctx->stream));

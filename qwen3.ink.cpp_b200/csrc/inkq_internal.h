@@ -113,8 +113,9 @@ struct inkq_ctx {
     float *f16_scale;        // its per-row power-of-two factors
     size_t f16_scale_cap;
     void *encode_tiled;      // cuTensorMapEncodeTiled entry point
-    cudaStream_t copy_stream;   // inkq_linear_host: device-to-host copies of finished column chunks (created on first use)
-    cudaEvent_t chunk_ev[4];
+    cudaStream_t copy_stream;   // inkq_linear_host: device-to-host copies of finished row chunks (created on first use)
+    cudaStream_t h2d_stream;    // inkq_linear_host: host-to-device copies of the row chunks
+    cudaEvent_t chunk_ev[8], h2d_ev[8], start_ev;
 };
 // Layout of the block dev_flag points to, in 4-byte words: [0] time-out flag, [1] ticket counter of the decode GEMV's last-CTA
 // epilogue, [4 .. 4 + ATT_MAX_HEADS) per-head ticket counters of the split decode attention, then its partial results
@@ -169,6 +170,7 @@ int after_launch(inkq_ctx *ctx, const char *what);
 
 // kernels' host launchers (defined in the respective .cu files)
 int launch_quantize(inkq_ctx *ctx, int qmode, const float *x, int M, int K, Act *a);
+int launch_quantize_rows(inkq_ctx *ctx, int qmode, const float *x, int m0, int rows, int M_total, int K, Act *a);
 // gu [M][2K] in (32 gate, 32 up) column groups -> the quantized rows of SiLU(gate) * up
 int launch_silu_mul_quantize(inkq_ctx *ctx, int qmode, const float *gu, int M, int K, Act *a);
 int launch_block_isum(inkq_ctx *ctx, Act *a, int M, int M_ld);
@@ -180,8 +182,10 @@ int launch_gemv_fused(inkq_ctx *ctx, const Weight *w, const float *x, int pro, c
 int launch_gemm_simt(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc);
 int launch_block_dots(inkq_ctx *ctx, const Act *a, const Weight *w, int32_t *dots);
 // tn_begin / tn_count: the launch covers the weight tiles (of 128 rows) tn_begin .. tn_begin + tn_count - 1 (default: all)
+// tn_begin / tn_count: a range of the weight's 128-row tiles; m_begin / m_count: a window of the activation rows (m_begin a
+// multiple of 4; C and the extra destinations still point at row 0)
 int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc, int32_t *dots, const ExtraDst *extra = nullptr,
-                   int tn_begin = 0, int tn_count = -1);
+                   int tn_begin = 0, int tn_count = -1, int m_begin = 0, int m_count = -1);
 int launch_gemm_w41_f16(inkq_ctx *ctx, const uint16_t *a16, int M, const Weight *w, float *C, int ldc);   // CUDA cores
 int launch_gemm_w41_tc(inkq_ctx *ctx, const uint16_t *a16, int M, const Weight *w, float *C, int ldc);    // tcgen05 kind::f16
 int launch_gemv_w41(inkq_ctx *ctx, const uint16_t *a16, const Weight *w, float *C);                        // M == 1, bandwidth-bound

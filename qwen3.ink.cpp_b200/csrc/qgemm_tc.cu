@@ -612,10 +612,10 @@ static int launch_cw(inkq_ctx *ctx, int cw, const CUtensorMap *maps, const TcPar
 }
 
 static int encode2d(inkq_ctx *ctx, CUtensorMap *map, CUtensorMapDataType dt, int elem_bytes, const void *base, uint64_t dim0, uint64_t dim1,
-                    uint32_t box0, uint32_t box1, CUtensorMapSwizzle swz)
+                    uint32_t box0, uint32_t box1, CUtensorMapSwizzle swz, uint64_t pitch_elems = 0)
 {
     const cuuint64_t gdim[2] = {dim0, dim1};
-    const cuuint64_t gstride[1] = {dim0 * static_cast<uint64_t>(elem_bytes)};
+    const cuuint64_t gstride[1] = {(pitch_elems ? pitch_elems : dim0) * static_cast<uint64_t>(elem_bytes)};
     const cuuint32_t box[2] = {box0, box1};
     const cuuint32_t estr[2] = {1u, 1u};
     CUresult cr = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled)(map, dt, 2, const_cast<void *>(base), gdim, gstride, box, estr,
@@ -630,12 +630,16 @@ static int encode2d(inkq_ctx *ctx, CUtensorMap *map, CUtensorMapDataType dt, int
 // K=32 MMAs and their commits, wide ones by the epilogue arithmetic.  The ratios hardly depend on K (both terms are per block).
 static const float tile_cost[9] = {0.f, 1.00f, 1.10f, 1.22f, 1.42f, 1.61f, 1.81f, 2.05f, 2.38f};
 
-int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc, int32_t *dots, const ExtraDst *extra, int tn_begin, int tn_count)
+int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int ldc, int32_t *dots, const ExtraDst *extra, int tn_begin, int tn_count,
+                   int m_begin, int m_count)
 {
     if (tn_count < 0) tn_count = w->tiles - tn_begin;   // default: every tile from tn_begin on
+    if (m_count < 0) m_count = a->M - m_begin;          // default: every row from m_begin on
+    if (m_begin < 0 || (m_begin & 3) != 0 || m_count < 1 || m_begin + m_count > a->M || (m_begin != 0 && dots != nullptr))
+        return fail(ctx, INKQ_ERR_INVALID, "bad activation row window");
     if (ctx->encode_tiled == nullptr) return fail(ctx, INKQ_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled entry point not available");
     if (w->sc32 == nullptr) return fail(ctx, INKQ_ERR_INVALID, "this weight holds no fp32 scale records (weight-only layers use inkq_gemm_w41_f16act)");
-    const int M = a->M;
+    const int M = m_count;
     // Split of the M activation rows into tiles of block_m columns (a multiple of 16, at most 128).  With few
     // weight tiles (a shard of a column-sharded layer) narrower tiles fill more SMs; the choice minimises
     // waves x tile cost.  It depends on the shapes and the SM count only, and every choice gives the same bits
@@ -658,18 +662,26 @@ int launch_gemm_tc(inkq_ctx *ctx, const Act *a, const Weight *w, float *C, int l
     const int nb = a->K / QK;
 
     CUtensorMap maps[3];
-    int rc = encode2d(ctx, &maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->q, a->K, M, 128u, block_m, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (!rc) rc = encode2d(ctx, &maps[1], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a->d, a->M_ld, nb, block_m, STAGE_BLOCKS, CU_TENSOR_MAP_SWIZZLE_NONE);
-    if (!rc) rc = encode2d(ctx, &maps[2], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a->s, a->M_ld, nb, block_m, STAGE_BLOCKS, CU_TENSOR_MAP_SWIZZLE_NONE);
+    // a row window starts m_begin rows into q and m_begin entries into every block's line of the planes
+    int rc = encode2d(ctx, &maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->q + static_cast<size_t>(m_begin) * a->K, a->K, M, 128u, block_m,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!rc) rc = encode2d(ctx, &maps[1], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a->d + m_begin, a->M_ld - m_begin, nb, block_m, STAGE_BLOCKS,
+                           CU_TENSOR_MAP_SWIZZLE_NONE, a->M_ld);
+    if (!rc) rc = encode2d(ctx, &maps[2], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a->s + m_begin, a->M_ld - m_begin, nb, block_m, STAGE_BLOCKS,
+                           CU_TENSOR_MAP_SWIZZLE_NONE, a->M_ld);
     if (rc) return rc;
 
     TcParams prm;
     prm.nibT = w->nibT;
     prm.sc32 = w->sc32;
     prm.zpT = w->zpT;
-    prm.C = C;
+    const size_t c_off = static_cast<size_t>(m_begin) * ldc;
+    prm.C = (C != nullptr) ? C + c_off : nullptr;
     prm.extra = ExtraDst{};
-    if (extra != nullptr) prm.extra = *extra;
+    if (extra != nullptr) {
+        prm.extra = *extra;
+        for (int e = 0; e < prm.extra.n; e++) prm.extra.p[e] += c_off;
+    }
     prm.dots = dots;
     prm.flag = ctx->dev_flag;
     prm.M = M;

@@ -37,8 +37,11 @@ __device__ __forceinline__ uint32_t pack_sat_s8x4(int a, int b, int c, int d)
 template <bool SILU_MUL>
 __global__ void __launch_bounds__(256) k_quantize_q8(const float4 *__restrict__ x, int M, int K, int M_ld, int mode,
                                                      int8_t *__restrict__ q, float *__restrict__ d, float *__restrict__ s,
-                                                     int32_t *__restrict__ isum)
+                                                     int32_t *__restrict__ isum, int ld)
 {
+    // x, q and the planes point at the first of the M rows this launch quantizes; M_ld = M rounded up to 4 (the padding
+    // rows of the planes are zeroed), ld = distance between two blocks' entries in the planes (>= M_ld: a launch may fill
+    // a window of rows of a larger matrix)
     // lets a dependent kernel launched with programmatic stream serialization (the decode QGEMV) start
     // its weight prefetch while this grid runs; it still waits for this grid's completion before reading
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -53,7 +56,7 @@ __global__ void __launch_bounds__(256) k_quantize_q8(const float4 *__restrict__ 
     // 16 scattered words, and still reads one full 128-byte line of x per pair
     const int b = static_cast<int>(blk / M_ld);
     const int m = static_cast<int>(blk % M_ld);
-    const size_t plane = static_cast<size_t>(b) * M_ld + m;
+    const size_t plane = static_cast<size_t>(b) * ld + m;
     if (m >= M) {  // padding rows of the scale planes read as zero
         if (half == 0) {
             d[plane] = 0.0f;
@@ -140,7 +143,7 @@ int launch_quantize(inkq_ctx *ctx, int qmode, const float *x, int M, int K, Act 
     const int M_ld = (M + 3) & ~3;
     const long long threads = static_cast<long long>(M_ld) * (K / QK) * 2;
     const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
-    k_quantize_q8<false><<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<const float4 *>(x), M, K, M_ld, qmode, a->q, a->d, a->s, a->isum);
+    k_quantize_q8<false><<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<const float4 *>(x), M, K, M_ld, qmode, a->q, a->d, a->s, a->isum, M_ld);
     a->M = M;
     a->M_ld = M_ld;
     a->qmode = qmode;
@@ -148,12 +151,28 @@ int launch_quantize(inkq_ctx *ctx, int qmode, const float *x, int M, int K, Act 
     return after_launch(ctx, "k_quantize_q8");
 }
 
+// Rows [m0, m0 + rows) of a matrix of M_total rows whose other rows are quantized by other launches into the same handle
+// (m0 a multiple of 4).  x points at row m0.
+int launch_quantize_rows(inkq_ctx *ctx, int qmode, const float *x, int m0, int rows, int M_total, int K, Act *a)
+{
+    const int ld = (M_total + 3) & ~3, rows_ld = (rows + 3) & ~3;
+    const long long threads = static_cast<long long>(rows_ld) * (K / QK) * 2;
+    const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
+    k_quantize_q8<false><<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<const float4 *>(x), rows, K, rows_ld, qmode, a->q + static_cast<size_t>(m0) * K,
+                                                         a->d + m0, a->s + m0, a->isum + m0, ld);
+    a->M = M_total;
+    a->M_ld = ld;
+    a->qmode = qmode;
+    a->ssq_parts = 0;
+    return after_launch(ctx, "k_quantize_q8 (row window)");
+}
+
 int launch_silu_mul_quantize(inkq_ctx *ctx, int qmode, const float *gu, int M, int K, Act *a)
 {
     const int M_ld = (M + 3) & ~3;
     const long long threads = static_cast<long long>(M_ld) * (K / QK) * 2;
     const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
-    k_quantize_q8<true><<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<const float4 *>(gu), M, K, M_ld, qmode, a->q, a->d, a->s, a->isum);
+    k_quantize_q8<true><<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<const float4 *>(gu), M, K, M_ld, qmode, a->q, a->d, a->s, a->isum, M_ld);
     a->M = M;
     a->M_ld = M_ld;
     a->qmode = qmode;

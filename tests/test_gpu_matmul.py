@@ -178,12 +178,13 @@ def test_full_prefill_shape(pkg, gpu, oracle):
 
 
 @pytest.mark.parametrize("scheme", [0, 1])
-def test_linear_host_chunked_copy_back(pkg, gpu, scheme):
-    """inkq_linear_host computes in four launches over quarters of the weight tiles and copies finished columns back
-    meanwhile: ragged last tile, padded host rows (ldc > N), equals the device path bit for bit and leaves the padding
-    untouched."""
+@pytest.mark.parametrize("M", [37, 97, 130, 322, 1100])
+def test_linear_host_row_windows(pkg, gpu, scheme, M):
+    """inkq_linear_host works on windows of rows from M = 96 on (activations in, quantizer + QGEMM, finished rows out, on
+    three streams): ragged last window and last weight tile, padded host rows (ldc > N); equals the device path bit for
+    bit, leaves the padding untouched, and a second call right behind the first does not disturb it."""
     import torch
-    M, N, K, ldc = 37, 1064, 128, 1072           # 9 weight tiles, the last one 40 rows
+    N, K, ldc = 1064, 128, 1072           # 9 weight tiles, the last one 40 rows
     w = pkg.synth.weights(N, K, 41)
     wh = gpu.weight(scheme, pkg.SCALES_F16, w["nib"], w["d"], w["m"] if scheme == 0 else None)
     x = pkg.synth.activations(M, K, 41)
@@ -193,6 +194,13 @@ def test_linear_host_chunked_copy_back(pkg, gpu, scheme):
     Ch = np.full((M, ldc), -7.0, np.float32)
     gpu.linear_host(wh, x, M, Ch, ldc)
     assert np.array_equal(Ch[:, :N], C.cpu().numpy()) and (Ch[:, N:] == -7.0).all()
+    x2 = pkg.synth.activations(M, K, 43)
+    C2 = torch.empty((M, N), device="cuda")
+    Ch2 = np.empty((M, N), np.float32)
+    gpu.linear_host(wh, x2, M, Ch2, N)
+    gpu.linear(wh, torch.from_numpy(x2).cuda(), M, C2, N)
+    gpu.synchronize()
+    assert np.array_equal(Ch2, C2.cpu().numpy())
 
 
 def test_mismatched_quantizer_mode_is_rejected(pkg, gpu, oracle):
