@@ -576,24 +576,40 @@ def scaling_m8192(pkg, torch, dist, ctx, world, rank, pk, min_seconds=0.3):
     w16 = (torch.randn((v1 - v0, K), device="cuda", generator=gen) * 0.02).half()
     wh = ctx.f16w_dev(w16, v1 - v0, K)
     del w16
-    sc = pkg.tp.PeerScatter(pkg, ctx, dist, M, vocab, world, rank, slots=1) if world > 1 else None
-    Cl = torch.empty((M, v1 - v0), device="cuda") if world == 1 else None
+    # (a) every rank keeps the logits of its own vocabulary columns (what a sharded sampler consumes: per-row maxima meet
+    #     in a few bytes); (b) every rank receives the whole [M][vocab] fp32 matrix through the epilogue's peer stores:
+    #     (P-1)/P of 5 GB leave every rank, so that arm is bound by NVLink, not by the tensor cores
+    Cl = torch.empty((M, v1 - v0), device="cuda")
 
     def lstep(i):
-        if sc is None:
-            ctx.f16w_matmul_prec(wh, x, M, Cl, v1 - v0, 1)
-        else:
-            ctx.f16w_matmul_scatter(wh, x, M, sc.ps, pkg.tp.scatter_offset(0, M, vocab, v0, pkg.PEER_RESERVED_BYTES), vocab, 1)
-            sc.barrier()
+        ctx.f16w_matmul_prec(wh, x, M, Cl, v1 - v0, 1)
     for i in range(2):
         lstep(i)
     torch.cuda.synchronize()
     est = cuda_time_ms(torch, lambda i: lstep(i), 1)
     ms, reps = timed_region(torch, dist, world, lambda: lstep(0), est, min_seconds)
     per = ms / reps
-    out["lm_head"] = {"M": M, "N": vocab, "K": K, "ms_per_step": per, "TFLOPS": 2.0 * M * vocab * K / (per * 1e-3) / 1e12,
-                      "frac_of_bf16_burst_per_gpu": 2.0 * M * vocab * K / (per * 1e-3) / 1e12 / pk["bf16_tflops"] / world, "activations": "fp16 (one pass)",
-                      "timing": "eager", "exchange": "peer stores from the epilogue + barrier kernel" if sc else "none"}
+    flop = 2.0 * M * vocab * K
+    out["lm_head"] = {"M": M, "N": vocab, "K": K, "ms_per_step": per, "TFLOPS": flop / (per * 1e-3) / 1e12,
+                      "frac_of_bf16_burst_per_gpu": flop / (per * 1e-3) / 1e12 / pk["bf16_tflops"] / world, "activations": "fp16 (one pass)",
+                      "timing": "eager", "exchange": "none: every rank keeps the logits of its vocabulary columns"}
+    del Cl
+    torch.cuda.empty_cache()
+    sc = pkg.tp.PeerScatter(pkg, ctx, dist, M, vocab, world, rank, slots=1) if world > 1 else None
+    if sc is not None:
+        def gstep(i):
+            ctx.f16w_matmul_scatter(wh, x, M, sc.ps, pkg.tp.scatter_offset(0, M, vocab, v0, pkg.PEER_RESERVED_BYTES), vocab, 1)
+            sc.barrier()
+        for i in range(2):
+            gstep(i)
+        torch.cuda.synchronize()
+        est = cuda_time_ms(torch, lambda i: gstep(i), 1)
+        ms, reps = timed_region(torch, dist, world, lambda: gstep(0), est, min_seconds)
+        per = ms / reps
+        sent = 4.0 * M * (v1 - v0) * (world - 1)
+        out["lm_head_gathered"] = {"ms_per_step": per, "TFLOPS": flop / (per * 1e-3) / 1e12, "nvlink_bytes_sent_per_rank": sent,
+                                   "nvlink_GBs_per_rank": sent / (per * 1e-3) / 1e9,
+                                   "exchange": "peer stores from the epilogue + barrier kernel: every rank ends with the whole [M][vocab] matrix"}
     wh.close()
     if sc is not None:
         sc.close()
