@@ -55,7 +55,7 @@ int inkq_glue_linear_m1(inkq_ctx *ctx, const inkq_weight *w, const float *x_dev,
  *       row 32b+e, row 64b+32+e is up row 32b+e of a fused gate_up projection - and SiLU(gate)*up is quantized
  *       into `out` (C_dev unused)      4: C += y; the CTA's 32 results times norm_w are quantized into `out` at once,
  *       WITHOUT the row's RMS factor, which stays pending in the handle (sums of squares per 32 results) and is applied
- *       to the block scales by the inkq_glue_decode_gemv call that reads `out` (W (f v) = f (W v)): same result as
+ *       to the finished sums by the inkq_glue_decode_gemv call that reads `out` (W (f v) = f (W v)): same result as
  *       epilogue 2 up to a last-bit difference before the rounding to int8, without any whole-row pass.  Such a handle
  *       is only valid as the `in` of inkq_glue_decode_gemv (inkq_act_export shows its raw, unscaled content)
  *   inkq_glue_rmsnorm_quant: the same RMSNorm + quantizer for a row that no product made (after the embedding)

@@ -333,20 +333,42 @@ __global__ void __launch_bounds__(ATT_SPLIT_NT) k_attention_split(const float *_
     const int share = (nkeys + ATT_S - 1) / ATT_S;
     const int k0 = min(sp * share, nkeys), n = min(nkeys - k0, share);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid < HEAD_DIM) qs[tid] = q[static_cast<size_t>(h) * HEAD_DIM + tid];
-    __syncthreads();
     const __half *kb = k_cache + (static_cast<size_t>(kvh) * max_pos + k0) * HEAD_DIM;
     const __half *vb = v_cache + (static_cast<size_t>(kvh) * max_pos + k0) * HEAD_DIM;
     const int sub = tid & 3;
+    // Everything the share needs from memory is requested up front - the query, the first 128 keys (four threads per
+    // key, 64 bytes each) and this warp's first eight value rows - so that one L2 latency covers all of it; a share of
+    // more than 128 keys (contexts beyond 512 positions) takes the remaining ones in further, unprefetched passes.
+    constexpr int KPASS = ATT_SPLIT_NT / 4, VPRE = 8;
+    uint4 pk0[4];
+    {
+        const int j = tid >> 2;
+        const uint4 *kr = reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(min(j, max(n - 1, 0))) * HEAD_DIM) + sub * 4;
+#pragma unroll
+        for (int u = 0; u < 4; u++) pk0[u] = (j < n) ? kr[u] : make_uint4(0, 0, 0, 0);
+    }
+    uint2 pv0[VPRE];
+#pragma unroll
+    for (int u = 0; u < VPRE; u++) {
+        const int j = warp + u * ATT_SPLIT_NW;
+        pv0[u] = (j < n) ? reinterpret_cast<const uint2 *>(vb + static_cast<size_t>(j) * HEAD_DIM)[lane] : make_uint2(0, 0);
+    }
+    if (tid < HEAD_DIM) qs[tid] = q[static_cast<size_t>(h) * HEAD_DIM + tid];
+    __syncthreads();
     float lmax = -INFINITY;
-    for (int jb = 0; jb < n; jb += ATT_SPLIT_NT / 4) {
+    for (int jb = 0; jb < n; jb += KPASS) {
         const int j = jb + (tid >> 2);
         float acc = 0.0f;
         if (j < n) {
-            const uint4 *kr = reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(j) * HEAD_DIM) + sub * 4;
             uint4 pk[4];
+            if (jb == 0) {
 #pragma unroll
-            for (int u = 0; u < 4; u++) pk[u] = kr[u];
+                for (int u = 0; u < 4; u++) pk[u] = pk0[u];
+            } else {
+                const uint4 *kr = reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(j) * HEAD_DIM) + sub * 4;
+#pragma unroll
+                for (int u = 0; u < 4; u++) pk[u] = kr[u];
+            }
 #pragma unroll
             for (int u = 0; u < 4; u++) {
                 const uint32_t wd[4] = {pk[u].x, pk[u].y, pk[u].z, pk[u].w};
@@ -384,17 +406,22 @@ __global__ void __launch_bounds__(ATT_SPLIT_NT) k_attention_split(const float *_
     if (lane == 0) red[ATT_SPLIT_NW + warp] = lsum;
     __syncthreads();
     float a[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 8
-    for (int j = warp; j < n; j += ATT_SPLIT_NW) {
-        const float pj = sc[j];
-        const uint2 pk = reinterpret_cast<const uint2 *>(vb + static_cast<size_t>(j) * HEAD_DIM)[lane];
+    auto add_value = [&](float pj, const uint2 pk) {
         const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.x));
         const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.y));
         a[0] = fmaf(pj, f0.x, a[0]);
         a[1] = fmaf(pj, f0.y, a[1]);
         a[2] = fmaf(pj, f1.x, a[2]);
         a[3] = fmaf(pj, f1.y, a[3]);
+    };
+#pragma unroll
+    for (int u = 0; u < VPRE; u++) {
+        const int j = warp + u * ATT_SPLIT_NW;
+        if (j < n) add_value(sc[j], pv0[u]);
     }
+#pragma unroll 4
+    for (int j = warp + VPRE * ATT_SPLIT_NW; j < n; j += ATT_SPLIT_NW)
+        add_value(sc[j], reinterpret_cast<const uint2 *>(vb + static_cast<size_t>(j) * HEAD_DIM)[lane]);
 #pragma unroll
     for (int i = 0; i < 4; i++) part[warp * HEAD_DIM + lane * 4 + i] = a[i];
     __syncthreads();

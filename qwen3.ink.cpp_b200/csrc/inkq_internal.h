@@ -61,7 +61,7 @@ struct Act {
     int32_t *isum;
     // Pending RMS scale (decode step only, inkq_glue_decode_gemv epilogue 4): the row was quantized as x * g WITHOUT
     // the factor 1 / sqrt(mean(x^2) + eps), and ssq[0 .. ssq_parts) holds the sums of squares of its 32-element groups;
-    // the consuming matrix-vector product derives the factor from them and applies it to the block scales.
+    // the consuming matrix-vector product derives the factor from them and applies it to its finished sums.
     // ssq_parts == 0: nothing pending (every other producer resets it).
     float *ssq = nullptr;
     int ssq_parts = 0, norm_n = 0;

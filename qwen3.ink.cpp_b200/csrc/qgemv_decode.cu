@@ -15,7 +15,7 @@
 //   EPI_ACC_QUANT_PENDING  C[n] += y[n]; the CTA's 32 results times the norm weights are one quantization block,
 //                   quantized on the spot WITHOUT the row's RMS factor, and the CTA leaves the sum of squares of its
 //                   32 results; the factor 1 / sqrt(mean(C^2) + eps) is a scalar of the whole row, so the consuming
-//                   product applies it to the block scales (W (f v) = f (W v)): no CTA has to see the whole row and
+//                   product applies it to its finished sums (W (f v) = f (W v)): no CTA has to see the whole row and
 //                   the serial last-CTA pass of EPI_ACC_NORMQ disappears.  The quantized values differ from
 //                   EPI_ACC_NORMQ's in the last bit at most (x * g against (x * f) * g before rounding to int8); the
 //                   block scales stay fp32 (an fp16 scale of an un-normalized row could overflow).
@@ -164,19 +164,21 @@ __global__ void __launch_bounds__(WARPS * 32, GemvShape<WARPS, DEEP>::CTAS_PER_S
     // the weights do not depend on the predecessor in the stream; everything below does
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    for (int i = threadIdx.x; i < K / 16; i += blockDim.x) reinterpret_cast<uint4 *>(qa)[i] = reinterpret_cast<const uint4 *>(q)[i];
-    float in_scale = 1.0f;
-    if (pend.parts > 0) {
-        // every warp of every CTA adds the group sums in the same order (lane-strided, then an xor tree): one value for all
-        float ss = 0.0f;
-        for (int i = lane; i < pend.parts; i += 32) ss = __fadd_rn(ss, __ldcg(pend.ssq + i));
+    // A pending RMS factor f of the input row multiplies the finished sums (W (f v) = f (W v)), so only the warp that
+    // finishes them needs it: warp 0 requests the group sums now (the first 128: a row of 4096 values; four loads in
+    // flight per lane) and adds them up after the product, when they have long arrived.
+    float pv[4] = {0.f, 0.f, 0.f, 0.f};
+    if (pend.parts > 0 && warp == 0) {
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, off));
-        in_scale = rms_inv(ss, pend.n, pend.eps);
+        for (int u = 0; u < 4; u++) {
+            const int i = u * 32 + lane;
+            pv[u] = (i < pend.parts) ? __ldcg(pend.ssq + i) : 0.0f;
+        }
     }
+    for (int i = threadIdx.x; i < K / 16; i += blockDim.x) reinterpret_cast<uint4 *>(qa)[i] = reinterpret_cast<const uint4 *>(q)[i];
     for (int b = threadIdx.x; b < nb; b += blockDim.x) {
-        da[b] = __fmul_rn(d[static_cast<size_t>(b) * M_ld], in_scale);
-        if (HAS_MIN) sa[b] = __fmul_rn(s[static_cast<size_t>(b) * M_ld], in_scale);
+        da[b] = d[static_cast<size_t>(b) * M_ld];
+        if (HAS_MIN) sa[b] = s[static_cast<size_t>(b) * M_ld];
         else reinterpret_cast<int32_t *>(sa)[b] = isum[static_cast<size_t>(b) * M_ld];
     }
     __syncthreads();
@@ -198,6 +200,18 @@ __global__ void __launch_bounds__(WARPS * 32, GemvShape<WARPS, DEEP>::CTAS_PER_S
             tot[gi] = sum;
         }
         __syncthreads();   // part is rewritten by the next group
+    }
+    if (pend.parts > 0 && warp == 0) {
+        // every CTA adds the group sums in the same order (lane-strided ascending, then an xor tree): one factor for all
+        float ss = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 4; u++) ss = __fadd_rn(ss, pv[u]);
+        for (int i = 128 + lane; i < pend.parts; i += 32) ss = __fadd_rn(ss, __ldcg(pend.ssq + i));
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, off));
+        const float f = rms_inv(ss, pend.n, pend.eps);
+        tot[0] = __fmul_rn(tot[0], f);
+        tot[1] = __fmul_rn(tot[1], f);
     }
 
     if (epi.mode == EPI_PAIR_SILUQ) {
