@@ -304,20 +304,20 @@ __global__ void __launch_bounds__(NT) k_attention(const float *__restrict__ q, c
 
 // Decode-step attention split over the keys: ATT_S CTAs per query head, each takes a contiguous share of the
 // keys 0 .. pos0 (so a head's 2 x 256 bytes per key come in through ATT_S times as many loads in flight; a decode
-// step has one query token and would otherwise run on nq of the SMs).  A CTA leaves an unnormalized partial
-// (running max, sum of exponentials, 128 weighted value sums); the CTA of a head that finishes last (ticket counter,
-// nobody waits) merges the partials in ascending split order - the result does not depend on which CTA merges - and
-// writes and/or quantizes the head's output.  Scores: four threads per key (32 dimensions each, xor-shuffle);
+// step has one query token and would otherwise run on nq of the SMs).  A CTA produces an unnormalized partial
+// (running max, sum of exponentials, 128 weighted value sums); the ATT_S CTAs of a head form a thread-block cluster,
+// write their partials into the first one's shared memory and meet at the cluster barrier; the first one merges them
+// in ascending share order and writes and/or quantizes the head's output.  Scores: four threads per key (32 dimensions each, xor-shuffle);
 // values: warp w takes keys w, w + 16, ... of the share, lane = 4 output dimensions.
 #ifndef INKQ_ATT_S
 #define INKQ_ATT_S 4   // tuning knob: shares per head
 #endif
 constexpr int ATT_S = INKQ_ATT_S, ATT_SPLIT_NT = 512, ATT_SPLIT_NW = ATT_SPLIT_NT / 32;
-static_assert(ATT_S >= 1 && ATT_S <= ATT_MAX_SPLITS, "more shares than the scratch holds");
-__global__ void __launch_bounds__(ATT_SPLIT_NT) k_attention_split(const float *__restrict__ q, const __half *__restrict__ k_cache,
-                                                                  const __half *__restrict__ v_cache, const int *__restrict__ pos0_dev, int nq,
-                                                                  int nkv, int max_pos, float scale, float *__restrict__ out, const QuantOut qo,
-                                                                  float *__restrict__ partials, unsigned *__restrict__ counters)
+static_assert(ATT_S >= 1 && ATT_S <= 8, "a portable cluster holds at most 8 CTAs");
+constexpr int ATT_PART_WORDS = HEAD_DIM + 4;   // a share's partial: 128 sums, running max, sum of exponentials
+__global__ void __cluster_dims__(ATT_S, 1, 1) __launch_bounds__(ATT_SPLIT_NT)
+    k_attention_split(const float *__restrict__ q, const __half *__restrict__ k_cache, const __half *__restrict__ v_cache,
+                      const int *__restrict__ pos0_dev, int nq, int nkv, int max_pos, float scale, float *__restrict__ out, const QuantOut qo)
 {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -326,7 +326,6 @@ __global__ void __launch_bounds__(ATT_SPLIT_NT) k_attention_split(const float *_
     float *part = sm + HEAD_DIM;                  // NW * 128
     float *red = part + ATT_SPLIT_NW * HEAD_DIM;  // 2 * NW
     float *sc = red + 2 * ATT_SPLIT_NW;           // scores of the share
-    __shared__ unsigned ticket_s;
     const int h = blockIdx.x / ATT_S, sp = blockIdx.x % ATT_S;
     const int kvh = h / (nq / nkv);
     const int nkeys = min(*pos0_dev + 1, max_pos);
@@ -425,7 +424,12 @@ __global__ void __launch_bounds__(ATT_SPLIT_NT) k_attention_split(const float *_
 #pragma unroll
     for (int i = 0; i < 4; i++) part[warp * HEAD_DIM + lane * 4 + i] = a[i];
     __syncthreads();
-    float *mine = partials + (static_cast<size_t>(h) * ATT_MAX_SPLITS + sp) * ATT_PART_WORDS;
+    // the head's ATT_S shares are one thread-block cluster: every share writes its partial into share 0's shared memory
+    // (distributed shared memory), the cluster meets at its hardware barrier, share 0 merges
+    __shared__ float merge[ATT_S][ATT_PART_WORDS];
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    float *mine = cluster.map_shared_rank(&merge[0][0], 0) + sp * ATT_PART_WORDS;
     if (tid < HEAD_DIM) {
         float o = 0.0f;
 #pragma unroll
@@ -438,21 +442,16 @@ __global__ void __launch_bounds__(ATT_SPLIT_NT) k_attention_split(const float *_
             mine[HEAD_DIM] = (n > 0) ? gmax : -INFINITY;
             mine[HEAD_DIM + 1] = den;
         }
-        __threadfence();   // every storing thread: its partial before the ticket
     }
-    __syncthreads();
-    if (tid == 0) ticket_s = atomicAdd(counters + h, 1u);
-    __syncthreads();
-    if (ticket_s != ATT_S - 1) return;
-    __threadfence();       // the other shares' partials before the reads below
+    cluster.sync();
+    if (sp != 0) return;
     if (tid < HEAD_DIM) {
-        const float *ph = partials + static_cast<size_t>(h) * ATT_MAX_SPLITS * ATT_PART_WORDS;
         float m[ATT_S], l[ATT_S], o[ATT_S];
 #pragma unroll
         for (int s2 = 0; s2 < ATT_S; s2++) {
-            m[s2] = __ldcg(ph + s2 * ATT_PART_WORDS + HEAD_DIM);
-            l[s2] = __ldcg(ph + s2 * ATT_PART_WORDS + HEAD_DIM + 1);
-            o[s2] = __ldcg(ph + s2 * ATT_PART_WORDS + tid);
+            m[s2] = merge[s2][HEAD_DIM];
+            l[s2] = merge[s2][HEAD_DIM + 1];
+            o[s2] = merge[s2][tid];
         }
         float mm = m[0];   // share 0 always holds key 0
 #pragma unroll
@@ -468,8 +467,8 @@ __global__ void __launch_bounds__(ATT_SPLIT_NT) k_attention_split(const float *_
         if (out != nullptr) out[static_cast<size_t>(h) * HEAD_DIM + tid] = res;
         if (qo.q != nullptr) quantize_block_lanes(res, h * (HEAD_DIM / QK) + warp, lane, qo);
     }
-    if (tid == 0) counters[h] = 0u;   // ready for the next launch
 }
+
 
 __global__ void __launch_bounds__(256) k_silu_mul(const float4 *__restrict__ gate, const float4 *__restrict__ up, long long n4,
                                                   float4 *__restrict__ out)
@@ -860,16 +859,14 @@ static int attention_impl(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_c
             scale, out_dev, qo, qrow0);
         return after_launch(ctx, "k_attention_prefill");
     }
-    if (T == 1 && nq <= ATT_MAX_HEADS && nq * ATT_S <= 2 * ctx->num_sms && !quant_rows) {
-        // a decode step: the keys of each head split over ATT_S CTAs, merged by the one that finishes last
+    if (T == 1 && nq * ATT_S <= 2 * ctx->num_sms && !quant_rows) {
+        // a decode step: the keys of each head split over a cluster of ATT_S CTAs
         const int share_max = (max_pos + ATT_S - 1) / ATT_S;
         const size_t smem_s = sizeof(float) * (HEAD_DIM + ATT_SPLIT_NW * HEAD_DIM + 2 * ATT_SPLIT_NW + static_cast<size_t>(share_max));
         INKQ_REQUIRE(ctx, smem_s <= 200 * 1024, "context too long for the decode attention kernel");
         if (smem_s > 48 * 1024) cudaFuncSetAttribute(k_attention_split, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_s));
-        unsigned *counters = reinterpret_cast<unsigned *>(ctx->dev_flag) + 4;
-        float *partials = reinterpret_cast<float *>(ctx->dev_flag) + 4 + ATT_MAX_HEADS;
         launch_pdl(k_attention_split, dim3(nq * ATT_S), dim3(ATT_SPLIT_NT), smem_s, ctx->stream, q_dev, reinterpret_cast<const __half *>(k_cache_dev),
-                   reinterpret_cast<const __half *>(v_cache_dev), pos0_dev, nq, nkv, max_pos, scale, out_dev, qo, partials, counters);
+                   reinterpret_cast<const __half *>(v_cache_dev), pos0_dev, nq, nkv, max_pos, scale, out_dev, qo);
         return after_launch(ctx, "k_attention_split");
     }
     // few (token, head) items (a decode step): 16 warps per item so that the item's keys are spread over more

@@ -100,7 +100,7 @@ struct inkq_ctx {
     std::string err;
     uint64_t launches;
     int num_sms;
-    int *dev_flag;        // device word set by a kernel whose bounded wait ran out (word 0), ticket counters and the split attention's scratch behind it
+    int *dev_flag;        // device word set by a kernel whose bounded wait ran out (word 0), a ticket counter behind it
     inkq::Act *scratch_act;  // activation scratch of inkq_linear (grown on demand)
     size_t scratch_elems;    // its capacity in activation elements (M * K)
     size_t scratch_planes;   // capacity of each of its per-block planes, in entries
@@ -117,12 +117,9 @@ struct inkq_ctx {
     cudaStream_t h2d_stream;    // inkq_linear_host: host-to-device copies of the row chunks
     cudaEvent_t chunk_ev[8], h2d_ev[8], start_ev;
 };
-// Layout of the block dev_flag points to, in 4-byte words: [0] time-out flag, [1] ticket counter of the decode GEMV's last-CTA
-// epilogue, [4 .. 4 + ATT_MAX_HEADS) per-head ticket counters of the split decode attention, then its partial results
-// [ATT_MAX_HEADS][ATT_MAX_SPLITS][ATT_PART_WORDS] floats.
+// dev_flag points to four 4-byte words: [0] time-out flag, [1] ticket counter of the decode GEMV's last-CTA epilogue
 namespace inkq {
-constexpr int ATT_MAX_HEADS = 128, ATT_MAX_SPLITS = 8, ATT_PART_WORDS = 132;
-constexpr size_t CTX_FLAG_WORDS = 4 + ATT_MAX_HEADS + static_cast<size_t>(ATT_MAX_HEADS) * ATT_MAX_SPLITS * ATT_PART_WORDS;
+constexpr size_t CTX_FLAG_WORDS = 4;
 }
 struct inkq_weight : inkq::Weight {};
 struct inkq_act : inkq::Act {};
