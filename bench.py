@@ -361,7 +361,9 @@ def model_pp_tg(pkg, torch, ctx, prompt_len=322, new_tokens=128, reps=3):
     prompt = torch.from_numpy(pkg.synth.tokens(prompt_len, cfg.vocab)).cuda()
     model.reset()
     model.prefill(prompt)
+    n0 = ctx.launches()
     model.decode_step()
+    launches_per_token = ctx.launches() - n0      # counted by the library: one eager decode step
     model.capture_decode()
     torch.cuda.synchronize()
     pp_ms, tg_ms = [], []
@@ -378,9 +380,8 @@ def model_pp_tg(pkg, torch, ctx, prompt_len=322, new_tokens=128, reps=3):
         pp_ms.append(a.elapsed_time(b))
         tg_ms.append(b.elapsed_time(c))
     n_gen = len(model.generated_tokens())
-    # the same decode step with every operator as its own launch (17 per layer), for comparison
+    # the same decode step with every operator as its own launch, for comparison
     unfused_ms = None
-    launches_per_token = {"epilogue": 5 * cfg.layers + 4, "prologue": 6 * cfg.layers + 4, "separate": 17 * cfg.layers + 4}[cfg.decode_mode]
     if cfg.decode_mode != "separate":
         model.cfg.decode_mode = "separate"
         model.reset()
@@ -431,7 +432,9 @@ def model_tp(pkg, torch, dist, ctx, world, rank, prompt_len=322, new_tokens=128,
         return float(t.item())
     model.reset()
     model.prefill(prompt)
+    n0 = ctx.launches()
     model.decode_step()
+    step_launches = ctx.launches() - n0      # counted by the library (barrier kernels included)
     model.capture_decode()
     torch.cuda.synchronize()
     pp_ms, tg_ms, pb_ms = [], [], []
@@ -461,7 +464,8 @@ def model_tp(pkg, torch, dist, ctx, world, rank, prompt_len=322, new_tokens=128,
     out = {"n_gpus": world, "pp322_tok_s": prompt_len / (min(pp_ms) * 1e-3), "tg128_tok_s": new_tokens / (min(tg_ms) * 1e-3),
            "prefill_ms": min(pp_ms), "decode_ms_per_token": min(tg_ms) / new_tokens,
            "batch_prefill": {"prompts": batch, "tokens_each": prompt_len, "ms": min(pb_ms), "tok_s": batch * prompt_len / (min(pb_ms) * 1e-3)},
-           "decode_mode": "separate operators (17 launches per layer" + (" + 5 barrier kernels" if world > 1 else "") + "), one CUDA graph per step",
+           "decode_mode": "one kernel per operator" + (" + a barrier kernel per sharded linear" if world > 1 else "") + ", one CUDA graph per step",
+           "decode_launches_per_token": step_launches,
            "sharding": "every linear column-sharded, outputs exchanged by peer stores from the kernels' epilogues" if world > 1 else "none"}
     model.close()
     del model

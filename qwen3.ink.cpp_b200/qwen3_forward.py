@@ -11,7 +11,7 @@ linear goes through Context.linear (Qwen_Linear_with_bias_Int4::forward: quantiz
 a prompt, + QGEMV for a single token); everything between them is the thin glue of
 csrc/glue_ops.cu.  In a decode step (one token) the norms, SiLU*up, the activation quantizer and the residual
 additions run in the epilogues of the kernels that produce each row (inkq_glue_decode_gemv,
-inkq_glue_attention_quant): 5 launches per layer instead of 17.  One decode step is captured once as a CUDA
+inkq_glue_attention_quant): 6 launches per layer instead of 11.  One decode step is captured once as a CUDA
 graph and replayed.
 
 Column-sharded form (world > 1, one process per GPU): every linear holds the weight rows [rank*N/P, (rank+1)*N/P) of the
@@ -43,8 +43,8 @@ class Qwen3Config:
     eps: float = 1e-6
     max_pos: int = 512
     lm_head_fp16: bool = True     # fp16 lm_head (benchmark config); False: A81W41 like the reference
-    decode_mode: str = "epilogue"  # decode step: "epilogue" (norm / SiLU*up / quantizer in the producers' epilogues, 5 launches per
-                                   # layer), "prologue" (in the QGEMV prologues, 6 launches) or "separate" (17 launches)
+    decode_mode: str = "epilogue"  # decode step: "epilogue" (norm / SiLU*up / quantizer in the producers' epilogues, 6 launches per
+                                   # layer), "prologue" (in the QGEMV prologues, 6 launches) or "separate" (one per operator: 11)
     decode_norm: str = "pending"   # "epilogue" decode mode: "pending" (each CTA quantizes its own 32 results, the row's RMS factor is applied
                                    # by the consumer: no whole-row pass) or "last_cta" (RMSNorm + quantizer by the CTA that finishes last)
     prefill_mode: str = "fused"    # prompt: "fused" (residual add + RMSNorm + quantizer in one kernel, SiLU*up inside the quantizer,
