@@ -361,9 +361,9 @@ def model_pp_tg(pkg, torch, ctx, prompt_len=322, new_tokens=128, reps=3):
     prompt = torch.from_numpy(pkg.synth.tokens(prompt_len, cfg.vocab)).cuda()
     model.reset()
     model.prefill(prompt)
-    n0 = ctx.launches()
+    n0 = ctx.launches
     model.decode_step()
-    launches_per_token = ctx.launches() - n0      # counted by the library: one eager decode step
+    launches_per_token = ctx.launches - n0      # counted by the library: one eager decode step
     model.capture_decode()
     torch.cuda.synchronize()
     pp_ms, tg_ms = [], []
@@ -432,9 +432,9 @@ def model_tp(pkg, torch, dist, ctx, world, rank, prompt_len=322, new_tokens=128,
         return float(t.item())
     model.reset()
     model.prefill(prompt)
-    n0 = ctx.launches()
+    n0 = ctx.launches
     model.decode_step()
-    step_launches = ctx.launches() - n0      # counted by the library (barrier kernels included)
+    step_launches = ctx.launches - n0      # counted by the library (barrier kernels included)
     model.capture_decode()
     torch.cuda.synchronize()
     pp_ms, tg_ms, pb_ms = [], [], []
