@@ -85,6 +85,13 @@ int inkq_glue_silu_mul_quant_rows(inkq_ctx *ctx, const float *gu_dev, int M, int
  * total_rows, and the handle is complete when every row has been written).  At most 4 query heads per kv head. */
 int inkq_glue_attention_quant_rows(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev,
                                    int T, int nq, int nkv, int max_pos, float scale, inkq_act *out, int out_qmode, int row0, int total_rows);
+/* One token: inkq_glue_qknorm_rope_cache and inkq_glue_attention_quant in one kernel.  Starts from the fused qkv
+ * projection's output row [(nq + 2 nkv) * 128]: per-head RMSNorm + RoPE of the query heads and of the new key, the new
+ * key and value appended to the caches at position *pos0, attention over positions 0 .. *pos0, output quantized into
+ * `out`.  Same arithmetic as the two calls; nq * 4 must not exceed twice the SM count. */
+int inkq_glue_qkv_attention_quant(inkq_ctx *ctx, const float *qkv_dev, const float *q_norm_w, const float *k_norm_w, const float *cos_dev,
+                                  const float *sin_dev, const int *pos0_dev, int nq, int nkv, int max_pos, float eps, float scale,
+                                  uint16_t *k_cache_dev, uint16_t *v_cache_dev, inkq_act *out, int out_qmode);
 /* a += b (residual).  qwen3/src/qwen/QwenDecoderLayer.cc:73,105 */
 int inkq_glue_add_inplace(inkq_ctx *ctx, float *a_dev, const float *b_dev, long long n);
 /* Greedy sampling: *token_out = argmax(logits) (first index on ties), appended to generated

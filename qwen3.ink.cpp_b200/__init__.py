@@ -43,7 +43,7 @@ SYMBOLS = [
 # every symbol include/inkq_glue.h declares
 GLUE_SYMBOLS = ["inkq_glue_embedding", "inkq_glue_rmsnorm", "inkq_glue_qknorm_rope_cache", "inkq_glue_attention", "inkq_glue_silu_mul",
                 "inkq_glue_add_inplace", "inkq_glue_argmax_advance", "inkq_glue_silu_mul_rows", "inkq_glue_linear_m1", "inkq_glue_decode_gemv", "inkq_glue_rmsnorm_quant",
-                "inkq_glue_attention_quant", "inkq_glue_add_rmsnorm_quant_rows", "inkq_glue_silu_mul_quant_rows", "inkq_glue_attention_quant_rows"]
+                "inkq_glue_attention_quant", "inkq_glue_add_rmsnorm_quant_rows", "inkq_glue_silu_mul_quant_rows", "inkq_glue_attention_quant_rows", "inkq_glue_qkv_attention_quant"]
 
 
 PEER_RESERVED_BYTES = 256   # INKQ_PEER_RESERVED_BYTES

@@ -30,4 +30,22 @@ __device__ __forceinline__ float4 rms_scale4(const float4 v, float inv, const fl
                        __fmul_rn(__fmul_rn(v.w, inv), g.w));
 }
 
+// Per-head RMSNorm (weights nw) and rotate-half RoPE (tables cs / sn of the token's position) of a 128-element head that
+// one warp holds as v[i] = x[lane + 32 i]  (qwen3/src/qwen/QwenAttention.cc:85-92, qwen3/src/ops/RotaryPosEmb.cc:6-79):
+// out[j] = x[j] cos[j] + rot[j] sin[j], rot[j] = -x[j + 64] for j < 64, x[j - 64] otherwise; the partners sit in one lane.
+__device__ __forceinline__ void head_norm_rope(float (&v)[4], int lane, const float *__restrict__ nw, const float *__restrict__ cs,
+                                               const float *__restrict__ sn, float eps, float (&r)[4])
+{
+    float ss = __fmaf_rn(v[3], v[3], __fmaf_rn(v[2], v[2], __fmaf_rn(v[1], v[1], __fmul_rn(v[0], v[0]))));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+    const float inv = rms_inv(ss, 128, eps);
+#pragma unroll
+    for (int i = 0; i < 4; i++) v[i] = __fmul_rn(__fmul_rn(v[i], inv), nw[lane + 32 * i]);
+    r[0] = __fmaf_rn(v[0], cs[lane], -__fmul_rn(v[2], sn[lane]));
+    r[1] = __fmaf_rn(v[1], cs[lane + 32], -__fmul_rn(v[3], sn[lane + 32]));
+    r[2] = __fmaf_rn(v[2], cs[lane + 64], __fmul_rn(v[0], sn[lane + 64]));
+    r[3] = __fmaf_rn(v[3], cs[lane + 96], __fmul_rn(v[1], sn[lane + 96]));
+}
+
 }  // namespace inkq

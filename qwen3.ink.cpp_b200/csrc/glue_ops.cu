@@ -176,20 +176,9 @@ __global__ void __launch_bounds__(256) k_qknorm_rope_cache(const float *__restri
         for (int i = 0; i < 4; i++) dst[lane + 32 * i] = __float2half_rn(v[i]);
         return;
     }
-    float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float inv = 1.0f / sqrtf(ss / static_cast<float>(HEAD_DIM) + eps);
-    const float *nw = (h < nq) ? q_norm_w : k_norm_w;
-#pragma unroll
-    for (int i = 0; i < 4; i++) v[i] = v[i] * inv * nw[lane + 32 * i];
-    const float *cs = cos_t + static_cast<size_t>(pos) * HEAD_DIM, *sn = sin_t + static_cast<size_t>(pos) * HEAD_DIM;
     float r[4];
-    // out[j] = x[j]*cos[j] + rot[j]*sin[j], rot[j] = -x[j+64] for j < 64, x[j-64] otherwise
-    r[0] = v[0] * cs[lane] - v[2] * sn[lane];
-    r[1] = v[1] * cs[lane + 32] - v[3] * sn[lane + 32];
-    r[2] = v[2] * cs[lane + 64] + v[0] * sn[lane + 64];
-    r[3] = v[3] * cs[lane + 96] + v[1] * sn[lane + 96];
+    head_norm_rope(v, lane, (h < nq) ? q_norm_w : k_norm_w, cos_t + static_cast<size_t>(pos) * HEAD_DIM, sin_t + static_cast<size_t>(pos) * HEAD_DIM,
+                   eps, r);
     if (h < nq) {
         float *dst = q_out + (static_cast<size_t>(t) * nq + h) * HEAD_DIM;
 #pragma unroll
@@ -315,9 +304,20 @@ __global__ void __launch_bounds__(NT) k_attention(const float *__restrict__ q, c
 constexpr int ATT_S = INKQ_ATT_S, ATT_SPLIT_NT = 512, ATT_SPLIT_NW = ATT_SPLIT_NT / 32;
 static_assert(ATT_S >= 1 && ATT_S <= 8, "a portable cluster holds at most 8 CTAs");
 constexpr int ATT_PART_WORDS = HEAD_DIM + 4;   // a share's partial: 128 sums, running max, sum of exponentials
+// When qkv is not NULL the kernel starts from the fused qkv projection's output row [(nq + 2 nkv) * 128] instead of a
+// ready query: warp 0 of every CTA normalizes and rotates the query head itself, and the share that holds the newest key
+// (position pos0) does the same for the key head and takes the value head, uses both from shared memory (rounded to
+// fp16, as the cache holds them) and - for the first query head of a kv group - appends them to the caches.  Same
+// arithmetic as k_qknorm_rope_cache (head_norm_rope), one kernel and one pass through L2 less per layer.
+struct FusedQkv {
+    const float *qkv, *q_norm_w, *k_norm_w, *cos_t, *sin_t;
+    float eps;
+    __half *k_cache_w, *v_cache_w;
+};
 __global__ void __cluster_dims__(ATT_S, 1, 1) __launch_bounds__(ATT_SPLIT_NT)
     k_attention_split(const float *__restrict__ q, const __half *__restrict__ k_cache, const __half *__restrict__ v_cache,
-                      const int *__restrict__ pos0_dev, int nq, int nkv, int max_pos, float scale, float *__restrict__ out, const QuantOut qo)
+                      const int *__restrict__ pos0_dev, int nq, int nkv, int max_pos, float scale, float *__restrict__ out, const QuantOut qo,
+                      const FusedQkv fz)
 {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -328,7 +328,8 @@ __global__ void __cluster_dims__(ATT_S, 1, 1) __launch_bounds__(ATT_SPLIT_NT)
     float *sc = red + 2 * ATT_SPLIT_NW;           // scores of the share
     const int h = blockIdx.x / ATT_S, sp = blockIdx.x % ATT_S;
     const int kvh = h / (nq / nkv);
-    const int nkeys = min(*pos0_dev + 1, max_pos);
+    const int pos_raw = *pos0_dev;
+    const int nkeys = min(pos_raw + 1, max_pos);
     const int share = (nkeys + ATT_S - 1) / ATT_S;
     const int k0 = min(sp * share, nkeys), n = min(nkeys - k0, share);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -339,20 +340,53 @@ __global__ void __cluster_dims__(ATT_S, 1, 1) __launch_bounds__(ATT_SPLIT_NT)
     // key, 64 bytes each) and this warp's first eight value rows - so that one L2 latency covers all of it; a share of
     // more than 128 keys (contexts beyond 512 positions) takes the remaining ones in further, unprefetched passes.
     constexpr int KPASS = ATT_SPLIT_NT / 4, VPRE = 8;
+    __shared__ __align__(16) __half knew[HEAD_DIM], vnew[HEAD_DIM];
+    const bool fused = fz.qkv != nullptr;
+    // the newest key is the last one of the last share that holds any; in the fused form it comes from shared memory
+    const int j_new = (fused && pos_raw < max_pos && n > 0 && k0 + n == nkeys) ? n - 1 : -1;   // (a position past the caches is not stored)
     uint4 pk0[4];
     {
         const int j = tid >> 2;
         const uint4 *kr = reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(min(j, max(n - 1, 0))) * HEAD_DIM) + sub * 4;
 #pragma unroll
-        for (int u = 0; u < 4; u++) pk0[u] = (j < n) ? kr[u] : make_uint4(0, 0, 0, 0);
+        for (int u = 0; u < 4; u++) pk0[u] = (j < n && j != j_new) ? kr[u] : make_uint4(0, 0, 0, 0);
     }
     uint2 pv0[VPRE];
 #pragma unroll
     for (int u = 0; u < VPRE; u++) {
         const int j = warp + u * ATT_SPLIT_NW;
-        pv0[u] = (j < n) ? reinterpret_cast<const uint2 *>(vb + static_cast<size_t>(j) * HEAD_DIM)[lane] : make_uint2(0, 0);
+        pv0[u] = (j < n && j != j_new) ? reinterpret_cast<const uint2 *>(vb + static_cast<size_t>(j) * HEAD_DIM)[lane] : make_uint2(0, 0);
     }
-    if (tid < HEAD_DIM) qs[tid] = q[static_cast<size_t>(h) * HEAD_DIM + tid];
+    if (!fused) {
+        if (tid < HEAD_DIM) qs[tid] = q[static_cast<size_t>(h) * HEAD_DIM + tid];
+    } else if (warp < 3) {
+        const int pos = nkeys - 1;
+        const int G = nq / nkv;
+        const float *cs = fz.cos_t + static_cast<size_t>(pos) * HEAD_DIM, *sn = fz.sin_t + static_cast<size_t>(pos) * HEAD_DIM;
+        if (warp == 0) {
+            float v[4], r[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) v[i] = fz.qkv[static_cast<size_t>(h) * HEAD_DIM + lane + 32 * i];
+            head_norm_rope(v, lane, fz.q_norm_w, cs, sn, fz.eps, r);
+#pragma unroll
+            for (int i = 0; i < 4; i++) qs[lane + 32 * i] = r[i];
+        } else if (j_new >= 0) {
+            const bool writer = (h % G) == 0;   // one query head per kv group appends to the caches
+            float v[4], r[4];
+            const int src_head = (warp == 1) ? nq + kvh : nq + nkv + kvh;
+#pragma unroll
+            for (int i = 0; i < 4; i++) v[i] = fz.qkv[static_cast<size_t>(src_head) * HEAD_DIM + lane + 32 * i];
+            if (warp == 1) head_norm_rope(v, lane, fz.k_norm_w, cs, sn, fz.eps, r);
+            __half *sm_dst = (warp == 1) ? knew : vnew;
+            __half *gl_dst = ((warp == 1) ? fz.k_cache_w : fz.v_cache_w) + (static_cast<size_t>(kvh) * max_pos + pos) * HEAD_DIM;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const __half hv = __float2half_rn((warp == 1) ? r[i] : v[i]);
+                sm_dst[lane + 32 * i] = hv;
+                if (writer) gl_dst[lane + 32 * i] = hv;
+            }
+        }
+    }
     __syncthreads();
     float lmax = -INFINITY;
     for (int jb = 0; jb < n; jb += KPASS) {
@@ -360,7 +394,10 @@ __global__ void __cluster_dims__(ATT_S, 1, 1) __launch_bounds__(ATT_SPLIT_NT)
         float acc = 0.0f;
         if (j < n) {
             uint4 pk[4];
-            if (jb == 0) {
+            if (j == j_new) {
+#pragma unroll
+                for (int u = 0; u < 4; u++) pk[u] = reinterpret_cast<const uint4 *>(knew)[sub * 4 + u];
+            } else if (jb == 0) {
 #pragma unroll
                 for (int u = 0; u < 4; u++) pk[u] = pk0[u];
             } else {
@@ -416,11 +453,12 @@ __global__ void __cluster_dims__(ATT_S, 1, 1) __launch_bounds__(ATT_SPLIT_NT)
 #pragma unroll
     for (int u = 0; u < VPRE; u++) {
         const int j = warp + u * ATT_SPLIT_NW;
-        if (j < n) add_value(sc[j], pv0[u]);
+        if (j < n) add_value(sc[j], (j == j_new) ? reinterpret_cast<const uint2 *>(vnew)[lane] : pv0[u]);
     }
 #pragma unroll 4
     for (int j = warp + VPRE * ATT_SPLIT_NW; j < n; j += ATT_SPLIT_NW)
-        add_value(sc[j], reinterpret_cast<const uint2 *>(vb + static_cast<size_t>(j) * HEAD_DIM)[lane]);
+        add_value(sc[j], (j == j_new) ? reinterpret_cast<const uint2 *>(vnew)[lane]
+                                      : reinterpret_cast<const uint2 *>(vb + static_cast<size_t>(j) * HEAD_DIM)[lane]);
 #pragma unroll
     for (int i = 0; i < 4; i++) part[warp * HEAD_DIM + lane * 4 + i] = a[i];
     __syncthreads();
@@ -800,7 +838,7 @@ int inkq_glue_qknorm_rope_cache(inkq_ctx *ctx, const float *qkv_dev, const float
 }
 
 static int attention_impl(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev, int T,
-                          int nq, int nkv, int max_pos, float scale, float *out_dev, const QuantOut &qo, int qrow0 = 0);
+                          int nq, int nkv, int max_pos, float scale, float *out_dev, const QuantOut &qo, int qrow0 = 0, const FusedQkv &fz = FusedQkv{});
 
 int inkq_glue_attention(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev, int T,
                         int nq, int nkv, int max_pos, float scale, float *out_dev)
@@ -819,6 +857,28 @@ int inkq_glue_attention_quant(inkq_ctx *ctx, const float *q_dev, const uint16_t 
     INKQ_REQUIRE(ctx, out != nullptr && out->K == nq * HEAD_DIM, "the output activation handle must have been created for K = nq * 128");
     INKQ_REQUIRE(ctx, out_qmode == INKQ_Q8_1_F16 || out_qmode == INKQ_Q8_0_F16 || out_qmode == INKQ_Q8_1_F32, "bad output quantization mode");
     return attention_impl(ctx, q_dev, k_cache_dev, v_cache_dev, pos0_dev, 1, nq, nkv, max_pos, scale, nullptr, quant_out_of(out, nq * HEAD_DIM, out_qmode));
+}
+
+int inkq_glue_qkv_attention_quant(inkq_ctx *ctx, const float *qkv_dev, const float *q_norm_w, const float *k_norm_w, const float *cos_dev,
+                                  const float *sin_dev, const int *pos0_dev, int nq, int nkv, int max_pos, float eps, float scale,
+                                  uint16_t *k_cache_dev, uint16_t *v_cache_dev, inkq_act *out, int out_qmode)
+{
+    int rc = glue_use(ctx);
+    if (rc) return rc;
+    INKQ_REQUIRE(ctx, qkv_dev && q_norm_w && k_norm_w && cos_dev && sin_dev, "null argument");
+    INKQ_REQUIRE(ctx, out != nullptr && out->K == nq * HEAD_DIM, "the output activation handle must have been created for K = nq * 128");
+    INKQ_REQUIRE(ctx, out_qmode == INKQ_Q8_1_F16 || out_qmode == INKQ_Q8_0_F16 || out_qmode == INKQ_Q8_1_F32, "bad output quantization mode");
+    FusedQkv fz;
+    fz.qkv = qkv_dev;
+    fz.q_norm_w = q_norm_w;
+    fz.k_norm_w = k_norm_w;
+    fz.cos_t = cos_dev;
+    fz.sin_t = sin_dev;
+    fz.eps = eps;
+    fz.k_cache_w = reinterpret_cast<__half *>(k_cache_dev);
+    fz.v_cache_w = reinterpret_cast<__half *>(v_cache_dev);
+    return attention_impl(ctx, nullptr, k_cache_dev, v_cache_dev, pos0_dev, 1, nq, nkv, max_pos, scale, nullptr, quant_out_of(out, nq * HEAD_DIM, out_qmode), 0,
+                          fz);
 }
 
 int inkq_glue_attention_quant_rows(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev,
@@ -846,11 +906,13 @@ int inkq_glue_attention_quant_rows(inkq_ctx *ctx, const float *q_dev, const uint
 }
 
 static int attention_impl(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev, int T,
-                          int nq, int nkv, int max_pos, float scale, float *out_dev, const QuantOut &qo, int qrow0)
+                          int nq, int nkv, int max_pos, float scale, float *out_dev, const QuantOut &qo, int qrow0, const FusedQkv &fz)
 {
     int rc = INKQ_OK;
-    INKQ_REQUIRE(ctx, q_dev && k_cache_dev && v_cache_dev && pos0_dev, "null argument");
+    INKQ_REQUIRE(ctx, (q_dev || fz.qkv) && k_cache_dev && v_cache_dev && pos0_dev, "null argument");
     INKQ_REQUIRE(ctx, T >= 1 && nq % nkv == 0 && max_pos >= 1, "bad head configuration");
+    INKQ_REQUIRE(ctx, fz.qkv == nullptr || (T == 1 && nq * ATT_S <= 2 * ctx->num_sms),
+                 "the form that starts from the qkv row serves one token and at most SMs / 2 query heads");
     const bool quant_rows = qo.q != nullptr && (T > 1 || qrow0 > 0 || qo.M_ld > 4);
     INKQ_REQUIRE(ctx, !quant_rows || nq / nkv <= ATT_GMAX, "the quantizing prompt attention serves at most 4 query heads per kv head");
     if ((T >= 16 || quant_rows) && nq / nkv <= ATT_GMAX) {   // a prompt: key/value tiles shared by 8 tokens x the heads of a kv group
@@ -866,7 +928,7 @@ static int attention_impl(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_c
         INKQ_REQUIRE(ctx, smem_s <= 200 * 1024, "context too long for the decode attention kernel");
         if (smem_s > 48 * 1024) cudaFuncSetAttribute(k_attention_split, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_s));
         launch_pdl(k_attention_split, dim3(nq * ATT_S), dim3(ATT_SPLIT_NT), smem_s, ctx->stream, q_dev, reinterpret_cast<const __half *>(k_cache_dev),
-                   reinterpret_cast<const __half *>(v_cache_dev), pos0_dev, nq, nkv, max_pos, scale, out_dev, qo);
+                   reinterpret_cast<const __half *>(v_cache_dev), pos0_dev, nq, nkv, max_pos, scale, out_dev, qo, fz);
         return after_launch(ctx, "k_attention_split");
     }
     // few (token, head) items (a decode step): 16 warps per item so that the item's keys are spread over more

@@ -11,7 +11,7 @@ linear goes through Context.linear (Qwen_Linear_with_bias_Int4::forward: quantiz
 a prompt, + QGEMV for a single token); everything between them is the thin glue of
 csrc/glue_ops.cu.  In a decode step (one token) the norms, SiLU*up, the activation quantizer and the residual
 additions run in the epilogues of the kernels that produce each row (inkq_glue_decode_gemv,
-inkq_glue_attention_quant): 6 launches per layer instead of 11.  One decode step is captured once as a CUDA
+inkq_glue_qkv_attention_quant): 5 launches per layer instead of 11.  One decode step is captured once as a CUDA
 graph and replayed.
 
 Column-sharded form (world > 1, one process per GPU): every linear holds the weight rows [rank*N/P, (rank+1)*N/P) of the
@@ -43,10 +43,11 @@ class Qwen3Config:
     eps: float = 1e-6
     max_pos: int = 512
     lm_head_fp16: bool = True     # fp16 lm_head (benchmark config); False: A81W41 like the reference
-    decode_mode: str = "epilogue"  # decode step: "epilogue" (norm / SiLU*up / quantizer in the producers' epilogues, 6 launches per
+    decode_mode: str = "epilogue"  # decode step: "epilogue" (norm / SiLU*up / quantizer in the producers' epilogues, 5 launches per
                                    # layer), "prologue" (in the QGEMV prologues, 6 launches) or "separate" (one per operator: 11)
     decode_norm: str = "pending"   # "epilogue" decode mode: "pending" (each CTA quantizes its own 32 results, the row's RMS factor is applied
                                    # by the consumer: no whole-row pass) or "last_cta" (RMSNorm + quantizer by the CTA that finishes last)
+    decode_qkv_attention: bool = True   # "epilogue" decode mode: q/k-norm, RoPE and the cache append inside the attention kernel
     prefill_mode: str = "fused"    # prompt: "fused" (residual add + RMSNorm + quantizer in one kernel, SiLU*up inside the quantizer,
                                    # attention quantizes its own output: 9 launches per layer) or "separate" (one kernel per
                                    # operator, 15 launches); same bits
@@ -196,10 +197,15 @@ class Qwen3Synthetic:
             self._chk(L.inkq_glue_rmsnorm_quant(h, _p(b["x"]), _p(self.layers[0]["ln1"]), eps, H, self.act_h.h, Q, None))
             for i, ly in enumerate(self.layers):
                 self._chk(L.inkq_glue_decode_gemv(h, ly["qkv"].h, self.act_h.h, _p(b["qkv"]), 0, None, eps, None, Q, None))
-                self._chk(L.inkq_glue_qknorm_rope_cache(h, _p(b["qkv"]), _p(ly["qn"]), _p(ly["kn"]), _p(self.cos), _p(self.sin), _p(self.pos), T,
-                                                        cfg.nq, cfg.nkv, cfg.max_pos, eps, _p(b["q"]), _p(ly["k_cache"][0]), _p(ly["v_cache"][0])))
-                self._chk(L.inkq_glue_attention_quant(h, _p(b["q"]), _p(ly["k_cache"][0]), _p(ly["v_cache"][0]), _p(self.pos), cfg.nq, cfg.nkv,
-                                                      cfg.max_pos, C.c_float(scale), self.act_attn.h, Q))
+                if cfg.decode_qkv_attention:
+                    self._chk(L.inkq_glue_qkv_attention_quant(h, _p(b["qkv"]), _p(ly["qn"]), _p(ly["kn"]), _p(self.cos), _p(self.sin), _p(self.pos),
+                                                              cfg.nq, cfg.nkv, cfg.max_pos, eps, C.c_float(scale), _p(ly["k_cache"][0]),
+                                                              _p(ly["v_cache"][0]), self.act_attn.h, Q))
+                else:
+                    self._chk(L.inkq_glue_qknorm_rope_cache(h, _p(b["qkv"]), _p(ly["qn"]), _p(ly["kn"]), _p(self.cos), _p(self.sin), _p(self.pos), T,
+                                                            cfg.nq, cfg.nkv, cfg.max_pos, eps, _p(b["q"]), _p(ly["k_cache"][0]), _p(ly["v_cache"][0])))
+                    self._chk(L.inkq_glue_attention_quant(h, _p(b["q"]), _p(ly["k_cache"][0]), _p(ly["v_cache"][0]), _p(self.pos), cfg.nq, cfg.nkv,
+                                                          cfg.max_pos, C.c_float(scale), self.act_attn.h, Q))
                 tail = 4 if cfg.decode_norm == "pending" else 2
                 self._chk(L.inkq_glue_decode_gemv(h, ly["o"].h, self.act_attn.h, _p(b["x"]), tail, _p(ly["ln2"]), eps, self.act_h.h, Q, None))
                 self._chk(L.inkq_glue_decode_gemv(h, ly["gate_up"].h, self.act_h.h, None, 3, None, eps, self.act_f.h, Q, None))

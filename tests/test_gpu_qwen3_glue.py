@@ -434,3 +434,43 @@ def test_decode_with_pending_norm_agrees_with_last_cta_norm(pkg, gpu):
         gpu.synchronize()
     rel = (logits[0] - logits[1]).abs().max().item() / logits[0].abs().max().item()
     assert rel < 2e-2, rel
+
+
+@pytest.mark.parametrize("pos", [0, 2, 5, 130, 331])
+def test_decode_attention_starting_from_the_qkv_row_equals_the_two_kernels(pkg, gpu, pos):
+    """inkq_glue_qkv_attention_quant (q/k-norm, RoPE, cache append and attention in one kernel) against
+    inkq_glue_qknorm_rope_cache followed by inkq_glue_attention_quant: the same arithmetic, so the appended cache rows and
+    the quantized attention output are equal bit for bit; positions where a share is empty, holds only the new key, or
+    the new key is its last of many."""
+    import ctypes as C
+    import torch
+    L, h = gpu.L, gpu.h
+    P = lambda t: C.c_void_p(t.data_ptr())
+    nq, nkv, max_pos, hd = 8, 2, 512, 128
+    g = torch.Generator(device="cuda")
+    g.manual_seed(pos + 1)
+    qkv = torch.randn((1, (nq + 2 * nkv) * hd), device="cuda", generator=g)
+    qn = torch.rand(hd, device="cuda", generator=g) + 0.5
+    kn = torch.rand(hd, device="cuda", generator=g) + 0.5
+    ang = torch.rand((max_pos, hd), device="cuda", generator=g) * 6.28
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    kc0 = torch.randn((nkv, max_pos, hd), device="cuda", generator=g).half()
+    vc0 = torch.randn((nkv, max_pos, hd), device="cuda", generator=g).half()
+    posd = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    eps, scale = C.c_float(1e-6), C.c_float(1.0 / np.sqrt(hd))
+    # two kernels
+    kc_a, vc_a = kc0.clone(), vc0.clone()
+    q = torch.empty((1, nq * hd), device="cuda")
+    a_ref = gpu.act(1, nq * hd)
+    gpu.check(L.inkq_glue_qknorm_rope_cache(h, P(qkv), P(qn), P(kn), P(cos), P(sin), P(posd), 1, nq, nkv, max_pos, eps, P(q), P(kc_a), P(vc_a)))
+    gpu.check(L.inkq_glue_attention_quant(h, P(q), P(kc_a), P(vc_a), P(posd), nq, nkv, max_pos, scale, a_ref.h, pkg.Q8_1_F16))
+    # one kernel
+    kc_b, vc_b = kc0.clone(), vc0.clone()
+    a_got = gpu.act(1, nq * hd)
+    gpu.check(L.inkq_glue_qkv_attention_quant(h, P(qkv), P(qn), P(kn), P(cos), P(sin), P(posd), nq, nkv, max_pos, eps, scale, P(kc_b), P(vc_b),
+                                              a_got.h, pkg.Q8_1_F16))
+    gpu.synchronize()
+    assert torch.equal(kc_a, kc_b) and torch.equal(vc_a, vc_b)
+    assert not torch.equal(kc_b[:, pos], kc0[:, pos])            # the row was really appended
+    for got, ref in zip(a_got.export(1), a_ref.export(1)):
+        assert np.array_equal(got, ref)
