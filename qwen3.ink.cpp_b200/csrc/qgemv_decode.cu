@@ -175,6 +175,14 @@ __global__ void __launch_bounds__(WARPS * 32, GemvShape<WARPS, DEEP>::CTAS_PER_S
             pv[u] = (i < pend.parts) ? __ldcg(pend.ssq + i) : 0.0f;
         }
     }
+    // the residual value and the norm weight this lane's result meets in the epilogue are requested now as well (nobody
+    // else touches them while this grid runs), so their latency passes under the product
+    const int n_early = t * TILE_N + (g0 << 5) + lane;
+    float c_early = 0.0f, g_early = 0.0f;
+    if (warp == 0 && n_early < rows && groups == 1) {
+        if (epi.mode != EPI_STORE) c_early = C[n_early];
+        if (epi.mode == EPI_ACC_QUANT_PENDING) g_early = epi.g[n_early];
+    }
     for (int i = threadIdx.x; i < K / 16; i += blockDim.x) reinterpret_cast<uint4 *>(qa)[i] = reinterpret_cast<const uint4 *>(q)[i];
     for (int b = threadIdx.x; b < nb; b += blockDim.x) {
         da[b] = d[static_cast<size_t>(b) * M_ld];
@@ -225,19 +233,19 @@ __global__ void __launch_bounds__(WARPS * 32, GemvShape<WARPS, DEEP>::CTAS_PER_S
     const int n = t * TILE_N + (g0 << 5) + lane;
     if (epi.mode == EPI_ACC_QUANT_PENDING) {
         if (warp == 0) {   // rows is a multiple of 32 here: the whole warp holds results
-            const float y = __fadd_rn(C[n], tot[0]);
+            const float y = __fadd_rn(c_early, tot[0]);
             C[n] = y;
             float ss = __fmul_rn(y, y);
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, off));
             if (lane == 0) epi.ssq_out[n >> 5] = ss;
-            quantize_block_lanes(__fmul_rn(y, epi.g[n]), n >> 5, lane, epi.out);
+            quantize_block_lanes(__fmul_rn(y, g_early), n >> 5, lane, epi.out);
         }
         return;
     }
     if (warp == 0 && n < rows) {
         float y = tot[0];
-        if (epi.mode != EPI_STORE) y = __fadd_rn(C[n], y);
+        if (epi.mode != EPI_STORE) y = __fadd_rn(c_early, y);
         C[n] = y;
     }
     if (epi.mode != EPI_ACC_NORMQ) return;
