@@ -42,8 +42,8 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_gemv_w41(con
     const int p_begin = (warp * pairs) / WARPS, p_end = ((warp + 1) * pairs) / WARPS;
     const size_t slab = static_cast<size_t>(t) * pairs;
     PairBatch b0, b1;
-    if (p_begin < p_end) load_batch<true>(b0, nibT, sc16, nullptr, slab, r, p_begin, p_end);
-    if (p_begin + GEMV_UNROLL < p_end) load_batch<true>(b1, nibT, sc16, nullptr, slab, r, p_begin + GEMV_UNROLL, p_end);
+    if (p_begin < p_end) load_batch<true, false>(b0, nibT, sc16, nullptr, slab, r, p_begin, p_end);
+    if (p_begin + GEMV_UNROLL < p_end) load_batch<true, false>(b1, nibT, sc16, nullptr, slab, r, p_begin + GEMV_UNROLL, p_end);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     for (int i = threadIdx.x; i < K / 2; i += blockDim.x) {
@@ -74,10 +74,10 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 2) k_gemv_w41(con
     float acc = 0.0f;
     for (int p0 = p_begin; p0 < p_end; p0 += 2 * GEMV_UNROLL) {
         acc = consume(b0, acc, p0);
-        if (p0 + 2 * GEMV_UNROLL < p_end) load_batch<true>(b0, nibT, sc16, nullptr, slab, r, p0 + 2 * GEMV_UNROLL, p_end);
+        if (p0 + 2 * GEMV_UNROLL < p_end) load_batch<true, false>(b0, nibT, sc16, nullptr, slab, r, p0 + 2 * GEMV_UNROLL, p_end);
         if (p0 + GEMV_UNROLL < p_end) {
             acc = consume(b1, acc, p0 + GEMV_UNROLL);
-            if (p0 + 3 * GEMV_UNROLL < p_end) load_batch<true>(b1, nibT, sc16, nullptr, slab, r, p0 + 3 * GEMV_UNROLL, p_end);
+            if (p0 + 3 * GEMV_UNROLL < p_end) load_batch<true, false>(b1, nibT, sc16, nullptr, slab, r, p0 + 3 * GEMV_UNROLL, p_end);
         }
     }
     part[warp * 32 + lane] = acc;

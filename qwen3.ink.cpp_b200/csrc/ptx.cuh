@@ -224,6 +224,13 @@ __device__ __forceinline__ uint4 ldg_stream_v4(const void *p)
     asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
+// 32 contiguous bytes in one request (256-bit load; p must be 32-byte aligned): a whole sector per lane
+__device__ __forceinline__ void ldg_stream_v8(const void *p, uint4 &lo, uint4 &hi)
+{
+    asm("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+        : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+        : "l"(p));
+}
 __device__ __forceinline__ uint2 ldg_stream_v2(const void *p)
 {
     uint2 v;

@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(WARPS * 32, GemvShape<WARPS, DEEP>::CTAS_PER_S
 
     // The weight stream does not depend on the activations: put the first two batches in flight
     // before anything else, so the staging of the activation row hides behind their latency.
-    RowStream<HAS_MIN, GemvShape<WARPS, DEEP>::DEPTH> rs;
+    RowStream<HAS_MIN, GemvShape<WARPS, DEEP>::DEPTH, GemvShape<WARPS, DEEP>::WIDE> rs;
     rs.prime(nibT, sc16, zpT, slab, r, p_begin, p_end);
     // Programmatic dependent launch: this grid may have started while its predecessor in the stream
     // (normally the quantizer that produces q, d, s) was still running.  The weights above are

@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(WARPS * 32, GemvShape<WARPS, DEEP>::CTAS_PER_S
     const size_t slab = static_cast<size_t>(t) * pairs;
 
     int r = (g0 << 5) + lane;
-    RowStream<HAS_MIN, GemvShape<WARPS, DEEP>::DEPTH> rs;
+    RowStream<HAS_MIN, GemvShape<WARPS, DEEP>::DEPTH, GemvShape<WARPS, DEEP>::WIDE> rs;
     rs.prime(nibT, sc16, zpT, slab, r, p_begin, p_end);
     // the weights do not depend on the predecessor in the stream; everything below does
     asm volatile("griddepcontrol.wait;" ::: "memory");
