@@ -12,8 +12,8 @@
 // Mapping: 2 lanes own one block (four interleaved float4 each), so the two IEEE
 // divisions are done twice per block, not eight times, four 128-bit loads are in
 // flight per lane and every load instruction of a warp touches whole 32-byte
-// sectors; max and sum need one xor-shuffle.  HBM-bound: 4 bytes read and 1.375
-// bytes written per element.
+// sectors; max and sum need one xor-shuffle, and the pair trades its packed words so that each lane
+// stores 16 contiguous bytes.  HBM-bound: 4 bytes read and 1.375 bytes written per element.
 #include <cuda_fp16.h>
 
 #include "glue_math.cuh"
@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(256) k_quantize_q8(const float4 *__restrict__ 
     const float dd = __fdiv_rn(mx, 127.0f);
     const float id = (mx != 0.0f) ? __fdiv_rn(127.0f, mx) : 0.0f;
     int sum = 0;
-    uint32_t *dst = reinterpret_cast<uint32_t *>(q) + (static_cast<size_t>(m) * K + static_cast<size_t>(b) * QK) / 4 + half;
+    uint32_t wq[4];   // this lane's words 2j + half of the block's eight
 #pragma unroll
     for (int j = 0; j < 4; j++) {
         const int i0 = __float2int_rn(__fmul_rn(v[j].x, id));
@@ -99,9 +99,15 @@ __global__ void __launch_bounds__(256) k_quantize_q8(const float4 *__restrict__ 
         const int i2 = __float2int_rn(__fmul_rn(v[j].z, id));
         const int i3 = __float2int_rn(__fmul_rn(v[j].w, id));
         sum += (i0 + i1) + (i2 + i3);   // the unsaturated values, as the reference sums them before packing
-        dst[2 * j] = pack_sat_s8x4(i0, i1, i2, i3);
+        wq[j] = pack_sat_s8x4(i0, i1, i2, i3);
     }
     sum += __shfl_xor_sync(gmask, sum, 1);
+    // the pair trades words so that lane 0 holds words 0..3 and lane 1 words 4..7: one 16-byte store each, the block's 32
+    // bytes leave as a whole sector (four scattered 4-byte stores per lane cost a quarter of the kernel at M = 8192)
+    const uint32_t xa = __shfl_xor_sync(gmask, half ? wq[0] : wq[2], 1);
+    const uint32_t xb = __shfl_xor_sync(gmask, half ? wq[1] : wq[3], 1);
+    reinterpret_cast<uint4 *>(q)[(static_cast<size_t>(m) * K + static_cast<size_t>(b) * QK) / 16 + half] =
+        half ? make_uint4(xa, wq[2], xb, wq[3]) : make_uint4(wq[0], xa, wq[1], xb);
     if (half == 0) {
         const float ss = __fmul_rn(dd, static_cast<float>(sum));
         if (mode == INKQ_Q8_1_F32) {
