@@ -82,7 +82,7 @@ int inkq_glue_add_rmsnorm_quant_rows(inkq_ctx *ctx, float *x_dev, const float *d
 int inkq_glue_silu_mul_quant_rows(inkq_ctx *ctx, const float *gu_dev, int M, int F, inkq_act *out, int out_qmode);
 /* inkq_glue_attention for T tokens of one prompt with its output quantized into rows row0 .. row0 + T - 1 of `out`
  * (created for K = nq * 128 and at least total_rows rows; a batch of prompts calls it once per prompt with the same
- * total_rows, and the handle is complete when every row has been written).  At most 4 query heads per kv head. */
+ * total_rows, and the handle is complete when every row has been written). */
 int inkq_glue_attention_quant_rows(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_cache_dev, const uint16_t *v_cache_dev, const int *pos0_dev,
                                    int T, int nq, int nkv, int max_pos, float scale, inkq_act *out, int out_qmode, int row0, int total_rows);
 /* One token: inkq_glue_qknorm_rope_cache and inkq_glue_attention_quant in one kernel.  Starts from the fused qkv

@@ -517,194 +517,6 @@ __global__ void __launch_bounds__(256) k_silu_mul(const float4 *__restrict__ gat
     out[i] = make_float4(silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z), silu_mul(g.w, u.w));
 }
 
-// Prompt attention: one CTA per (block of 8 query tokens, kv head).  Warp w owns query token t0 + w and the
-// G = nq / nkv (<= 4) query heads that share the kv head, so a key/value tile (32 keys, staged once in shared
-// memory as fp16) serves 8 * G queries instead of being re-read from L2 by every (token, head).  Scores: lane =
-// key of the tile, 128-dim dot products against the warp's pre-scaled queries (broadcast reads); online softmax
-// per (token, head) with warp reductions; values: lane = 4 output dims, keys of the tile in turn.
-constexpr int ATT_QT = 8, ATT_GMAX = 4, ATT_KT = 32, ATT_KROW = HEAD_DIM + 8;   // padded key rows: conflict-free 16-byte reads
-__global__ void __launch_bounds__(256) k_attention_prefill(const float *__restrict__ q, const __half *__restrict__ k_cache,
-                                                           const __half *__restrict__ v_cache, const int *__restrict__ pos0_dev, int T, int nq,
-                                                           int nkv, int max_pos, float scale, float *__restrict__ out, const QuantOut qo,
-                                                           int qrow0)
-{
-    __shared__ __align__(16) float qs[ATT_QT][ATT_GMAX][HEAD_DIM];
-    __shared__ __align__(16) __half ks[ATT_KT][ATT_KROW];
-    __shared__ __align__(16) __half vs[ATT_KT][HEAD_DIM];
-    __shared__ __align__(16) float ps[ATT_QT][ATT_GMAX][ATT_KT];
-    const int G = nq / nkv;
-    // the last token blocks see the most keys: they get the lowest CTA indices, so that they start first
-    const int t0 = (gridDim.x - 1 - blockIdx.x) * ATT_QT, g = blockIdx.y;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = t0 + warp;
-    const int pos0 = *pos0_dev;
-    const int my_keys = (t < T) ? min(pos0 + t + 1, max_pos) : 0;               // causal: keys 0 .. pos0 + t
-    const int cta_keys = min(pos0 + min(t0 + ATT_QT, T), max_pos);
-    for (int i = threadIdx.x; i < ATT_QT * G * (HEAD_DIM / 4); i += 256) {
-        const int d4 = i % (HEAD_DIM / 4), hh = (i / (HEAD_DIM / 4)) % G, w = i / (HEAD_DIM / 4) / G;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (t0 + w < T) v = reinterpret_cast<const float4 *>(q + (static_cast<size_t>(t0 + w) * nq + g * G + hh) * HEAD_DIM)[d4];
-        reinterpret_cast<float4 *>(qs[w][hh])[d4] = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
-    }
-    const __half *kb = k_cache + static_cast<size_t>(g) * max_pos * HEAD_DIM;
-    const __half *vb = v_cache + static_cast<size_t>(g) * max_pos * HEAD_DIM;
-    float mrun[ATT_GMAX], lrun[ATT_GMAX], acc[ATT_GMAX][4];
-#pragma unroll
-    for (int hh = 0; hh < ATT_GMAX; hh++) {
-        mrun[hh] = -INFINITY;
-        lrun[hh] = 0.0f;
-        acc[hh][0] = acc[hh][1] = acc[hh][2] = acc[hh][3] = 0.0f;
-    }
-    // Key/value tiles go global -> registers -> shared memory; the registers of tile i+1 are loaded before tile i is
-    // consumed, so the L2 latency of a tile hides behind the arithmetic of its predecessor.
-    constexpr int LD_PER_THREAD = ATT_KT * (HEAD_DIM / 8) / 256;   // 2 x (key, value) 16-byte chunks per thread
-    uint4 kreg[LD_PER_THREAD], vreg[LD_PER_THREAD];
-    auto fetch_tile = [&](int k0) {
-#pragma unroll
-        for (int u = 0; u < LD_PER_THREAD; u++) {
-            const int i = threadIdx.x + u * 256;
-            const int r = i / (HEAD_DIM / 8), c = i % (HEAD_DIM / 8);
-            kreg[u] = make_uint4(0, 0, 0, 0);
-            vreg[u] = make_uint4(0, 0, 0, 0);
-            if (k0 + r < cta_keys) {
-                kreg[u] = reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(k0 + r) * HEAD_DIM)[c];
-                vreg[u] = reinterpret_cast<const uint4 *>(vb + static_cast<size_t>(k0 + r) * HEAD_DIM)[c];
-            }
-        }
-    };
-    fetch_tile(0);
-    for (int k0 = 0; k0 < cta_keys; k0 += ATT_KT) {
-        __syncthreads();   // the previous tile is consumed (and, first time, qs is written)
-#pragma unroll
-        for (int u = 0; u < LD_PER_THREAD; u++) {
-            const int i = threadIdx.x + u * 256;
-            const int r = i / (HEAD_DIM / 8), c = i % (HEAD_DIM / 8);
-            *reinterpret_cast<uint4 *>(&ks[r][c * 8]) = kreg[u];
-            *reinterpret_cast<uint4 *>(&vs[r][c * 8]) = vreg[u];
-        }
-        __syncthreads();
-        if (k0 + ATT_KT < cta_keys) fetch_tile(k0 + ATT_KT);
-        if (k0 >= my_keys) continue;   // warp-uniform: this token sees none of the tile's keys
-        // ---- scores of key k0 + lane for the warp's G heads
-        float sdot[ATT_GMAX] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-        for (int c = 0; c < HEAD_DIM / 8; c++) {
-            const uint4 pk = *reinterpret_cast<const uint4 *>(&ks[lane][c * 8]);
-            const uint32_t wd[4] = {pk.x, pk.y, pk.z, pk.w};
-            float kf[8];
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&wd[i]));
-                kf[2 * i] = f.x;
-                kf[2 * i + 1] = f.y;
-            }
-#pragma unroll
-            for (int hh = 0; hh < ATT_GMAX; hh++) {
-                if (hh < G) {
-                    const float4 qa = *reinterpret_cast<const float4 *>(&qs[warp][hh][c * 8]);
-                    const float4 qb = *reinterpret_cast<const float4 *>(&qs[warp][hh][c * 8 + 4]);
-                    sdot[hh] = fmaf(qa.x, kf[0], sdot[hh]);
-                    sdot[hh] = fmaf(qa.y, kf[1], sdot[hh]);
-                    sdot[hh] = fmaf(qa.z, kf[2], sdot[hh]);
-                    sdot[hh] = fmaf(qa.w, kf[3], sdot[hh]);
-                    sdot[hh] = fmaf(qb.x, kf[4], sdot[hh]);
-                    sdot[hh] = fmaf(qb.y, kf[5], sdot[hh]);
-                    sdot[hh] = fmaf(qb.z, kf[6], sdot[hh]);
-                    sdot[hh] = fmaf(qb.w, kf[7], sdot[hh]);
-                }
-            }
-        }
-        const bool visible = (k0 + lane) < my_keys;
-#pragma unroll
-        for (int hh = 0; hh < ATT_GMAX; hh++) {
-            if (hh < G) {
-                const float sc = visible ? sdot[hh] : -INFINITY;
-                float tmax = sc;
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
-                const float mnew = fmaxf(mrun[hh], tmax);        // finite: key k0 is visible to this token
-                const float pe = visible ? __expf(sc - mnew) : 0.0f;
-                float tsum = pe;
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) tsum += __shfl_xor_sync(0xffffffffu, tsum, o);
-                const float corr = __expf(mrun[hh] - mnew);      // exp(-inf) = 0 on the first tile
-                lrun[hh] = lrun[hh] * corr + tsum;
-                mrun[hh] = mnew;
-                acc[hh][0] *= corr;
-                acc[hh][1] *= corr;
-                acc[hh][2] *= corr;
-                acc[hh][3] *= corr;
-                ps[warp][hh][lane] = pe;
-            }
-        }
-        __syncwarp();
-        // ---- values: lane owns output dims 4*lane .. 4*lane+3
-        const int nk = min(ATT_KT, my_keys - k0);
-        for (int j = 0; j < nk; j++) {
-            const uint2 pk = *reinterpret_cast<const uint2 *>(&vs[j][lane * 4]);
-            const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.x));
-            const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&pk.y));
-#pragma unroll
-            for (int hh = 0; hh < ATT_GMAX; hh++) {
-                if (hh < G) {
-                    const float pj = ps[warp][hh][j];
-                    acc[hh][0] = fmaf(pj, f0.x, acc[hh][0]);
-                    acc[hh][1] = fmaf(pj, f0.y, acc[hh][1]);
-                    acc[hh][2] = fmaf(pj, f1.x, acc[hh][2]);
-                    acc[hh][3] = fmaf(pj, f1.y, acc[hh][3]);
-                }
-            }
-        }
-        __syncwarp();   // ps is rewritten by the next tile
-    }
-    if (t < T) {
-#pragma unroll
-        for (int hh = 0; hh < ATT_GMAX; hh++) {
-            if (hh < G) {
-                const float inv = 1.0f / lrun[hh];
-                const float4 o = make_float4(acc[hh][0] * inv, acc[hh][1] * inv, acc[hh][2] * inv, acc[hh][3] * inv);
-                if (out != nullptr) reinterpret_cast<float4 *>(out + (static_cast<size_t>(t) * nq + g * G + hh) * HEAD_DIM)[lane] = o;
-                if (qo.q != nullptr) {
-                    // the head's 128 outputs are four quantization blocks of row qrow0 + t of the output projection's
-                    // input, eight lanes each; same arithmetic as the stand-alone quantizer
-                    float mx = fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w)));
-#pragma unroll
-                    for (int sh = 1; sh < 8; sh <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sh));
-                    const float dd = __fdiv_rn(mx, 127.0f);
-                    const float id = (mx != 0.0f) ? __fdiv_rn(127.0f, mx) : 0.0f;
-                    const int i0 = __float2int_rn(__fmul_rn(o.x, id)), i1 = __float2int_rn(__fmul_rn(o.y, id));
-                    const int i2 = __float2int_rn(__fmul_rn(o.z, id)), i3 = __float2int_rn(__fmul_rn(o.w, id));
-                    int sum = (i0 + i1) + (i2 + i3);
-#pragma unroll
-                    for (int sh = 1; sh < 8; sh <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, sh);
-                    const int row = qrow0 + t, head = g * G + hh;
-                    reinterpret_cast<uint32_t *>(qo.q)[(static_cast<size_t>(row) * nq + head) * (HEAD_DIM / 4) + lane] = pack_sat_s8x4_m1(i0, i1, i2, i3);
-                    if ((lane & 7) == 0) {
-                        const size_t pl = static_cast<size_t>(head * (HEAD_DIM / QK) + (lane >> 3)) * qo.M_ld + row;
-                        const float sv = __fmul_rn(dd, static_cast<float>(sum));
-                        if (qo.qmode == INKQ_Q8_1_F32) {
-                            qo.d[pl] = dd;
-                            qo.s[pl] = sv;
-                        } else {
-                            qo.d[pl] = __half2float(__float2half_rn(dd));
-                            qo.s[pl] = (qo.qmode == INKQ_Q8_1_F16) ? __half2float(__float2half_rn(sv)) : 0.0f;
-                        }
-                        qo.isum[pl] = sum;
-                    }
-                }
-            }
-        }
-    } else if (qo.q != nullptr && qrow0 + t < qo.M_ld) {
-        // padding rows of the scale planes (only the call that holds the last rows reaches them) read as zero
-        for (int b = lane; b < G * (HEAD_DIM / QK); b += 32) {
-            const size_t pl = static_cast<size_t>(g * G * (HEAD_DIM / QK) + b) * qo.M_ld + qrow0 + t;
-            qo.d[pl] = 0.0f;
-            qo.s[pl] = 0.0f;
-            qo.isum[pl] = 0;
-        }
-    }
-}
-
 // gu [T][2F] in (32 gate, 32 up) column groups -> out [T][F]: out[k] = SiLU(gu[64*(k/32) + k%32]) * gu[64*(k/32) + 32 + k%32]
 __global__ void __launch_bounds__(256) k_silu_mul_rows(const float4 *__restrict__ gu, int T, int F4, float4 *__restrict__ out)
 {
@@ -914,13 +726,8 @@ static int attention_impl(inkq_ctx *ctx, const float *q_dev, const uint16_t *k_c
     INKQ_REQUIRE(ctx, fz.qkv == nullptr || (T == 1 && nq * ATT_S <= 2 * ctx->num_sms),
                  "the form that starts from the qkv row serves one token and at most SMs / 2 query heads");
     const bool quant_rows = qo.q != nullptr && (T > 1 || qrow0 > 0 || qo.M_ld > 4);
-    INKQ_REQUIRE(ctx, !quant_rows || nq / nkv <= ATT_GMAX, "the quantizing prompt attention serves at most 4 query heads per kv head");
-    if ((T >= 16 || quant_rows) && nq / nkv <= ATT_GMAX) {   // a prompt: key/value tiles shared by 8 tokens x the heads of a kv group
-        k_attention_prefill<<<dim3((T + ATT_QT - 1) / ATT_QT, nkv), 256, 0, ctx->stream>>>(
-            q_dev, reinterpret_cast<const __half *>(k_cache_dev), reinterpret_cast<const __half *>(v_cache_dev), pos0_dev, T, nq, nkv, max_pos,
-            scale, out_dev, qo, qrow0);
-        return after_launch(ctx, "k_attention_prefill");
-    }
+    if (T >= 16 || quant_rows)   // a prompt: tensor-core kernel (attention_prefill_mma.cu), 64 tokens of one query head per CTA
+        return launch_attention_prefill_mma(ctx, q_dev, k_cache_dev, v_cache_dev, pos0_dev, T, nq, nkv, max_pos, scale, out_dev, qo, qrow0);
     if (T == 1 && nq * ATT_S <= 2 * ctx->num_sms && !quant_rows) {
         // a decode step: the keys of each head split over a cluster of ATT_S CTAs
         const int share_max = (max_pos + ATT_S - 1) / ATT_S;

@@ -167,6 +167,10 @@ int after_launch(inkq_ctx *ctx, const char *what);
 
 // kernels' host launchers (defined in the respective .cu files)
 int launch_quantize(inkq_ctx *ctx, int qmode, const float *x, int M, int K, Act *a);
+struct QuantOut;
+// prompt attention on the tensor cores (attention_prefill_mma.cu); out and / or qo.q receive the result
+int launch_attention_prefill_mma(inkq_ctx *ctx, const float *q, const uint16_t *k_cache, const uint16_t *v_cache, const int *pos0_dev, int T, int nq,
+                                 int nkv, int max_pos, float scale, float *out, const QuantOut &qo, int qrow0);
 int launch_quantize_rows(inkq_ctx *ctx, int qmode, const float *x, int m0, int rows, int M_total, int K, Act *a);
 // gu [M][2K] in (32 gate, 32 up) column groups -> the quantized rows of SiLU(gate) * up
 int launch_silu_mul_quantize(inkq_ctx *ctx, int qmode, const float *gu, int M, int K, Act *a);
