@@ -67,7 +67,7 @@ def test_silu_mul_and_residual_add(pkg, gpu, reference):
     assert np.array_equal(a.cpu().numpy(), reference.add(gate, up))
 
 
-@pytest.mark.parametrize("T,past", [(45, 0), (9, 20), (1, 329), (1, 0), (1, 2), (1, 130)])
+@pytest.mark.parametrize("T,past", [(45, 0), (70, 50), (200, 141), (9, 20), (1, 329), (1, 0), (1, 2), (1, 130)])
 def test_qk_norm_rope_cache_and_attention(pkg, gpu, reference, T, past):
     """Per-head q/k RMSNorm + RoPE + KV-cache append (QwenAttention.cc:78-121) and causal GQA attention
     (:122-190), the reference's operators chained as its forward chains them."""
