@@ -155,6 +155,7 @@ int inkq_ctx_create(int device, void *stream, inkq_ctx **out)
     ctx->pin_x = ctx->pin_c = nullptr;
     ctx->pin_x_cap = ctx->pin_c_cap = 0;
     ctx->dev_flag = nullptr;
+    ctx->host_flag = nullptr;
     ctx->encode_tiled = nullptr;
     ctx->copy_stream = nullptr;
     ctx->h2d_stream = nullptr;
@@ -173,7 +174,9 @@ int inkq_ctx_create(int device, void *stream, inkq_ctx **out)
     ctx->num_sms = prop.multiProcessorCount;
     // word 0: set by a kernel whose bounded wait ran out; word 1: ticket counter of the decode GEMV's last-CTA epilogue
     if ((e = cudaMalloc(reinterpret_cast<void **>(&ctx->dev_flag), CTX_FLAG_WORDS * sizeof(int))) != cudaSuccess ||
-        (e = cudaMemset(ctx->dev_flag, 0, CTX_FLAG_WORDS * sizeof(int))) != cudaSuccess) {
+        (e = cudaMemset(ctx->dev_flag, 0, CTX_FLAG_WORDS * sizeof(int))) != cudaSuccess ||
+        (e = cudaHostAlloc(reinterpret_cast<void **>(&ctx->host_flag), sizeof(int), cudaHostAllocDefault)) != cudaSuccess) {
+        cudaFree(ctx->dev_flag);
         delete ctx;
         return fail(nullptr, INKQ_ERR_ALLOC, std::string("context allocation: ") + cudaGetErrorString(e));
     }
@@ -201,6 +204,7 @@ int inkq_ctx_destroy(inkq_ctx *ctx)
     cudaFree(ctx->lin_x);
     cudaFree(ctx->lin_c);
     cudaFree(ctx->dev_flag);
+    cudaFreeHost(ctx->host_flag);
     if (ctx->copy_stream != nullptr) cudaStreamDestroy(ctx->copy_stream);
     if (ctx->h2d_stream != nullptr) cudaStreamDestroy(ctx->h2d_stream);
     if (ctx->start_ev != nullptr) cudaEventDestroy(ctx->start_ev);
@@ -223,9 +227,10 @@ int inkq_ctx_synchronize(inkq_ctx *ctx)
 {
     int rc = use(ctx);
     if (rc) return rc;
+    // the time-out word travels to a page-locked host word at the end of the stream: one wait covers the work and the flag
+    INKQ_CUDA(ctx, cudaMemcpyAsync(ctx->host_flag, ctx->dev_flag, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     INKQ_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    int flag = 0;
-    INKQ_CUDA(ctx, cudaMemcpy(&flag, ctx->dev_flag, sizeof(int), cudaMemcpyDeviceToHost));
+    const int flag = *static_cast<volatile int *>(ctx->host_flag);
     if (flag != 0) {
         cudaMemset(ctx->dev_flag, 0, sizeof(int));
         return fail(ctx, INKQ_ERR_TIMEOUT, "a bounded device-side wait ran out inside a kernel; its output is invalid");

@@ -101,6 +101,7 @@ struct inkq_ctx {
     uint64_t launches;
     int num_sms;
     int *dev_flag;        // device word set by a kernel whose bounded wait ran out (word 0), a ticket counter behind it
+    int *host_flag;       // page-locked host word the flag is copied to at the end of the stream in inkq_ctx_synchronize
     inkq::Act *scratch_act;  // activation scratch of inkq_linear (grown on demand)
     size_t scratch_elems;    // its capacity in activation elements (M * K)
     size_t scratch_planes;   // capacity of each of its per-block planes, in entries
