@@ -9,6 +9,8 @@ shape: M=322 activations x K=4096, N=12288 A81W41 weights (fp32 block scales).
   value   whole-job int8 TOPS (2*M*N*K per step) with inputs resident in HBM
   e2e     the same metric through the host-buffer entry point (inkq_linear_host):
           pinned host activations in, host result out, copies inside the timed region
+          (N > 1: every rank calls it on its weight rows and delivers its columns of the
+          result into one page-locked host matrix that all ranks map)
   N > 1   the weight rows (output columns) are sharded across the ranks, every rank
           quantizes the full activations and runs its shard; the QGEMM's epilogue stores
           each finished element into every rank's [M][N] buffer over peer-mapped memory
